@@ -1,0 +1,87 @@
+/* C-ABI of the B200-native NWC kernel library (nwc_b200/lib/nwc_ops.so).
+ *
+ * The ten entry points below are exactly the ones the reference's ctypes bridge binds (reference:
+ * nwc/nwc_torch.py:58-77) and have the reference's signatures, argument meaning and return codes, so the reference's
+ * own Python package runs on this library unchanged (NWC_DLL=/path/to/nwc_ops.so).  Every pointer named "device" is
+ * CUDA device memory owned by the caller; the library allocates no device memory on the decode path, launches only on
+ * the stream it is given and never synchronises there, so every decode call can be captured in a CUDA graph.
+ *
+ * `elem` carries the element type in bits 0..3 (0 = bf16, 1 = fp8 e4m3 with per-row fp32 scale) and the block layout
+ * in bits 4..7 (0 = 8 x 512 blocks, prefix code; 1 = 16 x 512 blocks in mma fragment order, prefix code; 2 = 16 x 512
+ * blocks, fixed-width ranks plus exception lists).  `n` = M * K weights, `block` must be 4096.
+ * Alignment: data, low, x, out and y must be 16-byte aligned (tensors from any CUDA allocator are).
+ */
+#ifndef NWC_OPS_H
+#define NWC_OPS_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Capabilities.  0: format version (11), 1: states per lane (1), 2: decoder table words (4096), 3: header bytes per
+   block (32), 4: block size (4096), 5: elem parameter present (1), 6: layout 1 (1), 7: layout 2 (1); else -1.
+   Replaces csrc/nwc_ops.cu:100-106. */
+int nwc_info(int what);
+
+/* out = [blocks, raw-plane bytes, scratch floats, K16].  0 ok, -1 bad shape.  Replaces csrc/nwc_ops.cu:121-126. */
+int nwc_layout(uint64_t M, uint32_t K, int elem, uint64_t *out);
+
+/* Encoder, HOST pointers in and out (w: n bf16 or fp8 values; freq, psym: uint16[1024]; bases: uint32[blocks];
+   hdr: uint8[32 * blocks]; data: cap bytes; low: raw-plane bytes).  The work runs on the current CUDA device.
+   Returns the data length including 64 bytes of slack; -1 bad shape or capacity (the caller retries with a larger
+   cap); -2 fp8 NaN; -3 more than 255 exceptions in one lane (layout 2); <= -100: -(100 + cudaError).
+   Replaces csrc/nwc_ops.cu:245-320 and 175-243. */
+int64_t nwc_encode(const void *w, uint64_t n, uint32_t K, int elem, uint16_t *freq, uint16_t *psym, uint32_t *bases,
+                   uint8_t *hdr, uint8_t *data, uint64_t cap, uint8_t *low);
+
+/* 4096-word decoder table from the symbol table (host).  Replaces csrc/nwc_ops.cu:324-348. */
+void nwc_build_tab(const uint16_t *freq, const uint16_t *psym, int elem, uint32_t *lut);
+
+/* Token path: y = bf16(scale * (W x) + bias).  x is fp32[K16] for layout 0 and bf16[K rounded up to 32] for layouts
+   1 and 2, zero beyond K; bias bf16[M] or NULL; scale fp32[M] or NULL; scratch fp32[padded rows * column blocks];
+   y bf16[M].  Returns 0, -1 bad shape / alignment, or the CUDA error of the launch.  Replaces csrc/nwc_ops.cu:1130-1141. */
+int nwc_linear_bf16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                    const uint8_t *low, const float *x, const uint16_t *bias, const float *scale, float *scratch,
+                    uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem);
+
+/* fp32 test path: y = W x with fp32 x (K16, or K rounded up to 32 for layouts 1 and 2) and fp32 y[M]; accumulates
+   with atomics after clearing y.  Replaces csrc/nwc_ops.cu:1110-1118. */
+int nwc_matvec(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+               const uint8_t *low, const float *x, float *y, uint64_t n, uint32_t block, uint32_t K, int elem);
+
+/* Whole matrix -> bf16[M][K16] (fp8: the unscaled fp8 values).  Replaces csrc/nwc_ops.cu:1121-1126. */
+int nwc_dequant(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                const uint8_t *low, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem);
+
+/* Rows ids[0..n_ids) -> bf16[n_ids][K16]; ids outside [0, M) leave their output row untouched.
+   Replaces csrc/nwc_ops.cu:1143-1160. */
+int nwc_gather(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+               const uint8_t *low, const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block,
+               uint32_t K, int elem);
+
+/* Uncompressed fp8 weight-only matvec (bandwidth baseline): y = bf16(scale * (W8 x)), x fp32[K16].
+   Replaces csrc/nwc_ops.cu:1163-1168. */
+int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint64_t M, uint32_t K);
+
+/* SM count of the current device; prepares the kernels for it.  Replaces csrc/nwc_ops.cu:1170-1192. */
+int nwc_setup(void);
+
+/* ---- additions of this library (no counterpart in the reference) ------------------------------------------------ */
+
+/* nwc_encode with DEVICE pointers for w, bases, hdr, data and low (psym stays host memory): lets a model that is
+   already on the GPU be converted without a host round trip.  Synchronises `stream`.  Same return codes. */
+int64_t nwc_encode_device(void *stream, const void *w, uint64_t n, uint32_t K, int elem, uint16_t *psym, uint32_t *bases,
+                          uint8_t *hdr, uint8_t *data, uint64_t cap, uint8_t *low);
+
+/* nwc_linear_bf16 with the number of K splits forced (1 .. column blocks; 0 = automatic): used by tests to cover both
+   the direct-write and the partial-sum path on any shape. */
+int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr,
+                           const uint32_t *lut, const uint8_t *low, const float *x, const uint16_t *bias,
+                           const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K,
+                           int elem, uint32_t splits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

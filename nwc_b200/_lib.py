@@ -1,0 +1,68 @@
+"""ctypes bridge to nwc_ops.so (the C-ABI declared in include/nwc_ops.h).
+
+Search order: the NWC_DLL environment variable (A/B tests against another build), then nwc_b200/lib/nwc_ops.so.  There
+is no fallback: without the CUDA library the package does not import.  Mirrors the binding block of the reference's
+bridge (reference: nwc/nwc_torch.py:14-82).
+"""
+import ctypes
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "nwc_ops.so"
+
+
+def find_library() -> str:
+    tried = []
+    for cand in (os.environ.get("NWC_DLL"), os.path.join(HERE, "lib", LIB_NAME)):
+        if not cand: continue
+        tried.append(cand)
+        if os.path.exists(cand): return cand
+    raise ImportError("nwc_b200: kernel library not found (run `python -m nwc_b200.build`, needs nvcc); looked for " + ", ".join(tried))
+
+
+LIB_PATH = find_library()
+lib = ctypes.CDLL(LIB_PATH)
+
+P, U64, U32, I = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int
+_SIGNATURES = {
+    "nwc_info": (I, [I]),
+    "nwc_layout": (I, [U64, U32, I, P]),
+    "nwc_encode": (ctypes.c_int64, [P, U64, U32, I, P, P, P, P, P, U64, P]),
+    "nwc_encode_device": (ctypes.c_int64, [P, P, U64, U32, I, P, P, P, P, U64, P]),
+    "nwc_build_tab": (None, [P, P, I, P]),
+    "nwc_linear_bf16": (I, [P, P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I]),
+    "nwc_linear_bf16_splits": (I, [P, P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I, U32]),
+    "nwc_matvec": (I, [P, P, P, P, P, P, P, P, U64, U32, U32, I]),
+    "nwc_dequant": (I, [P, P, P, P, P, P, P, U64, U32, U32, I]),
+    "nwc_gather": (I, [P, P, P, P, P, P, P, U32, P, U64, U32, U32, I]),
+    "nwc_ref_fp8": (I, [P, P, P, P, P, U64, U32]),
+    "nwc_setup": (I, []),
+}
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)            # AttributeError here = a library that does not implement the C-ABI
+    _fn.restype, _fn.argtypes = _res, _args
+
+VERSION = lib.nwc_info(0)
+TAB_WORDS = lib.nwc_info(2)
+HDR_BLOCK = lib.nwc_info(3)
+FIXED_BLOCK = lib.nwc_info(4)
+NPAIR = 1024                      # length of the freq / psym arrays of the encoder interface
+RAW_SLACK = 512                   # bytes after the raw plane: the plane is read one super-chunk slot ahead
+LANES = 32
+
+SM_COUNT = lib.nwc_setup() if torch.cuda.is_available() else 0
+
+
+def ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def require_cuda():
+    if not torch.cuda.is_available():
+        raise RuntimeError("nwc_b200 runs on CUDA devices only (no CPU path)")

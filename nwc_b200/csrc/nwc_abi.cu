@@ -1,0 +1,122 @@
+/* extern "C" surface of nwc_ops.so: argument checks, per-device set-up and dispatch.  See include/nwc_ops.h for the
+ * contract of every entry point and the reference interface it replaces. */
+#include <mutex>
+#include "../../include/nwc_ops.h"
+#include "nwc_encode.h"
+#include "nwc_launch.h"
+
+#define NWC_EXPORT extern "C" __attribute__((visibility("default")))
+
+using namespace nwc;
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices];         /* 0 = device not prepared yet */
+std::mutex g_setup_lock;
+
+/* SM count of the current device, preparing the kernels' shared-memory opt-in on first use of that device */
+int device_sms() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    if (g_sm_count[dev]) return g_sm_count[dev];
+    std::lock_guard<std::mutex> hold(g_setup_lock);
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
+    configure_segment_kernels();
+    g_sm_count[dev] = sms;
+    return sms;
+}
+
+bool shape_ok(uint64_t n, uint32_t block, uint32_t K) { return block == kBlockWeights && K != 0 && n != 0 && n % K == 0 && n / K <= 0xFFFFFFFFull; }
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int run_segments(int mode, void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                 const uint8_t *low, const void *x, float *y32, uint16_t *out, const uint16_t *bias, const float *scale, uint16_t *y,
+                 uint64_t n, uint32_t block, uint32_t K, int elem, uint32_t splits) {
+    if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1) return -1;
+    if (!aligned16(data) || !aligned16(low) || !aligned16(lut) || (x && !aligned16(x)) || (out && !aligned16(out))) return -1;
+    const int sms = device_sms();
+    if (!sms) return (int)cudaErrorNoDevice;
+    SegmentArgs a{data, bases, hdr, lut, low, x, y32, out, bias, scale, y, (uint32_t)(n / K), K, splits};
+    const Geometry g(a.M, K, layout_of(elem));
+    if (a.splits > g.CB) a.splits = g.CB;
+    return (int)launch_segments(mode, elem, sms, (cudaStream_t)stream, a);
+}
+
+}  // namespace
+
+NWC_EXPORT int nwc_info(int what) {
+    switch (what) {
+        case 0: return kFormatVersion;
+        case 1: return 1;
+        case 2: return (int)kTableWords;
+        case 3: return (int)kLanes;
+        case 4: return (int)kBlockWeights;
+        case 5: case 6: case 7: return 1;
+        default: return -1;
+    }
+}
+
+NWC_EXPORT int nwc_layout(uint64_t M, uint32_t K, int elem, uint64_t *out) {
+    if (!M || !K || M > 0xFFFFFFFFull) return -1;
+    const Geometry g((uint32_t)M, K, layout_of(elem));
+    out[0] = g.nb; out[1] = g.raw_plane_bytes(elem); out[2] = g.scratch_floats(); out[3] = g.K16;
+    return 0;
+}
+
+NWC_EXPORT int64_t nwc_encode(const void *w, uint64_t n, uint32_t K, int elem, uint16_t *freq, uint16_t *psym, uint32_t *bases,
+                              uint8_t *hdr, uint8_t *data, uint64_t cap, uint8_t *low) {
+    return encode_host(w, n, K, elem, freq, psym, bases, hdr, data, cap, low);
+}
+
+NWC_EXPORT int64_t nwc_encode_device(void *stream, const void *w, uint64_t n, uint32_t K, int elem, uint16_t *psym, uint32_t *bases,
+                                     uint8_t *hdr, uint8_t *data, uint64_t cap, uint8_t *low) {
+    if (!K || !n || n % K || n / K > 0xFFFFFFFFull) return -1;
+    return encode_device((cudaStream_t)stream, w, n, K, elem, psym, bases, hdr, data, cap, low);
+}
+
+NWC_EXPORT void nwc_build_tab(const uint16_t *freq, const uint16_t *psym, int elem, uint32_t *lut) { (void)freq; build_table(psym, elem, lut); }
+
+NWC_EXPORT int nwc_linear_bf16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                               const uint8_t *low, const float *x, const uint16_t *bias, const float *scale, float *scratch, uint16_t *y,
+                               uint64_t n, uint32_t block, uint32_t K, int elem) {
+    return run_segments(0, stream, data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, n, block, K, elem, 0);
+}
+
+NWC_EXPORT int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                                      const uint8_t *low, const float *x, const uint16_t *bias, const float *scale, float *scratch,
+                                      uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, uint32_t splits) {
+    return run_segments(0, stream, data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, n, block, K, elem, splits);
+}
+
+NWC_EXPORT int nwc_matvec(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                          const uint8_t *low, const float *x, float *y, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    if (!shape_ok(n, block, K)) return -1;
+    const cudaError_t e = cudaMemsetAsync(y, 0, 4ull * (n / K), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    return run_segments(2, stream, data, bases, hdr, lut, low, x, y, nullptr, nullptr, nullptr, nullptr, n, block, K, elem, 0);
+}
+
+NWC_EXPORT int nwc_dequant(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                           const uint8_t *low, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    return run_segments(1, stream, data, bases, hdr, lut, low, nullptr, nullptr, out, nullptr, nullptr, nullptr, n, block, K, elem, 0);
+}
+
+NWC_EXPORT int nwc_gather(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                          const uint8_t *low, const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1) return -1;
+    if (n_ids == 0) return 0;
+    if (!aligned16(data) || !aligned16(low) || !aligned16(lut) || !aligned16(out)) return -1;
+    if (!device_sms()) return (int)cudaErrorNoDevice;
+    SegmentArgs a{data, bases, hdr, lut, low, nullptr, nullptr, out, nullptr, nullptr, nullptr, (uint32_t)(n / K), K, 1};
+    return (int)launch_gather(elem, (cudaStream_t)stream, a, ids, n_ids);
+}
+
+NWC_EXPORT int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint64_t M, uint32_t K) {
+    if (!M || !K || M > 0xFFFFFFFFull) return -1;
+    if (((K & 15u) == 0u) && (!aligned16(w) || !aligned16(x))) return -1;
+    return (int)launch_native_fp8((cudaStream_t)stream, w, scale, x, y, (uint32_t)M, K);
+}
+
+NWC_EXPORT int nwc_setup(void) { return device_sms(); }

@@ -1,0 +1,35 @@
+/* Host-side launch interface between the C-ABI layer and the kernel translation units. */
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "nwc_geometry.h"
+
+namespace nwc {
+
+constexpr uint32_t kSegmentThreads = 512;   /* 16 warps per CTA, one CTA per SM */
+
+/* Arguments of the segment kernels; every pointer is device memory owned by the caller. */
+struct SegmentArgs {
+    const uint8_t *data;        /* lane streams (layouts 0, 1) or exception entries (layout 2)              */
+    const uint32_t *bases;      /* byte offset of every block inside data                                   */
+    const uint8_t *hdr;         /* per block and lane: stream words (layouts 0, 1) or exception count        */
+    const uint32_t *lut;        /* 4096-word decoder table                                                   */
+    const uint8_t *low;         /* raw plane(s)                                                              */
+    const void *x;              /* activation vector: fp32 or bf16, see nwc_linear_bf16                      */
+    float *y32;                 /* fp32 partial sums [padded rows][splits], or the fp32 result of nwc_matvec */
+    uint16_t *out;              /* dequantised matrix, row stride K16                                        */
+    const uint16_t *bias;       /* bf16 or null                                                              */
+    const float *scale;         /* fp32 per row or null                                                      */
+    uint16_t *y;                /* bf16 result                                                               */
+    uint32_t M, K;
+    uint32_t splits;            /* K splits per row group; 0 = let the launcher choose                       */
+};
+
+uint32_t choose_splits(const Geometry &g, int mode, int sms);
+cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a);
+void configure_segment_kernels();
+
+cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids);
+cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);
+
+}  // namespace nwc
