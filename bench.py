@@ -1,0 +1,217 @@
+"""Benchmark of the NWC batch-1 decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--model qwen3-0.6b] [--layout 0] [--elem bf16]
+
+Workload (N = 1): a Qwen3-0.6B-architecture decoder with random-init weights of the reference's distribution
+(W = r_i * 0.02 * z, r_i log-normal(0, 0.3), norms 1), compressed bf16 layout 0, batch 1, 32 random prompt ids, greedy
+decode replayed as one CUDA graph per token.  A step is one decoded token.
+  value     tokens/s of K graph replays, device-timed, nothing copied to or from the host inside the region
+  e2e       the same through DecodeEngine.step(): token id from pinned host memory in, next token id back, every step
+  roofline  the dominant kernel (the fused decode-matvec on the lm_head matrix, larger than L2) launched back to back:
+            algorithmic bytes (the reference's own per-matrix byte count) / CUDA-event time, against the measured HBM peak
+  cpu_baseline  the CPU oracle's fused decode+matvec on all host cores over a bounded sample (one decoder layer plus
+            1/8 of the lm_head rows), extrapolated to a whole token
+With N > 1 (torchrun, one rank per GPU) every rank decodes its own sequence on its own replica of the model: no
+data-path collective, weak scaling; value = N * K / max-over-ranks time.
+--impl reference runs the CPU path alone (rank 0), each step one pass over the bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path: sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--model", default="qwen3-0.6b")
+    ap.add_argument("--layout", type=int, default=0)
+    ap.add_argument("--elem", default="bf16")
+    ap.add_argument("--prompt", type=int, default=32)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f: return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    QUERY = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True); self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout: self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None: return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25); self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU path (oracle port of the reference's format; the reference ships no compiled CPU decoder for formats v9+)
+
+def cpu_sample(cfg, layout, elem_code, threads, repeats=1):
+    """Seconds per token of the CPU fused decode+matvec, extrapolated from one layer + 1/8 of the lm_head rows."""
+    import numpy as np
+    import oracle as O
+    code = O.code_of(elem_code, layout)
+    shapes = [("qkv", cfg.qkv_rows, cfg.hidden), ("o", cfg.hidden, cfg.n_q * cfg.head_dim), ("gate_up", 2 * cfg.intermediate, cfg.hidden),
+              ("down", cfg.hidden, cfg.intermediate), ("lm_head/8", cfg.vocab // 8, cfg.hidden)]
+    packed = []
+    for i, (name, M, K) in enumerate(shapes):
+        w, x = O.synth_weights(M, K, 1000 + i)
+        src = w
+        if elem_code: src, _ = O.quantize_fp8(w)
+        packed.append((O.encode(src, code), O.bf16_to_f32(x)))
+    times = []
+    for _ in range(repeats):
+        per = []
+        for p, x in packed:
+            t = time.perf_counter(); O.matvec_f32(p, x, threads=threads); per.append(time.perf_counter() - t)
+        times.append(cfg.layers * sum(per[:4]) + 8.0 * per[4])
+    return times, "1 decoder layer (qkv, o, gate_up, down) + 1/8 of the lm_head rows per pass, extrapolated to layers x layer + 8 x slice"
+
+
+def run_reference(a, cfg):
+    threads = os.cpu_count() or 1
+    elem_code = 1 if a.elem == "fp8" else 0
+    for _ in range(max(0, min(a.warmup, 1))): cpu_sample(cfg, a.layout, elem_code, threads)
+    steps = max(1, min(a.steps, 8))
+    times, what = cpu_sample(cfg, a.layout, elem_code, threads, repeats=steps)
+    sec = statistics.mean(times)
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": a.gpus, "steps": steps, "warmup": min(a.warmup, 1),
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
+            "config": workload(a, cfg), "cpu_baseline": {"value": 1.0 / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what},
+            "e2e": {"value": 1.0 / sec, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload(a, cfg):
+    return {"workload": f"{cfg.name}-architecture decoder, random init, NWC {a.elem} layout {a.layout}, batch 1, {a.prompt} random prompt ids, greedy decode as a CUDA graph",
+            "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "l2_policy": "weights streamed per token (0.8 GB) exceed the 126 MB L2; roofline kernel input (lm_head, 214 MB) exceeds L2"}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+
+def main():
+    a = parse()
+    from nwc_b200.decode import PRESETS  # the package import fails loudly when the CUDA library is missing
+    cfg = PRESETS[a.model]
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if a.impl == "reference":
+        if rank == 0: run_reference(a, cfg)
+        return
+    import torch
+    from nwc_b200.decode import DecodeEngine, DecoderWeights
+    from nwc_b200 import _lib as L
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
+    eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16)
+    eng.capture()
+    g = torch.Generator().manual_seed(1234 + rank)
+    prompt = torch.randint(0, cfg.vocab, (a.prompt,), generator=g)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None: dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: K graph replays, device-timed ----
+    eng.prefill(prompt)
+    for _ in range(a.warmup): eng._run()
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(a.steps): eng._run()
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1)
+    clocks = sampler.stop() if sampler else None
+    if int(eng.status.item()): raise RuntimeError("decode position left the KV cache")
+    # ---- e2e: host token in, host token out, every step ----
+    eng.prefill(prompt)
+    tok = int(eng.cur.item())
+    for _ in range(a.warmup): tok = eng.step(tok)
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(a.steps): tok = eng.step(tok)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - w0) * 1e3
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if dist is not None: dist.destroy_process_group()
+        return
+    # ---- roofline of the dominant kernel: lm_head matvec back to back inside one graph ----
+    peak, peak_kind = measured_peak()
+    w = weights.lm_head
+    reps = 20
+    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side): eng._linear(w, eng.xn, eng.logits)
+    torch.cuda.current_stream().wait_stream(side)
+    kg = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(kg):
+        for _ in range(reps): eng._linear(w, eng.xn, eng.logits)
+    for _ in range(3): kg.replay()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record(); kg.replay(); k1.record(); torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / reps
+    achieved = w.bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "segment_kernel (fused decode-matvec), lm_head %dx%d layout %d" % (w.out_features, w.in_features, w.layout),
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "bytes_per_launch": w.bytes, "us_per_launch": kernel_ms * 1e3,
+                "model_bytes_per_token": weights.bytes_per_token(), "model_frac_of_roofline": weights.bytes_per_token() / (ms / a.steps * 1e-3) / 1e9 / peak}
+    cpu = None
+    if not a.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        times, what = cpu_sample(cfg, a.layout, 1 if a.elem == "fp8" else 0, threads, repeats=2)
+        cpu = {"value": 1.0 / min(times), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what}
+    line = {"metric": "decode_tokens_per_s", "value": world * a.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
+            "config": dict(workload(a, cfg), parallelism="replicas x%d (no data-path collective)" % world if world > 1 else "1 GPU"),
+            "e2e": {"value": world * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+            "gpu_launches": a.steps * eng.launches_per_step, "launches_per_step": eng.launches_per_step,
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line))
+    if dist is not None: dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

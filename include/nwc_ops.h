@@ -81,6 +81,44 @@ int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const uint32_t *ba
                            const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K,
                            int elem, uint32_t splits);
 
+/* Status word of the kernels' bounded waits: 0, or 2 when a warp gave up waiting for a bulk copy (its rows are then
+   missing from y).  Synchronises the device; clear != 0 resets the word. */
+int nwc_kernel_status(int clear);
+
+/* on = 0 routes every call through the kernels that load with plain vector loads instead of bulk-copy rings (A/B
+   tests); on = 1 (default) restores the rings. */
+void nwc_set_ring_kernels(int on);
+
+/* nwc_linear_bf16 with a bf16 activation vector for every layout (layout 0: bf16[K16]; layouts 1, 2: bf16[K rounded up
+   to 32]): the decode loop keeps activations in bf16, which spares layout 0 the fp32 copy and the second mma pass. */
+int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                   const uint8_t *low, const uint16_t *x, const uint16_t *bias, const float *scale, float *scratch,
+                   uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem);
+
+/* ---- decode-step kernels (the reference leaves these operations to Transformers eager code inside its CUDA graph,
+   scripts/graph_decode.py:46-60; there is no reference library entry point for them) ------------------------------- */
+
+/* h <- bf16(h + delta) (delta may be NULL); xn16 <- bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))); xn32 (may be NULL)
+   receives the same values as fp32.  All vectors have H elements. */
+int nwc_add_rmsnorm(void *stream, uint16_t *h, const uint16_t *delta, const uint16_t *weight, float eps, uint32_t H,
+                    uint16_t *xn16, float *xn32);
+
+/* One token of grouped-query attention.  qkv = [n_q | n_kv | n_kv] heads x head_dim (bf16) of the token at position
+   *pos; q_norm / k_norm: per-head RMSNorm weights (bf16[head_dim]) or NULL; cos_t / sin_t: bf16[max positions][head_dim];
+   k_cache / v_cache: bf16[n_kv][max_len][head_dim], appended at *pos; out: bf16[n_q * head_dim].
+   *status is set to 1 (and nothing is written) when *pos is outside [0, max_len). */
+int nwc_attention_decode(void *stream, const uint16_t *qkv, const uint16_t *q_norm, const uint16_t *k_norm,
+                         const uint16_t *cos_t, const uint16_t *sin_t, uint16_t *k_cache, uint16_t *v_cache,
+                         const int32_t *pos, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_len, float eps,
+                         uint16_t *out, int *status);
+
+/* a16 <- bf16(bf16(silu(gate)) * up) with gate = gate_up[0..I), up = gate_up[I..2I); a32 (may be NULL) as fp32 */
+int nwc_swiglu(void *stream, const uint16_t *gate_up, uint32_t I, uint16_t *a16, float *a32);
+
+/* Greedy choice over bf16 logits[V] (lowest index wins ties): cur[0] <- token, log[*step] <- token (log may be NULL),
+   then *pos += 1 and *step += 1. */
+int nwc_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step);
+
 #ifdef __cplusplus
 }
 #endif

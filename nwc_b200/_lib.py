@@ -19,7 +19,7 @@ def find_library() -> str:
         if not cand: continue
         tried.append(cand)
         if os.path.exists(cand): return cand
-    raise ImportError("nwc_b200: kernel library not found (run `python -m nwc_b200.build`, needs nvcc); looked for " + ", ".join(tried))
+    raise ImportError("nwc_b200: kernel library not found (run `python nwc_b200/build.py`, needs nvcc); looked for " + ", ".join(tried))
 
 
 LIB_PATH = find_library()
@@ -34,11 +34,18 @@ _SIGNATURES = {
     "nwc_build_tab": (None, [P, P, I, P]),
     "nwc_linear_bf16": (I, [P, P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_linear_bf16_splits": (I, [P, P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I, U32]),
+    "nwc_linear_x16": (I, [P, P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I]),
+    "nwc_add_rmsnorm": (I, [P, P, P, P, ctypes.c_float, U32, P, P]),
+    "nwc_attention_decode": (I, [P, P, P, P, P, P, P, P, P, U32, U32, U32, U32, ctypes.c_float, P, P]),
+    "nwc_swiglu": (I, [P, P, U32, P, P]),
+    "nwc_argmax": (I, [P, P, U32, P, P, P, P]),
     "nwc_matvec": (I, [P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_dequant": (I, [P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_gather": (I, [P, P, P, P, P, P, P, U32, P, U64, U32, U32, I]),
     "nwc_ref_fp8": (I, [P, P, P, P, P, U64, U32]),
     "nwc_setup": (I, []),
+    "nwc_kernel_status": (I, [I]),
+    "nwc_set_ring_kernels": (None, [I]),
 }
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)            # AttributeError here = a library that does not implement the C-ABI

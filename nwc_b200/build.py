@@ -1,6 +1,8 @@
 """Builds nwc_b200/lib/nwc_ops.so from nwc_b200/csrc with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m nwc_b200.build [--verbose]
+    python nwc_b200/build.py [--verbose]
+
+Run it as a script (or load it by path): importing the nwc_b200 package needs the library this step produces.
 """
 import os
 import subprocess
@@ -9,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "lib", "nwc_ops.so")
-SOURCES = ["nwc_abi.cu", "nwc_kernels.cu", "nwc_gather.cu", "nwc_encode.cu"]
+SOURCES = ["nwc_abi.cu", "nwc_kernels.cu", "nwc_gather.cu", "nwc_encode.cu", "nwc_model.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared", "-Xcompiler", "-fPIC",
          "-Xcompiler", "-fvisibility=hidden"]
 

@@ -33,12 +33,12 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 int run_segments(int mode, void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                  const uint8_t *low, const void *x, float *y32, uint16_t *out, const uint16_t *bias, const float *scale, uint16_t *y,
-                 uint64_t n, uint32_t block, uint32_t K, int elem, uint32_t splits) {
+                 uint64_t n, uint32_t block, uint32_t K, int elem, uint32_t splits, int x_bf16 = 0) {
     if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1) return -1;
     if (!aligned16(data) || !aligned16(low) || !aligned16(lut) || (x && !aligned16(x)) || (out && !aligned16(out))) return -1;
     const int sms = device_sms();
     if (!sms) return (int)cudaErrorNoDevice;
-    SegmentArgs a{data, bases, hdr, lut, low, x, y32, out, bias, scale, y, (uint32_t)(n / K), K, splits};
+    SegmentArgs a{data, bases, hdr, lut, low, x, y32, out, bias, scale, y, (uint32_t)(n / K), K, splits, x_bf16, 0};
     const Geometry g(a.M, K, layout_of(elem));
     if (a.splits > g.CB) a.splits = g.CB;
     return (int)launch_segments(mode, elem, sms, (cudaStream_t)stream, a);
@@ -90,6 +90,12 @@ NWC_EXPORT int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const u
     return run_segments(0, stream, data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, n, block, K, elem, splits);
 }
 
+NWC_EXPORT int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                              const uint8_t *low, const uint16_t *x, const uint16_t *bias, const float *scale, float *scratch, uint16_t *y,
+                              uint64_t n, uint32_t block, uint32_t K, int elem) {
+    return run_segments(0, stream, data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, n, block, K, elem, 0, 1);
+}
+
 NWC_EXPORT int nwc_matvec(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                           const uint8_t *low, const float *x, float *y, uint64_t n, uint32_t block, uint32_t K, int elem) {
     if (!shape_ok(n, block, K)) return -1;
@@ -109,7 +115,7 @@ NWC_EXPORT int nwc_gather(void *stream, const uint8_t *data, const uint32_t *bas
     if (n_ids == 0) return 0;
     if (!aligned16(data) || !aligned16(low) || !aligned16(lut) || !aligned16(out)) return -1;
     if (!device_sms()) return (int)cudaErrorNoDevice;
-    SegmentArgs a{data, bases, hdr, lut, low, nullptr, nullptr, out, nullptr, nullptr, nullptr, (uint32_t)(n / K), K, 1};
+    SegmentArgs a{data, bases, hdr, lut, low, nullptr, nullptr, out, nullptr, nullptr, nullptr, (uint32_t)(n / K), K, 1, 0, 0};
     return (int)launch_gather(elem, (cudaStream_t)stream, a, ids, n_ids);
 }
 
@@ -120,3 +126,7 @@ NWC_EXPORT int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, c
 }
 
 NWC_EXPORT int nwc_setup(void) { return device_sms(); }
+
+NWC_EXPORT int nwc_kernel_status(int clear) { return read_kernel_status(clear != 0); }
+
+NWC_EXPORT void nwc_set_ring_kernels(int on) { set_ring_kernels(on != 0); }

@@ -22,6 +22,7 @@
  * kern_f32_to_bf16_bias 553-565.
  */
 #include "nwc_decode.cuh"
+#include "nwc_async.cuh"
 #include "nwc_launch.h"
 
 namespace nwc {
@@ -69,7 +70,7 @@ __device__ __forceinline__ uint4 raw_row16(const uint8_t *p, bool ok) {
     return ldg_stream128(p);
 }
 
-template <int ELEM, int MODE>
+template <int ELEM, int MODE, bool XF32>
 __device__ __forceinline__ void segment_layout0(const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb0, uint32_t cb1,
                                                 uint32_t split, uint32_t lane, uint32_t table, const uint8_t *sym, float *stash) {
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
@@ -86,7 +87,7 @@ __device__ __forceinline__ void segment_layout0(const SegmentArgs &a, const Geom
         if (lane * 32u < total) prefetch_l2(stream + lane * 128u);
         BitWindow<MR> W; W.open(reinterpret_cast<const uint32_t *>(stream) + before);
 
-        XFrag8<true> xa, xb;                                    /* columns 0..7 and 8..15 of the lane */
+        XFrag8<XF32> xa, xb;                                    /* columns 0..7 and 8..15 of the lane */
         if (MODE != kModeDequant) {
             if (col_ok) { xa.load(a.x, col0); xb.load(a.x, col0 + 8u); } else { xa.zero(); xb.zero(); }
         }
@@ -120,10 +121,10 @@ __device__ __forceinline__ void segment_layout0(const SegmentArgs &a, const Geom
                 uint32_t e01, e23; W.quad(table, sym, e01, e23);
                 pb[2 * k] = weave<0>(wb[k], e01); pb[2 * k + 1] = weave<2>(wb[k], e23);
                 if (MODE != kModeDequant) {
-                    const XFrag8<true> &xf = k < 2 ? xa : xb;
+                    const XFrag8<XF32> &xf = k < 2 ? xa : xb;
                     const int w = 2 * (k & 1);
                     mma_bf16(d, pa[2 * k], pb[2 * k], pa[2 * k + 1], pb[2 * k + 1], xf.head[w], xf.head[w + 1]);
-                    mma_bf16(d, pa[2 * k], pb[2 * k], pa[2 * k + 1], pb[2 * k + 1], xf.tail[w], xf.tail[w + 1]);
+                    if (XF32) mma_bf16(d, pa[2 * k], pb[2 * k], pa[2 * k + 1], pb[2 * k + 1], xf.tail[w], xf.tail[w + 1]);
                 }
             }
             if (MODE == kModeDequant) {
@@ -158,12 +159,11 @@ __device__ __forceinline__ void store_fragment(const SegmentArgs &a, const Geome
     if (row0 + r + 8u < g.M) *reinterpret_cast<uint2 *>(o + (uint64_t)8u * g.K16) = make_uint2(a1, a3);
 }
 
-template <int ELEM, int MODE>
+template <int ELEM, int MODE, bool XF32>
 __device__ __forceinline__ void segment_layout1(const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb0, uint32_t cb1,
                                                 uint32_t split, uint32_t lane, uint32_t table, const uint8_t *sym) {
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
     constexpr uint32_t RB = ELEM == kFp8 ? 8u : 16u;             /* raw bytes per lane and super-chunk */
-    constexpr bool XF32 = MODE == kModeAtomic;
     const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 16u;
     float d[4] = {0.f, 0.f, 0.f, 0.f};
     for (uint32_t cb = cb0; cb < cb1; cb++) {
@@ -201,10 +201,9 @@ __device__ __forceinline__ void segment_layout1(const SegmentArgs &a, const Geom
 }
 
 /* ---- layout 2 ----------------------------------------------------------------------------------------------------- */
-template <int ELEM, int MODE, int SC_PARITY>
+template <int ELEM, int MODE, bool XF32, int SC_PARITY>
 __device__ __forceinline__ void fixed_super_chunk(const SegmentArgs &a, const Geometry &g, const FixedTables &t, uint2 nib, uint4 raw,
                                                   uint32_t f0, uint32_t f1, uint32_t f2, uint32_t row0, uint32_t r, uint32_t kc, float (&d)[4]) {
-    constexpr bool XF32 = MODE == kModeAtomic;
     XFrag8<XF32> xf;
     if (MODE != kModeDequant) xf.load(a.x, kc);
     const uint32_t c[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -221,7 +220,7 @@ __device__ __forceinline__ void fixed_super_chunk(const SegmentArgs &a, const Ge
     }
 }
 
-template <int ELEM, int MODE>
+template <int ELEM, int MODE, bool XF32>
 __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb0, uint32_t cb1,
                                                 uint32_t split, uint32_t lane) {
     constexpr uint32_t ES = ELEM == kFp8 ? 2u : 3u;              /* bytes per exception entry */
@@ -241,10 +240,10 @@ __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geom
                                f2 = ldg_stream32(reinterpret_cast<const uint32_t *>(fp + 2u * kLanes * 4u));
                 fp += 3u * kLanes * 4u;
                 const uint2 n0 = ldg_stream64(np);
-                fixed_super_chunk<ELEM, MODE, 0>(a, g, t, n0, make_uint4(0u, 0u, 0u, 0u), f0, f1, f2, row0, r, kbase + sc * 32u, d);
+                fixed_super_chunk<ELEM, MODE, XF32, 0>(a, g, t, n0, make_uint4(0u, 0u, 0u, 0u), f0, f1, f2, row0, r, kbase + sc * 32u, d);
                 if (sc + 1u < nsc) {
                     const uint2 n1 = ldg_stream64(np + kLanes * 8u);
-                    fixed_super_chunk<ELEM, MODE, 1>(a, g, t, n1, make_uint4(0u, 0u, 0u, 0u), f0, f1, f2, row0, r, kbase + (sc + 1u) * 32u, d);
+                    fixed_super_chunk<ELEM, MODE, XF32, 1>(a, g, t, n1, make_uint4(0u, 0u, 0u, 0u), f0, f1, f2, row0, r, kbase + (sc + 1u) * 32u, d);
                 }
                 np += 2u * kLanes * 8u;
             }
@@ -256,7 +255,7 @@ __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geom
                 const uint2 nib = nib_ahead; const uint4 raw = raw_ahead;
                 np += kLanes * 8u; rp += kLanes * 16u;           /* one slot ahead: covered by the plane's slack */
                 nib_ahead = ldg_stream64(np); raw_ahead = ldg_stream128(rp);
-                fixed_super_chunk<ELEM, MODE, 0>(a, g, t, nib, raw, 0u, 0u, 0u, row0, r, kbase + sc * 32u, d);
+                fixed_super_chunk<ELEM, MODE, XF32, 0>(a, g, t, nib, raw, 0u, 0u, 0u, row0, r, kbase + sc * 32u, d);
             }
         }
         /* exceptions of this lane: (stream index, value) entries; their plane entries decoded to +-0 above */
@@ -268,7 +267,7 @@ __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geom
                 const uint32_t i = ep[0], j = i & 15u, col = cb * kBlockCols + (i >> 4) * 32u + frag_col(lane, j), upper = (j >> 1) & 1u;
                 const float w = ELEM == kFp8 ? fp8_to_float(ep[1]) : __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
                 if (MODE == kModeDequant) { a.out[(uint64_t)(row0 + r + 8u * upper) * g.K16 + col] = (uint16_t)(__float_as_uint(w) >> 16); continue; }
-                const float xv = MODE == kModeLinear ? bf16_to_float(__ldg(static_cast<const uint16_t *>(a.x) + col)) : __ldg(static_cast<const float *>(a.x) + col);
+                const float xv = XF32 ? __ldg(static_cast<const float *>(a.x) + col) : bf16_to_float(__ldg(static_cast<const uint16_t *>(a.x) + col));
                 if (upper) ex_hi = fmaf(w, xv, ex_hi); else ex_lo = fmaf(w, xv, ex_lo);
             }
         }
@@ -280,8 +279,318 @@ __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geom
     }
 }
 
+/* ---- layout 2, token path, bf16: planes streamed through a per-warp ring of bulk copies ------------------------------ */
+/* Work split.  The matrix is one flat sequence of super-chunk slots (row-group-major; both planes are contiguous in that
+   order).  Every warp of the persistent grid takes an equal, contiguous run of `per` slots, so all warps finish together
+   whatever the shape.  A row group that is cut by a run boundary gets one fp32 partial per warp that touched it (at most
+   `parts` per row, in the caller's scratch) and a small finalize kernel adds them in warp order; when no run boundary
+   falls inside a row group the warp writes bf16 y itself.
+   Data path.  A stage holds kRingSlots slots of both planes (256 B of nibbles and 512 B of low bytes per slot, each slot
+   lane-contiguous).  The warp keeps kRingStages stages in flight, so it never waits for HBM once the ring is full. */
+constexpr uint32_t kRingThreads = 1024, kRingSlots = 2, kRingStages = 4;
+constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
+constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes + kRingStages * 8u;
+
+struct FlatPlan {
+    uint32_t units_per_group;   /* slots (layout 2) per row group                                   */
+    uint32_t per;               /* units per warp                                                   */
+    uint32_t parts;             /* row stride of the partial sums = most warps that share a row group */
+    uint32_t direct;            /* 1: no row group is cut, warps write y themselves                  */
+};
+
+__device__ __forceinline__ void emit_flat(const SegmentArgs &a, const FlatPlan &p, uint32_t row, uint32_t part, float v) {
+    if (!p.direct) { a.y32[(uint64_t)row * p.parts + part] = v; return; }
+    if (row >= a.M) return;
+    if (a.scale) v *= __ldg(a.scale + row);
+    if (a.bias) v += bf16_to_float(__ldg(a.bias + row));
+    a.y[row] = bf16_round(v);
+}
+
+__global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan) {
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, r = lane >> 2, q = lane & 3u;
+    const uint32_t ring = smem_addr(ring_smem) + warp * kRingWarpBytes, bars = ring + kRingStages * kRingStageBytes;
+    const Geometry g(a.M, a.K, 2);
+    const uint32_t total = g.groups * g.slots, w = blockIdx.x * (kRingThreads / 32u) + warp;
+    const uint64_t u0 = (uint64_t)w * plan.per;
+    if (u0 >= total) return;
+    const uint32_t u1 = (uint32_t)min((uint64_t)total, u0 + plan.per), n_stage = (u1 - (uint32_t)u0 + kRingSlots - 1u) / kRingSlots;
+    if (lane == 0) { for (uint32_t b = 0; b < kRingStages; b++) mbar_init(bars + b * 8u, 1u); mbar_init_fence(); }
+    __syncwarp();
+    const uint8_t *nib_plane = a.low + u0 * 256u, *raw_plane = a.low + g.nibble_plane_bytes() + u0 * 512u;
+    auto issue = [&](uint32_t st) {                              /* lane 0: arm the barrier of stage st and start its two copies */
+        const uint32_t buf = st % kRingStages, first = st * kRingSlots, n = min(kRingSlots, u1 - (uint32_t)u0 - first);
+        const uint32_t bar = bars + buf * 8u, dst = ring + buf * kRingStageBytes;
+        mbar_expect(bar, n * 768u);
+        bulk_load(dst, nib_plane + (uint64_t)first * 256u, n * 256u, bar);
+        bulk_load(dst + kRingSlots * 256u, raw_plane + (uint64_t)first * 512u, n * 512u, bar);
+    };
+    if (lane == 0) for (uint32_t st = 0; st < min(n_stage, kRingStages); st++) issue(st);
+    FixedTables t; t.load(a.lut);
+    uint32_t rb = (uint32_t)(u0 / g.slots), s = (uint32_t)(u0 - (uint64_t)rb * g.slots);      /* row group and slot inside it */
+    float d[4] = {0.f, 0.f, 0.f, 0.f}, ex_lo = 0.f, ex_hi = 0.f;
+    auto flush = [&]() {                                         /* the warp's share of row group rb is complete */
+        ex_lo += __shfl_xor_sync(0xffffffffu, ex_lo, 1); ex_lo += __shfl_xor_sync(0xffffffffu, ex_lo, 2);
+        ex_hi += __shfl_xor_sync(0xffffffffu, ex_hi, 1); ex_hi += __shfl_xor_sync(0xffffffffu, ex_hi, 2);
+        if (q == 0u) {
+            const uint32_t part = w - (uint32_t)(((uint64_t)rb * g.slots) / plan.per);
+            emit_flat(a, plan, rb * 16u + r, part, d[0] + ex_lo); emit_flat(a, plan, rb * 16u + r + 8u, part, d[2] + ex_hi);
+        }
+        d[0] = d[1] = d[2] = d[3] = 0.f; ex_lo = ex_hi = 0.f;
+    };
+    uint32_t phase_bits = 0;
+    for (uint32_t st = 0; st < n_stage; st++) {
+        const uint32_t buf = st % kRingStages, bar = bars + buf * 8u, src = ring + buf * kRingStageBytes;
+        if (!mbar_wait(bar, (phase_bits >> buf) & 1u)) {         /* gave up: let copies already issued land, then leave */
+            for (uint32_t b = 0; b < kRingStages; b++) for (uint32_t i = 0; i < 64u && !mbar_poll(bars + b * 8u, (phase_bits >> b) & 1u); i++) {}
+            return;
+        }
+        phase_bits ^= 1u << buf;
+        const uint32_t n = min(kRingSlots, u1 - (uint32_t)u0 - st * kRingSlots);
+#pragma unroll
+        for (uint32_t j = 0; j < kRingSlots; j++) {
+            if (j < n) {
+                const uint2 nib = lds64(src + j * 256u + lane * 8u);
+                const uint4 raw = lds128(src + kRingSlots * 256u + j * 512u + lane * 16u);
+                if ((s & 15u) == 0u) {                           /* first slot of a block: this warp adds the block's exceptions */
+                    const uint32_t cb = s >> 4, b = rb * g.CB + cb;
+                    uint32_t sum;
+                    const uint32_t count = __ldg(a.hdr + (uint64_t)b * kLanes + lane), before = warp_exclusive_sum(count, lane, sum);
+                    if (sum) {
+                        const uint8_t *ep = a.data + __ldg(a.bases + b) + (uint64_t)before * 3u;
+                        for (uint32_t k = 0; k < count; k++, ep += 3) {
+                            const uint32_t i = ep[0], jj = i & 15u, col = cb * kBlockCols + (i >> 4) * 32u + frag_col(lane, jj);
+                            const float wv = __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
+                            const float xv = bf16_to_float(__ldg(static_cast<const uint16_t *>(a.x) + col));
+                            if ((jj >> 1) & 1u) ex_hi = fmaf(wv, xv, ex_hi); else ex_lo = fmaf(wv, xv, ex_lo);
+                        }
+                    }
+                }
+                fixed_super_chunk<kBf16, kModeLinear, false, 0>(a, g, t, nib, raw, 0u, 0u, 0u, rb * 16u, r, s * 32u + 8u * q, d);
+                if (++s == g.slots) { flush(); s = 0; rb++; }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && st + kRingStages < n_stage) { async_proxy_fence(); issue(st + kRingStages); }
+    }
+    if (s != 0u) flush();
+}
+
+/* y[i] = bf16((sum of the partials of the warps that shared row i's row group, in warp order) * scale[i] + bias[i]) */
+__global__ void finalize_flat_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ bias, const float *__restrict__ scale,
+                                     uint16_t *__restrict__ y, uint32_t M, uint32_t rows, const FlatPlan plan) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M) return;
+    const uint64_t first_unit = (uint64_t)(i / rows) * plan.units_per_group;
+    const uint32_t n = (uint32_t)((first_unit + plan.units_per_group - 1u) / plan.per - first_unit / plan.per) + 1u;
+    float v = 0.f;
+    for (uint32_t p = 0; p < n; p++) v += partial[(uint64_t)i * plan.parts + p];
+    if (scale) v *= scale[i];
+    if (bias) v += bf16_to_float(bias[i]);
+    y[i] = bf16_round(v);
+}
+
+/* Equal contiguous runs for `warps` warps.  The run length grows until the warps that can share one row group fit the
+   caller's scratch (CB floats per row); with a single column block no row group may be cut at all. */
+static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t warps, uint32_t min_per, FlatPlan &p) {
+    const uint64_t total = (uint64_t)g.groups * units_per_group;
+    uint64_t per = (total + warps - 1) / warps;
+    if (per < min_per) per = min_per;
+    if (g.CB == 1u) per = (per + units_per_group - 1) / units_per_group * units_per_group;
+    else if ((units_per_group - 1u) / per + 2u > g.CB) per = (units_per_group - 1u) / (g.CB - 1u) + 1u;
+    p.units_per_group = units_per_group; p.per = (uint32_t)per;
+    p.direct = per % units_per_group == 0 ? 1u : 0u;
+    p.parts = p.direct ? 1u : (uint32_t)((units_per_group - 1u) / per) + 2u;
+}
+
+/* ---- layouts 0 and 1, token path: lane streams staged in shared memory by bulk copies -------------------------------- */
+/* Same flat work split as above with the block (32 lane streams) as the unit.  A warp's run of blocks is one contiguous
+   span of `data`; the stream of block n + 1 is copied into the warp's second stage while block n is decoded, so the
+   bit windows refill from shared memory with 32-bit addresses and no lane ever waits for a 4-byte global load.  Raw
+   rows still come straight from global memory (coalesced 512 B per row and warp, two rows ahead).
+   A block whose stream does not fit a stage (escape-heavy data) is decoded through the global-memory window instead. */
+constexpr uint32_t kPrefixThreads = 1024, kPrefixStageBytes = 2560, kPrefixWarpBytes = 2u * kPrefixStageBytes + 256u + 16u;
+constexpr uint32_t kPrefixSmemBytes = 16416u + (kPrefixThreads / 32u) * kPrefixWarpBytes;
+
+/* bit window over a stream staged in shared memory; table look-ups form their address with one shift and one IMAD */
+template <uint32_t MAX_RANK>
+struct SmemWindow {
+    uint32_t hi, lo, next, mark, src;
+    __device__ __forceinline__ void open(uint32_t addr) { hi = lds32(addr); lo = lds32(addr + 4u); next = lds32(addr + 8u); mark = 1u; src = addr + 12u; }
+    __device__ __forceinline__ void consume(uint32_t c) {
+        const uint32_t before = mark;
+        const uint32_t nhi = __funnelshift_l(lo, hi, c), nlo = __funnelshift_l(0u, lo, c);
+        mark = __funnelshift_l(before, before, c);
+        const bool refill = mark < before;
+        const uint64_t merged = (uint64_t)next * (refill ? mark : 0u) + (((uint64_t)nhi << 32) | nlo);
+        hi = (uint32_t)(merged >> 32); lo = (uint32_t)merged;
+        if (refill) { next = lds32(src); src += 4u; }
+    }
+    __device__ __forceinline__ uint32_t look(uint32_t word, uint32_t table, uint32_t four) const {
+        uint32_t addr; asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(addr) : "r"(word >> 20), "r"(four), "r"(table));
+        return lds32(addr);
+    }
+    __device__ __forceinline__ uint32_t one(uint32_t sym) {
+        const uint32_t h = hi, zeros = min((uint32_t)__clz((int)h), 15u);
+        if (MAX_RANK == kMaxRankFp8 || zeros < MAX_RANK) {
+            uint32_t s8; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(s8) : "r"(sym + zeros));
+            const uint32_t b = (((h >> (30u - zeros)) & 1u) << 7) | s8;
+            consume(zeros + 2u);
+            return b;
+        }
+        consume(16u);
+        const uint32_t b = hi >> 24;
+        consume(8u);
+        return b;
+    }
+    __device__ __forceinline__ uint32_t pair(uint32_t table, uint32_t sym, uint32_t four) {
+        const uint32_t e = look(hi, table, four);
+        if (e < kEscape) { consume(e); return e; }
+        uint32_t b0 = (e >> 8) & 0xFFu;
+        if (e & (1u << 24)) consume(e); else b0 = one(sym);
+        const uint32_t b1 = one(sym);
+        return (b0 << 8) | (b1 << 16);
+    }
+    __device__ __forceinline__ void quad(uint32_t table, uint32_t sym, uint32_t four, uint32_t &e01, uint32_t &e23) {
+        const uint32_t a = look(hi, table, four);
+        const uint32_t b = look(__funnelshift_l(0u, hi, a), table, four);
+        if (((a | b) & kEscape) == 0u) { consume(a + b); e01 = a; e23 = b; }
+        else { e01 = pair(table, sym, four); e23 = pair(table, sym, four); }
+    }
+};
+/* the global-memory window behind the same interface (oversize blocks) */
+template <uint32_t MAX_RANK>
+struct GlobalWindow : BitWindow<MAX_RANK> {
+    const uint8_t *sym_ptr;
+    __device__ __forceinline__ void quad(uint32_t table, uint32_t, uint32_t, uint32_t &e01, uint32_t &e23) { BitWindow<MAX_RANK>::quad(table, sym_ptr, e01, e23); }
+};
+
+/* One layout-0 block: 8 rows x 16 columns per lane.  Even rows enter the mma as the "row r" half of the A fragment, odd
+   rows as the "row r + 8" half, the other half is zero; after two rows the diagonal of D holds the quad's dot products. */
+template <class WIN, int ELEM, bool XF32>
+__device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane,
+                                                      uint32_t table, uint32_t sym, uint32_t four, float *stash) {
+    const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 8u, col0 = cb * kBlockCols + lane * 16u;
+    const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
+    const bool col_ok = col0 < g.K16, diag = q == (r >> 1);
+    XFrag8<XF32> xa, xb;
+    if (col_ok) { xa.load(a.x, col0); xb.load(a.x, col0 + 8u); } else { xa.zero(); xb.zero(); }
+    const uint8_t *rawp = a.low + (uint64_t)row0 * stride + (ELEM == kFp8 ? (col0 >> 1) : col0);
+    uint4 raw0 = raw_row16<ELEM>(rawp, col_ok && row0 < g.M), raw1 = raw_row16<ELEM>(rawp + stride, col_ok && row0 + 1u < g.M);
+#pragma unroll 1
+    for (uint32_t rp = 0; rp < 4u; rp++) {
+        const uint4 rawA = raw0, rawB = raw1;
+        if (rp < 3u) {
+            raw0 = raw_row16<ELEM>(rawp + (uint64_t)(2u * rp + 2u) * stride, col_ok && row0 + 2u * rp + 2u < g.M);
+            raw1 = raw_row16<ELEM>(rawp + (uint64_t)(2u * rp + 3u) * stride, col_ok && row0 + 2u * rp + 3u < g.M);
+        }
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t wa[4] = {rawA.x, rawA.y, rawA.z, rawA.w}, wb[4] = {rawB.x, rawB.y, rawB.z, rawB.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint32_t e01, e23; W.quad(table, sym, four, e01, e23);
+            const XFrag8<XF32> &xf = k < 2 ? xa : xb;
+            const int w = 2 * (k & 1);
+            const uint32_t p0 = weave<0>(wa[k], e01), p1 = weave<2>(wa[k], e23);
+            mma_bf16(d, p0, 0u, p1, 0u, xf.head[w], xf.head[w + 1]);
+            if (XF32) mma_bf16(d, p0, 0u, p1, 0u, xf.tail[w], xf.tail[w + 1]);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint32_t e01, e23; W.quad(table, sym, four, e01, e23);
+            const XFrag8<XF32> &xf = k < 2 ? xa : xb;
+            const int w = 2 * (k & 1);
+            const uint32_t p0 = weave<0>(wb[k], e01), p1 = weave<2>(wb[k], e23);
+            mma_bf16(d, 0u, p0, 0u, p1, xf.head[w], xf.head[w + 1]);
+            if (XF32) mma_bf16(d, 0u, p0, 0u, p1, xf.tail[w], xf.tail[w + 1]);
+        }
+        if (diag) {
+            stash[(2u * rp) * 8u + r] = (r & 1u) ? d[1] : d[0];
+            stash[(2u * rp + 1u) * 8u + r] = (r & 1u) ? d[3] : d[2];
+        }
+    }
+    __syncwarp();
+    float sum = 0.f;
+    if (lane < 8u) {
+        const float4 s0 = *reinterpret_cast<const float4 *>(stash + lane * 8u), s1 = *reinterpret_cast<const float4 *>(stash + lane * 8u + 4u);
+        sum = ((s0.x + s0.y) + (s0.z + s0.w)) + ((s1.x + s1.y) + (s1.z + s1.w));
+    }
+    __syncwarp();
+    return sum;
+}
+
+template <int ELEM, bool XF32>
+__global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(const SegmentArgs a, const FlatPlan plan, const uint32_t four) {
+    constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    uint32_t *tables = reinterpret_cast<uint32_t *>(ring_smem);
+    stage_tables(tables, a.lut, threadIdx.x, kPrefixThreads);
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords;
+    uint8_t *mine = ring_smem + 16416u + warp * kPrefixWarpBytes;
+    const uint32_t stages = smem_addr(mine), bars = stages + 2u * kPrefixStageBytes + 256u;
+    float *stash = reinterpret_cast<float *>(mine + 2u * kPrefixStageBytes);
+    const Geometry g(a.M, a.K, 0);
+    const uint32_t w = blockIdx.x * (kPrefixThreads / 32u) + warp;
+    const uint64_t first = (uint64_t)w * plan.per;
+    if (first >= g.nb) return;
+    const uint32_t b0 = (uint32_t)first, b1 = (uint32_t)min((uint64_t)g.nb, first + plan.per);
+    if (lane == 0) { mbar_init(bars, 1u); mbar_init(bars + 8u, 1u); mbar_init_fence(); }
+    __syncwarp();
+    /* byte span of block b inside data: [start, start + bytes), rounded out to 16; bytes == 0 means "does not fit a stage" */
+    auto span = [&](uint32_t b, uint32_t words_of_b, uint32_t &start, uint32_t &bytes) {
+        const uint32_t base = __ldg(a.bases + b);
+        uint32_t len;
+        if (b + 1u < g.nb) len = __ldg(a.bases + b + 1u) - base;
+        else { uint32_t t; warp_exclusive_sum(words_of_b, lane, t); len = 4u * t; }
+        start = base & ~15u;
+        bytes = (base + len + 16u - start + 15u) & ~15u;          /* + 16: the windows read up to three words past a stream */
+        if (bytes > kPrefixStageBytes) bytes = 0u;
+    };
+    auto issue = [&](uint32_t b, uint32_t words_of_b) {
+        uint32_t start, bytes; span(b, words_of_b, start, bytes);
+        if (bytes && lane == 0) {
+            const uint32_t buf = (b - b0) & 1u;
+            async_proxy_fence();
+            mbar_expect(bars + buf * 8u, bytes);
+            bulk_load(stages + buf * kPrefixStageBytes, a.data + start, bytes, bars + buf * 8u);
+        }
+    };
+    uint32_t words = __ldg(a.hdr + (uint64_t)b0 * kLanes + lane);
+    uint32_t words_next = b0 + 1u < b1 ? __ldg(a.hdr + (uint64_t)(b0 + 1u) * kLanes + lane) : 0u;
+    issue(b0, words);
+    if (b0 + 1u < b1) issue(b0 + 1u, words_next);
+    uint32_t rb = b0 / g.CB, cb = b0 - rb * g.CB, phase_bits = 0;
+    float row_sum = 0.f;
+    for (uint32_t b = b0; b < b1; b++) {
+        const uint32_t words_after = b + 2u < b1 ? __ldg(a.hdr + (uint64_t)(b + 2u) * kLanes + lane) : 0u;
+        uint32_t start, bytes, total; span(b, words, start, bytes);
+        const uint32_t before = warp_exclusive_sum(words, lane, total), buf = (b - b0) & 1u, base = __ldg(a.bases + b);
+        if (bytes) {
+            if (!mbar_wait(bars + buf * 8u, (phase_bits >> buf) & 1u)) {
+                for (uint32_t i = 0; i < 64u && !mbar_poll(bars + (buf ^ 1u) * 8u, (phase_bits >> (buf ^ 1u)) & 1u); i++) {}
+                return;
+            }
+            phase_bits ^= 1u << buf;
+            SmemWindow<MR> W; W.open(stages + buf * kPrefixStageBytes + (base - start) + 4u * before);
+            row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
+        } else {
+            GlobalWindow<MR> W; W.sym_ptr = reinterpret_cast<const uint8_t *>(tables + kTableWords);
+            W.open(reinterpret_cast<const uint32_t *>(a.data + base) + before);
+            row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
+        }
+        if (b + 2u < b1) issue(b + 2u, words_after);              /* the stage just decoded is free again (all lanes passed the block's last __syncwarp) */
+        words = words_next; words_next = words_after;
+        if (++cb == g.CB || b + 1u == b1) {                       /* the warp's share of this row group is complete */
+            if (lane < 8u) emit_flat(a, plan, rb * 8u + lane, w - (uint32_t)(((uint64_t)rb * g.CB) / plan.per), row_sum);
+            row_sum = 0.f;
+            if (cb == g.CB) { cb = 0; rb++; }
+        }
+    }
+}
+
 /* ---- the persistent segment kernel -------------------------------------------------------------------------------- */
-template <int LAYOUT, int ELEM, int MODE>
+template <int LAYOUT, int ELEM, int MODE, bool XF32>
 __global__ void __launch_bounds__(kSegmentThreads, 1) segment_kernel(const SegmentArgs a) {
     extern __shared__ __align__(16) uint32_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -297,9 +606,9 @@ __global__ void __launch_bounds__(kSegmentThreads, 1) segment_kernel(const Segme
     for (uint32_t item = blockIdx.x * (kSegmentThreads / 32u) + warp; item < items; item += stride) {
         const uint32_t rb = item / a.splits, split = item - rb * a.splits;
         const uint32_t cb0 = (uint32_t)((uint64_t)split * g.CB / a.splits), cb1 = (uint32_t)((uint64_t)(split + 1u) * g.CB / a.splits);
-        if (LAYOUT == 0) segment_layout0<ELEM, MODE>(a, g, rb, cb0, cb1, split, lane, table, sym, stash);
-        else if (LAYOUT == 1) segment_layout1<ELEM, MODE>(a, g, rb, cb0, cb1, split, lane, table, sym);
-        else segment_layout2<ELEM, MODE>(a, g, rb, cb0, cb1, split, lane);
+        if (LAYOUT == 0) segment_layout0<ELEM, MODE, XF32>(a, g, rb, cb0, cb1, split, lane, table, sym, stash);
+        else if (LAYOUT == 1) segment_layout1<ELEM, MODE, XF32>(a, g, rb, cb0, cb1, split, lane, table, sym);
+        else segment_layout2<ELEM, MODE, XF32>(a, g, rb, cb0, cb1, split, lane);
     }
 }
 
@@ -317,18 +626,28 @@ __global__ void finalize_kernel(const float *__restrict__ partial, const uint16_
 
 template <int LAYOUT, int ELEM>
 static cudaError_t launch_modes(int mode, int grid, size_t smem, cudaStream_t st, const SegmentArgs &a) {
-    switch (mode) {
-        case kModeLinear: segment_kernel<LAYOUT, ELEM, kModeLinear><<<grid, kSegmentThreads, smem, st>>>(a); break;
-        case kModeDequant: segment_kernel<LAYOUT, ELEM, kModeDequant><<<grid, kSegmentThreads, smem, st>>>(a); break;
-        default: segment_kernel<LAYOUT, ELEM, kModeAtomic><<<grid, kSegmentThreads, smem, st>>>(a); break;
-    }
+    /* x is fp32 on the fp32 test path (all layouts) and on layout 0's token path unless the caller passes bf16 */
+    if (mode == kModeDequant) segment_kernel<LAYOUT, ELEM, kModeDequant, false><<<grid, kSegmentThreads, smem, st>>>(a);
+    else if (mode == kModeAtomic) segment_kernel<LAYOUT, ELEM, kModeAtomic, true><<<grid, kSegmentThreads, smem, st>>>(a);
+    else if (LAYOUT == 0 && !a.x_bf16) segment_kernel<LAYOUT, ELEM, kModeLinear, true><<<grid, kSegmentThreads, smem, st>>>(a);
+    else segment_kernel<LAYOUT, ELEM, kModeLinear, false><<<grid, kSegmentThreads, smem, st>>>(a);
     return cudaGetLastError();
 }
 
 /* number of K splits: one segment per row group when there are enough row groups to give every resident warp work,
    otherwise the fewest splits (at most one per column block) that reach two segments per warp */
-uint32_t choose_splits(const Geometry &g, int mode, int sms) {
+static bool g_disable_ring = false;
+void set_ring_kernels(bool on) { g_disable_ring = !on; }
+int read_kernel_status(bool clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_kernel_status, sizeof(int)) != cudaSuccess) return -1;
+    if (clear && v) { const int z = 0; cudaMemcpyToSymbol(g_kernel_status, &z, sizeof(int)); }
+    return v;
+}
+
+uint32_t choose_splits(const Geometry &g, int mode, int code, int sms) {
     if (mode == kModeDequant) return g.CB;                       /* no sums: finest grain */
+    (void)code;
     const uint64_t warps = (uint64_t)sms * (kSegmentThreads / 32u);
     if (g.groups >= 2u * warps || g.CB == 1u) return 1u;
     const uint64_t want = (2u * warps + g.groups - 1u) / g.groups;
@@ -338,13 +657,40 @@ uint32_t choose_splits(const Geometry &g, int mode, int sms) {
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(a.M, a.K, layout);
-    if (a.splits == 0) a.splits = choose_splits(g, mode, sms);
+    a.splits_forced = a.splits;
+    if (a.splits == 0) a.splits = choose_splits(g, mode, code, sms);
     const uint32_t warps_per_cta = kSegmentThreads / 32u;
     const uint64_t items = (uint64_t)g.groups * a.splits;
     int grid = (int)((items + warps_per_cta - 1) / warps_per_cta);
     if (grid > sms) grid = sms;
     const size_t smem = layout == 2 ? 0 : kTableSmemBytes + (size_t)warps_per_cta * 64u * sizeof(float);
     cudaError_t err;
+    FlatPlan plan;
+    if (layout == 0 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
+        make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), 1u, plan);
+        const uint64_t used = ((uint64_t)g.nb + plan.per - 1) / plan.per;
+        const int rgrid = (int)((used + kPrefixThreads / 32u - 1) / (kPrefixThreads / 32u));
+        if (elem == kFp8) { if (a.x_bf16) prefix_ring_kernel_layout0<kFp8, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kFp8, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
+        else { if (a.x_bf16) prefix_ring_kernel_layout0<kBf16, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kBf16, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
+        err = cudaGetLastError();
+        if (err == cudaSuccess && !plan.direct) {
+            finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
+            err = cudaGetLastError();
+        }
+        return err;
+    }
+    if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
+        make_flat_plan(g, g.slots, (uint64_t)sms * (kRingThreads / 32u), 2u * kRingSlots, plan);
+        const uint64_t total = (uint64_t)g.groups * g.slots, used = (total + plan.per - 1) / plan.per;
+        const int rgrid = (int)((used + kRingThreads / 32u - 1) / (kRingThreads / 32u));
+        ring_kernel_layout2<<<rgrid, kRingThreads, (kRingThreads / 32u) * kRingWarpBytes, st>>>(a, plan);
+        err = cudaGetLastError();
+        if (err == cudaSuccess && !plan.direct) {
+            finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
+            err = cudaGetLastError();
+        }
+        return err;
+    }
     if (layout == 0) err = elem == kFp8 ? launch_modes<0, kFp8>(mode, grid, smem, st, a) : launch_modes<0, kBf16>(mode, grid, smem, st, a);
     else if (layout == 1) err = elem == kFp8 ? launch_modes<1, kFp8>(mode, grid, smem, st, a) : launch_modes<1, kBf16>(mode, grid, smem, st, a);
     else err = elem == kFp8 ? launch_modes<2, kFp8>(mode, grid, smem, st, a) : launch_modes<2, kBf16>(mode, grid, smem, st, a);
@@ -356,16 +702,21 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     return err;
 }
 
-template <int LAYOUT, int ELEM, int MODE>
+template <int LAYOUT, int ELEM>
 static void opt_in_smem() {
-    cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)(kTableSmemBytes + (kSegmentThreads / 32u) * 64u * sizeof(float)));
+    const int bytes = (int)(kTableSmemBytes + (kSegmentThreads / 32u) * 64u * sizeof(float));
+    cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeLinear, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeLinear, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeDequant, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeAtomic, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 void configure_segment_kernels() {
-    opt_in_smem<0, kBf16, 0>(); opt_in_smem<0, kBf16, 1>(); opt_in_smem<0, kBf16, 2>();
-    opt_in_smem<0, kFp8, 0>(); opt_in_smem<0, kFp8, 1>(); opt_in_smem<0, kFp8, 2>();
-    opt_in_smem<1, kBf16, 0>(); opt_in_smem<1, kBf16, 1>(); opt_in_smem<1, kBf16, 2>();
-    opt_in_smem<1, kFp8, 0>(); opt_in_smem<1, kFp8, 1>(); opt_in_smem<1, kFp8, 2>();
+    cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((kRingThreads / 32u) * kRingWarpBytes));
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
+    opt_in_smem<0, kBf16>(); opt_in_smem<0, kFp8>(); opt_in_smem<1, kBf16>(); opt_in_smem<1, kFp8>();
 }
 
 }  // namespace nwc

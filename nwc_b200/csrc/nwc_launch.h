@@ -23,9 +23,13 @@ struct SegmentArgs {
     uint16_t *y;                /* bf16 result                                                               */
     uint32_t M, K;
     uint32_t splits;            /* K splits per row group; 0 = let the launcher choose                       */
+    int x_bf16;                 /* token path of layout 0: x is bf16[K16] instead of fp32[K16]                */
+    uint32_t splits_forced;     /* the caller's own splits request (0 = none): forced splits take the plain kernels */
 };
 
-uint32_t choose_splits(const Geometry &g, int mode, int sms);
+uint32_t choose_splits(const Geometry &g, int mode, int code, int sms);
+void set_ring_kernels(bool on);               /* tests: switch the bulk-copy ring kernels off to compare with the plain ones */
+int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gave up; synchronises */
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a);
 void configure_segment_kernels();
 

@@ -1,0 +1,220 @@
+"""Batch-1 greedy decode loop over compressed weights, replayed as one CUDA graph per token.
+
+Replaces the reference's graph-captured Hugging Face forward (reference: scripts/graph_decode.py:37-70,
+nwc/demo.py:71-89) with a fixed chain of this library's kernels: compressed embedding gather, then per layer
+add+RMSNorm -> fused qkv matvec -> q/k-norm + rotary + cache append + attention -> o matvec -> add+RMSNorm ->
+fused gate/up matvec -> SwiGLU -> down matvec, then final norm -> lm_head matvec -> argmax.  Token, position and step
+counter live in device memory, so the captured graph is replayed unchanged for every token.
+
+Architectures: Qwen3 (per-head q/k RMSNorm, tied or untied embeddings) and Llama-3 style (no q/k norm) decoders.
+"""
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+from .weight import NWCWeight
+
+
+@dataclass
+class DecoderConfig:
+    name: str
+    layers: int
+    hidden: int
+    intermediate: int
+    n_q: int
+    n_kv: int
+    head_dim: int
+    vocab: int
+    tied: bool
+    qk_norm: bool
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+
+    @property
+    def qkv_rows(self): return (self.n_q + 2 * self.n_kv) * self.head_dim
+
+
+PRESETS = {
+    "qwen3-0.6b": DecoderConfig("qwen3-0.6b", 28, 1024, 3072, 16, 8, 128, 151936, True, True),
+    "qwen3-4b": DecoderConfig("qwen3-4b", 36, 2560, 9728, 32, 8, 128, 151936, False, True),
+    "llama3-70b": DecoderConfig("llama3-70b", 80, 8192, 28672, 64, 8, 128, 128256, False, False, rope_theta=5e5, eps=1e-5),
+    "tiny": DecoderConfig("tiny", 2, 256, 1000, 4, 2, 64, 4096, True, True),
+}
+
+
+def synthetic_matrix(rows, cols, seed, device="cuda"):
+    """W[i, j] = r_i * 0.02 * z_ij with r_i log-normal(0, 0.3), z standard normal, seeded per tensor; bf16."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    r = torch.exp(0.3 * torch.randn(rows, 1, generator=g, device=device))
+    return (r * 0.02 * torch.randn(rows, cols, generator=g, device=device)).to(torch.bfloat16)
+
+
+class DecoderWeights:
+    """Compressed matrices and norm vectors of a decoder.  `source(name, rows, cols)` returns the bf16 matrix to
+    compress; `vector(name, n)` a bf16 norm weight."""
+
+    def __init__(self, cfg: DecoderConfig, source, vector, layout=0, elem="bf16", device="cuda"):
+        self.cfg = cfg
+        mk = lambda name, r, c, e=elem: NWCWeight(source(name, r, c), device, elem=e, layout=layout)
+        self.embed = mk("embed", cfg.vocab, cfg.hidden, "bf16" if not cfg.tied else elem)
+        self.lm_head = self.embed if cfg.tied else mk("lm_head", cfg.vocab, cfg.hidden)
+        self.layers = []
+        for i in range(cfg.layers):
+            self.layers.append({
+                "in_norm": vector(f"l{i}.in_norm", cfg.hidden), "post_norm": vector(f"l{i}.post_norm", cfg.hidden),
+                "q_norm": vector(f"l{i}.q_norm", cfg.head_dim) if cfg.qk_norm else None,
+                "k_norm": vector(f"l{i}.k_norm", cfg.head_dim) if cfg.qk_norm else None,
+                "qkv": mk(f"l{i}.qkv", cfg.qkv_rows, cfg.hidden), "o": mk(f"l{i}.o", cfg.hidden, cfg.n_q * cfg.head_dim),
+                "gate_up": mk(f"l{i}.gate_up", 2 * cfg.intermediate, cfg.hidden), "down": mk(f"l{i}.down", cfg.hidden, cfg.intermediate)})
+        self.final_norm = vector("final_norm", cfg.hidden)
+
+    @classmethod
+    def synthetic(cls, cfg, layout=0, elem="bf16", device="cuda", seed=0):
+        counter = [seed * 100003]
+        def source(name, r, c):
+            counter[0] += 1
+            return synthetic_matrix(r, c, counter[0], device)
+        return cls(cfg, source, lambda name, n: torch.ones(n, dtype=torch.bfloat16, device=device), layout, elem, device)
+
+    def matrices(self):
+        seen, out = set(), []
+        for w in [self.embed, self.lm_head] + [l[k] for l in self.layers for k in ("qkv", "o", "gate_up", "down")]:
+            if id(w) not in seen: seen.add(id(w)); out.append(w)
+        return out
+
+    def bytes_per_token(self):
+        """Compressed bytes one decode step streams: every matvec matrix once (the embedding lookup reads one row)."""
+        ws = [self.lm_head] + [l[k] for l in self.layers for k in ("qkv", "o", "gate_up", "down")]
+        return sum(w.bytes for w in ws)
+
+
+def rope_tables(cfg, max_len, device):
+    """cos / sin as the Transformers rotary module computes them: fp32 angles, rounded to bf16; [max_len, head_dim]."""
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.int64).float() / cfg.head_dim))
+    freqs = torch.arange(max_len, dtype=torch.float32)[:, None] * inv[None, :]
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(torch.bfloat16).to(device).contiguous(), emb.sin().to(torch.bfloat16).to(device).contiguous()
+
+
+class DecodeEngine:
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda"):
+        L.require_cuda()
+        self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
+        c = self.cfg
+        bf = lambda n: torch.zeros(n, dtype=torch.bfloat16, device=device)
+        pad32 = lambda n: (n + 31) // 32 * 32
+        self.h, self.xn = bf(pad32(c.hidden)), bf(pad32(c.hidden))
+        self.qkv, self.attn, self.proj = bf(c.qkv_rows), bf(pad32(c.n_q * c.head_dim)), bf(pad32(c.hidden))
+        self.gu, self.act = bf(2 * c.intermediate), bf(pad32(c.intermediate))
+        self.logits = bf(c.vocab)
+        self.k_cache = torch.zeros(c.layers, c.n_kv, max_len, c.head_dim, dtype=torch.bfloat16, device=device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.cos, self.sin = rope_tables(c, max_len, device)
+        self.cur = torch.zeros(1, dtype=torch.int64, device=device)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step_no = torch.zeros(1, dtype=torch.int32, device=device)
+        self.log = torch.zeros(max_len + 8, dtype=torch.int64, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.pinned_in = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self.pinned_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self.graph = None
+        self.launches_per_step = 0
+        self._count = 0
+        if weights.embed.scale is not None: raise NotImplementedError("fp8 embedding tables are not supported by the decode loop")
+
+    # ---- one token, eager: every call below is one or two kernels of this library on the current stream ----
+    def _linear(self, w: NWCWeight, x, y):
+        err = L.lib.nwc_linear_x16(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(x), None,
+                                   L.ptr(w.scale), L.ptr(w.scratch), L.ptr(y), w.n, w.block, w.in_features, w.code)
+        if err: raise RuntimeError(f"nwc_linear_x16 error {err}")
+        self._count += 2 if self._needs_finalize(w) else 1
+
+    @staticmethod
+    def _needs_finalize(w):
+        rows = 16 if w.layout else 8
+        groups, cb = (w.out_features + rows - 1) // rows, (w.in_features + 511) // 512
+        return cb > 1 and groups < 2 * L.SM_COUNT * 16
+
+    def _check(self, err, what):
+        if err: raise RuntimeError(f"{what} error {err}")
+        self._count += 1
+
+    def forward_token(self):
+        """Kernels of one decode step: reads self.cur / self.pos, leaves the greedy token in self.cur, advances pos."""
+        c, w, st = self.cfg, self.w, L.stream
+        self._count = 0
+        e = w.embed
+        self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(self.h),
+                                     e.n, e.block, e.in_features, e.code), "nwc_gather")
+        delta = None
+        for i, l in enumerate(w.layers):
+            self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(self.h), L.ptr(delta), L.ptr(l["in_norm"]), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
+            self._linear(l["qkv"], self.xn, self.qkv)
+            self._check(L.lib.nwc_attention_decode(st(), L.ptr(self.qkv), L.ptr(l["q_norm"]), L.ptr(l["k_norm"]), L.ptr(self.cos), L.ptr(self.sin),
+                                                   L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
+                                                   c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
+            self._linear(l["o"], self.attn, self.proj)
+            self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(self.h), L.ptr(self.proj), L.ptr(l["post_norm"]), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
+            self._linear(l["gate_up"], self.xn, self.gu)
+            self._check(L.lib.nwc_swiglu(st(), L.ptr(self.gu), c.intermediate, L.ptr(self.act), None), "nwc_swiglu")
+            self._linear(l["down"], self.act, self.proj)
+            delta = self.proj
+        self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(self.h), L.ptr(delta), L.ptr(w.final_norm), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
+        self._linear(w.lm_head, self.xn, self.logits)
+        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits), c.vocab, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
+        self.launches_per_step = self._count
+
+    # ---- graph ----
+    def capture(self, warmup=3):
+        """Capture one decode step as a CUDA graph (state is saved and restored around the warm-up runs)."""
+        saved = (self.cur.clone(), self.pos.clone(), self.step_no.clone())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.pos.zero_(); self.forward_token()
+        torch.cuda.current_stream().wait_stream(side)
+        self.pos.zero_()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.forward_token()
+        for t, s in zip((self.cur, self.pos, self.step_no), saved): t.copy_(s)
+        self.log.zero_()
+        torch.cuda.synchronize()
+
+    def reset(self):
+        self.pos.zero_(); self.step_no.zero_(); self.log.zero_(); self.status.zero_()
+
+    def _run(self):
+        if self.graph is not None: self.graph.replay()
+        else: self.forward_token()
+
+    def prefill(self, prompt_ids):
+        """Feed the prompt token by token through the decode step (teacher forcing); returns the first generated token
+        id as a device tensor.  Positions restart at 0."""
+        self.reset()
+        prompt = torch.as_tensor(prompt_ids, dtype=torch.int64, device=self.device).reshape(-1)
+        for i in range(prompt.numel()):
+            self.cur.copy_(prompt[i:i + 1])
+            self._run()
+        self.step_no.zero_()
+        return self.cur
+
+    def generate(self, n_tokens):
+        """n_tokens greedy steps from the current state; returns the generated ids (the token in self.cur is consumed
+        first, its successors are returned)."""
+        start = int(self.step_no.item())
+        for _ in range(n_tokens): self._run()
+        torch.cuda.synchronize()
+        if int(self.status.item()): raise RuntimeError("decode position left the KV cache")
+        return self.log[start:start + n_tokens].clone()
+
+    def step(self, token_id: int) -> int:
+        """Serving-style call with host values: token in from pinned host memory, next token back to the host."""
+        self.pinned_in[0] = token_id
+        self.cur.copy_(self.pinned_in, non_blocking=True)
+        self._run()
+        self.pinned_out.copy_(self.cur, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(self.pinned_out[0])

@@ -1,0 +1,89 @@
+"""The CUDA-graph decode loop against Hugging Face Transformers on the CPU: a small random-init Qwen3 model is run
+teacher-forced through both; at every step the engine's greedy token must equal HF's unless HF's two best logits are
+closer than bf16 resolution allows to separate (different but equally valid summation orders), and graph replay must
+give exactly the tokens of eager execution."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def build_pair(layout, layers=2):
+    from transformers import Qwen3Config, AutoModelForCausalLM
+    from nwc_b200.decode import DecoderConfig, DecoderWeights, DecodeEngine
+    torch.manual_seed(0)
+    hf_cfg = Qwen3Config(vocab_size=2048, hidden_size=256, intermediate_size=1000, num_hidden_layers=layers, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=64, max_position_embeddings=512, tie_word_embeddings=True, rope_theta=1e6, rms_norm_eps=1e-6)
+    hf_cfg._attn_implementation = "eager"
+    model = AutoModelForCausalLM.from_config(hf_cfg, dtype=torch.bfloat16).eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "norm" in n: p.copy_(1.0 + 0.1 * torch.randn_like(p.float()))
+    sd = model.state_dict()
+    cfg = DecoderConfig("tiny-qwen3", layers, 256, 1000, 4, 2, 64, 2048, True, True, rope_theta=1e6, eps=1e-6)
+
+    def source(name, r, c):
+        if name in ("embed", "lm_head"): return sd["model.embed_tokens.weight"].cuda()
+        i, kind = name[1:].split(".")
+        pre = f"model.layers.{i}."
+        if kind == "qkv": return torch.cat([sd[pre + f"self_attn.{k}_proj.weight"] for k in "qkv"], 0).cuda()
+        if kind == "o": return sd[pre + "self_attn.o_proj.weight"].cuda()
+        if kind == "gate_up": return torch.cat([sd[pre + "mlp.gate_proj.weight"], sd[pre + "mlp.up_proj.weight"]], 0).cuda()
+        return sd[pre + "mlp.down_proj.weight"].cuda()
+
+    def vector(name, n):
+        if name == "final_norm": return sd["model.norm.weight"].cuda()
+        i, kind = name[1:].split(".")
+        key = {"in_norm": "input_layernorm", "post_norm": "post_attention_layernorm", "q_norm": "self_attn.q_norm", "k_norm": "self_attn.k_norm"}[kind]
+        return sd[f"model.layers.{i}.{key}.weight"].cuda()
+
+    eng = DecodeEngine(DecoderWeights(cfg, source, vector, layout=layout), max_len=128)
+    return model, eng
+
+
+@pytest.mark.parametrize("layout", [0, 1, 2])
+def test_teacher_forced_tokens_match_transformers(layout):
+    model, eng = build_pair(layout)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 2048, (1, 12), generator=g)
+    with torch.no_grad(): ref = model.generate(prompt, max_new_tokens=40, do_sample=False)[0]
+    seq = ref.tolist()
+    with torch.no_grad(): logits = model(ref[None, :]).logits[0].float()          # [T, V] teacher-forced HF logits
+    eng.reset()
+    agree = ties = 0
+    for t in range(len(seq) - 1):
+        eng.cur.fill_(seq[t]); eng.forward_token()
+        mine = eng.logits.float().cpu()
+        tok = int(eng.cur.item())
+        top2 = logits[t].topk(2)
+        assert (mine - logits[t]).abs().max().item() <= 0.06 * logits[t].abs().max().item() + 0.05, t
+        if tok == int(top2.indices[0]): agree += 1
+        else:
+            gap = (top2.values[0] - top2.values[1]).item()
+            assert gap <= 2.0 ** -6 * abs(top2.values[0].item()) + 1e-3, (t, tok, top2)
+            ties += 1
+    assert agree >= (len(seq) - 1) - 4, (agree, ties)
+
+
+def test_graph_replay_equals_eager_and_step_api():
+    model, eng = build_pair(0)
+    prompt = list(range(7, 19))
+    eng.prefill(prompt)
+    eager = eng.generate(24).tolist()
+    eng.capture()
+    eng.prefill(prompt)
+    replay = eng.generate(24).tolist()
+    assert eager == replay
+    first = eng.prefill(prompt).item()
+    tok, served = first, []
+    for _ in range(24): tok = eng.step(tok); served.append(tok)
+    assert served == eager
+    assert eng.launches_per_step > 0 and int(eng.status.item()) == 0
+
+
+def test_position_outside_cache_sets_status_not_fault():
+    model, eng = build_pair(0, layers=1)
+    eng.reset(); eng.pos.fill_(eng.max_len)            # one past the cache: the attention kernel must refuse, not write
+    eng.forward_token(); torch.cuda.synchronize()
+    assert int(eng.status.item()) == 1

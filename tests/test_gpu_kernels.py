@@ -44,6 +44,14 @@ def check_matvec(nw, p, values, x_bits, bias=True, splits=(0,)):
         assert rel_l2(got, want_f) <= 2e-3, (s, rel_l2(got, want_f))
         assert np.abs(got - ref64).max() <= tol, (s, np.abs(got - ref64).max(), tol)
         assert (pad == -7.0).all()
+    from nwc_b200 import _lib as L
+    assert L.lib.nwc_kernel_status(1) == 0                             # no bounded wait gave up
+    L.lib.nwc_set_ring_kernels(0)                                     # the plain-load kernels must agree with the ring kernels
+    try:
+        plain = O.bf16_to_f32(bits(nw.linear_bf16(xb, bt)))
+        assert rel_l2(plain, want_f) <= 2e-3 and np.abs(plain - ref64).max() <= tol
+    finally:
+        L.lib.nwc_set_ring_kernels(1)
     y32 = nw.matvec(xb.float()).cpu().numpy()
     r32 = O.bf16_to_f32(values).astype(np.float64) @ xf.astype(np.float64)
     if p.scale is not None: r32 = r32 * p.scale

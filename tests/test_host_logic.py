@@ -20,8 +20,7 @@ P = lambda a: ctypes.c_void_p(a.ctypes.data)
 @pytest.fixture(scope="module")
 def lib():
     if not os.path.exists(LIB):
-        from nwc_b200.build import build
-        build()
+        subprocess.run(["python", os.path.join(ROOT, "nwc_b200", "build.py")], check=True)
     return ctypes.CDLL(LIB)
 
 
