@@ -292,10 +292,15 @@ constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
 constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes + kRingStages * 8u;
 
 struct FlatPlan {
-    uint32_t units_per_group;   /* slots (layout 2) per row group                                   */
-    uint32_t per;               /* units per warp                                                   */
-    uint32_t parts;             /* row stride of the partial sums = most warps that share a row group */
-    uint32_t direct;            /* 1: no row group is cut, warps write y themselves                  */
+    uint32_t units_per_group;   /* slots (layout 2) or blocks (layouts 0, 1) per row group                              */
+    uint32_t grain;             /* run boundaries are multiples of this many units (a whole row group when CB == 1)      */
+    uint32_t chunks;            /* total units / grain                                                                 */
+    uint32_t warps;             /* warps that take part; warp w owns chunks [w * chunks / warps, (w + 1) * chunks / warps) */
+    uint32_t parts;             /* row stride of the partial sums = most warps that can share a row group               */
+    uint32_t direct;            /* 1: no row group is cut, warps write y themselves                                      */
+    __host__ __device__ __forceinline__ uint64_t start(uint32_t w) const { return ((uint64_t)w * chunks / warps) * grain; }
+    /* the warp whose run holds unit u */
+    __host__ __device__ __forceinline__ uint32_t owner(uint64_t u) const { return (uint32_t)(((u / grain + 1u) * warps - 1u) / chunks); }
 };
 
 __device__ __forceinline__ void emit_flat(const SegmentArgs &a, const FlatPlan &p, uint32_t row, uint32_t part, float v) {
@@ -311,10 +316,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, r = lane >> 2, q = lane & 3u;
     const uint32_t ring = smem_addr(ring_smem) + warp * kRingWarpBytes, bars = ring + kRingStages * kRingStageBytes;
     const Geometry g(a.M, a.K, 2);
-    const uint32_t total = g.groups * g.slots, w = blockIdx.x * (kRingThreads / 32u) + warp;
-    const uint64_t u0 = (uint64_t)w * plan.per;
-    if (u0 >= total) return;
-    const uint32_t u1 = (uint32_t)min((uint64_t)total, u0 + plan.per), n_stage = (u1 - (uint32_t)u0 + kRingSlots - 1u) / kRingSlots;
+    const uint32_t w = warp * gridDim.x + blockIdx.x;           /* interleaved: a short plan still spreads over all SMs */
+    if (w >= plan.warps) return;
+    const uint64_t u0 = plan.start(w);
+    const uint32_t u1 = (uint32_t)plan.start(w + 1u), n_stage = (u1 - (uint32_t)u0 + kRingSlots - 1u) / kRingSlots;
     if (lane == 0) { for (uint32_t b = 0; b < kRingStages; b++) mbar_init(bars + b * 8u, 1u); mbar_init_fence(); }
     __syncwarp();
     const uint8_t *nib_plane = a.low + u0 * 256u, *raw_plane = a.low + g.nibble_plane_bytes() + u0 * 512u;
@@ -333,7 +338,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
         ex_lo += __shfl_xor_sync(0xffffffffu, ex_lo, 1); ex_lo += __shfl_xor_sync(0xffffffffu, ex_lo, 2);
         ex_hi += __shfl_xor_sync(0xffffffffu, ex_hi, 1); ex_hi += __shfl_xor_sync(0xffffffffu, ex_hi, 2);
         if (q == 0u) {
-            const uint32_t part = w - (uint32_t)(((uint64_t)rb * g.slots) / plan.per);
+            const uint32_t part = w - plan.owner((uint64_t)rb * g.slots);
             emit_flat(a, plan, rb * 16u + r, part, d[0] + ex_lo); emit_flat(a, plan, rb * 16u + r + 8u, part, d[2] + ex_hi);
         }
         d[0] = d[1] = d[2] = d[3] = 0.f; ex_lo = ex_hi = 0.f;
@@ -382,7 +387,7 @@ __global__ void finalize_flat_kernel(const float *__restrict__ partial, const ui
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= M) return;
     const uint64_t first_unit = (uint64_t)(i / rows) * plan.units_per_group;
-    const uint32_t n = (uint32_t)((first_unit + plan.units_per_group - 1u) / plan.per - first_unit / plan.per) + 1u;
+    const uint32_t n = plan.owner(first_unit + plan.units_per_group - 1u) - plan.owner(first_unit) + 1u;
     float v = 0.f;
     for (uint32_t p = 0; p < n; p++) v += partial[(uint64_t)i * plan.parts + p];
     if (scale) v *= scale[i];
@@ -390,17 +395,23 @@ __global__ void finalize_flat_kernel(const float *__restrict__ partial, const ui
     y[i] = bf16_round(v);
 }
 
-/* Equal contiguous runs for `warps` warps.  The run length grows until the warps that can share one row group fit the
-   caller's scratch (CB floats per row); with a single column block no row group may be cut at all. */
-static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t warps, uint32_t min_per, FlatPlan &p) {
+/* Equal contiguous runs (they differ by at most one grain) for up to `warps` warps.  Fewer warps take part when the
+   warps that could share one row group would not fit the caller's scratch (CB floats per row); with a single column
+   block no row group may be cut at all. */
+static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t warps, FlatPlan &p) {
     const uint64_t total = (uint64_t)g.groups * units_per_group;
-    uint64_t per = (total + warps - 1) / warps;
-    if (per < min_per) per = min_per;
-    if (g.CB == 1u) per = (per + units_per_group - 1) / units_per_group * units_per_group;
-    else if ((units_per_group - 1u) / per + 2u > g.CB) per = (units_per_group - 1u) / (g.CB - 1u) + 1u;
-    p.units_per_group = units_per_group; p.per = (uint32_t)per;
-    p.direct = per % units_per_group == 0 ? 1u : 0u;
-    p.parts = p.direct ? 1u : (uint32_t)((units_per_group - 1u) / per) + 2u;
+    p.units_per_group = units_per_group;
+    p.grain = g.CB == 1u ? units_per_group : 1u;
+    p.chunks = (uint32_t)(total / p.grain);
+    uint64_t use = warps < p.chunks ? warps : p.chunks;
+    if (p.grain == 1u && g.CB > 1u) {
+        const uint64_t need = (units_per_group - 1u) / (g.CB - 1u) + 1u;       /* shortest run that keeps parts <= CB */
+        if (total / use < need) use = total / need ? total / need : 1u;
+    }
+    p.warps = (uint32_t)use;
+    p.direct = p.grain % units_per_group == 0u ? 1u : 0u;
+    p.parts = p.direct ? 1u : (uint32_t)((units_per_group - 1u) / (total / use)) + 2u;
+    if (p.parts > g.CB) p.parts = g.CB;                                        /* bound above guarantees the true count fits */
 }
 
 /* ---- layouts 0 and 1, token path: lane streams staged in shared memory by bulk copies -------------------------------- */
@@ -416,19 +427,31 @@ constexpr uint32_t kPrefixSmemBytes = 16416u + (kPrefixThreads / 32u) * kPrefixW
 template <uint32_t MAX_RANK>
 struct SmemWindow {
     uint32_t hi, lo, next, mark, src;
+    /* the three opening loads are volatile so they stay behind the wait on the stage's barrier; every later load
+       depends on them */
     __device__ __forceinline__ void open(uint32_t addr) { hi = lds32(addr); lo = lds32(addr + 4u); next = lds32(addr + 8u); mark = 1u; src = addr + 12u; }
+    /* Drop c & 31 bits.  One fixed instruction sequence: three funnel shifts, the wrap test of the rotating fill mark,
+       two 32-bit multiply-adds that drop `next` behind the valid bits, and a predicated reload. */
     __device__ __forceinline__ void consume(uint32_t c) {
-        const uint32_t before = mark;
-        const uint32_t nhi = __funnelshift_l(lo, hi, c), nlo = __funnelshift_l(0u, lo, c);
-        mark = __funnelshift_l(before, before, c);
-        const bool refill = mark < before;
-        const uint64_t merged = (uint64_t)next * (refill ? mark : 0u) + (((uint64_t)nhi << 32) | nlo);
-        hi = (uint32_t)(merged >> 32); lo = (uint32_t)merged;
-        if (refill) { next = lds32(src); src += 4u; }
+        asm("{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b32 nh, nl, nm, mh;\n\t"
+            "shf.l.wrap.b32 nh, %1, %0, %5;\n\t"
+            "shf.l.wrap.b32 nl, 0, %1, %5;\n\t"
+            "shf.l.wrap.b32 nm, %3, %3, %5;\n\t"
+            "setp.lt.u32 p, nm, %3;\n\t"
+            "selp.u32 mh, nm, 0, p;\n\t"
+            "mad.lo.u32 %1, %2, mh, nl;\n\t"          /* on a refill nl is 0, otherwise mh is 0: no carry into the high word */
+            "mad.hi.u32 %0, %2, mh, nh;\n\t"
+            "mov.u32 %3, nm;\n\t"
+            "@p ld.shared.u32 %2, [%4];\n\t"
+            "@p add.u32 %4, %4, 4;\n\t"
+            "}" : "+r"(hi), "+r"(lo), "+r"(next), "+r"(mark), "+r"(src) : "r"(c));
     }
     __device__ __forceinline__ uint32_t look(uint32_t word, uint32_t table, uint32_t four) const {
-        uint32_t addr; asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(addr) : "r"(word >> 20), "r"(four), "r"(table));
-        return lds32(addr);
+        uint32_t e;
+        asm("{\n\t.reg .b32 i, a;\n\tshr.u32 i, %1, 20;\n\tmad.lo.u32 a, i, %2, %3;\n\tld.shared.u32 %0, [a];\n\t}" : "=r"(e) : "r"(word), "r"(four), "r"(table));
+        return e;
     }
     __device__ __forceinline__ uint32_t one(uint32_t sym) {
         const uint32_t h = hi, zeros = min((uint32_t)__clz((int)h), 15u);
@@ -451,11 +474,16 @@ struct SmemWindow {
         const uint32_t b1 = one(sym);
         return (b0 << 8) | (b1 << 16);
     }
+    /* Four symbols.  Both look-ups and the single advance are straight-line code; a lane that meets a flagged entry
+       decodes pair by pair in a side branch (advancing its window itself) and joins the common advance with a shift
+       of zero. */
     __device__ __forceinline__ void quad(uint32_t table, uint32_t sym, uint32_t four, uint32_t &e01, uint32_t &e23) {
-        const uint32_t a = look(hi, table, four);
-        const uint32_t b = look(__funnelshift_l(0u, hi, a), table, four);
-        if (((a | b) & kEscape) == 0u) { consume(a + b); e01 = a; e23 = b; }
-        else { e01 = pair(table, sym, four); e23 = pair(table, sym, four); }
+        uint32_t a = look(hi, table, four);
+        uint32_t b = look(__funnelshift_l(0u, hi, a), table, four);
+        uint32_t c = a + b;
+        if (((a | b) & kEscape) != 0u) { a = pair(table, sym, four); b = pair(table, sym, four); c = 0u; }
+        consume(c);
+        e01 = a; e23 = b;
     }
 };
 /* the global-memory window behind the same interface (oversize blocks) */
@@ -473,6 +501,8 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
     const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 8u, col0 = cb * kBlockCols + lane * 16u;
     const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
     const bool col_ok = col0 < g.K16, diag = q == (r >> 1);
+    /* four distinct registers that hold zero (the compiler cannot tell): the unused halves of the A fragments */
+    const uint32_t z0 = four >> 8, z1 = four >> 9, z2 = four >> 10, z3 = four >> 11;
     XFrag8<XF32> xa, xb;
     if (col_ok) { xa.load(a.x, col0); xb.load(a.x, col0 + 8u); } else { xa.zero(); xb.zero(); }
     const uint8_t *rawp = a.low + (uint64_t)row0 * stride + (ELEM == kFp8 ? (col0 >> 1) : col0);
@@ -492,8 +522,8 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
             const XFrag8<XF32> &xf = k < 2 ? xa : xb;
             const int w = 2 * (k & 1);
             const uint32_t p0 = weave<0>(wa[k], e01), p1 = weave<2>(wa[k], e23);
-            mma_bf16(d, p0, 0u, p1, 0u, xf.head[w], xf.head[w + 1]);
-            if (XF32) mma_bf16(d, p0, 0u, p1, 0u, xf.tail[w], xf.tail[w + 1]);
+            mma_bf16(d, p0, z1, p1, z3, xf.head[w], xf.head[w + 1]);
+            if (XF32) mma_bf16(d, p0, z1, p1, z3, xf.tail[w], xf.tail[w + 1]);
         }
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -501,8 +531,8 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
             const XFrag8<XF32> &xf = k < 2 ? xa : xb;
             const int w = 2 * (k & 1);
             const uint32_t p0 = weave<0>(wb[k], e01), p1 = weave<2>(wb[k], e23);
-            mma_bf16(d, 0u, p0, 0u, p1, xf.head[w], xf.head[w + 1]);
-            if (XF32) mma_bf16(d, 0u, p0, 0u, p1, xf.tail[w], xf.tail[w + 1]);
+            mma_bf16(d, z0, p0, z2, p1, xf.head[w], xf.head[w + 1]);
+            if (XF32) mma_bf16(d, z0, p0, z2, p1, xf.tail[w], xf.tail[w + 1]);
         }
         if (diag) {
             stash[(2u * rp) * 8u + r] = (r & 1u) ? d[1] : d[0];
@@ -531,10 +561,9 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
     const uint32_t stages = smem_addr(mine), bars = stages + 2u * kPrefixStageBytes + 256u;
     float *stash = reinterpret_cast<float *>(mine + 2u * kPrefixStageBytes);
     const Geometry g(a.M, a.K, 0);
-    const uint32_t w = blockIdx.x * (kPrefixThreads / 32u) + warp;
-    const uint64_t first = (uint64_t)w * plan.per;
-    if (first >= g.nb) return;
-    const uint32_t b0 = (uint32_t)first, b1 = (uint32_t)min((uint64_t)g.nb, first + plan.per);
+    const uint32_t w = warp * gridDim.x + blockIdx.x;           /* interleaved: a short plan still spreads over all SMs */
+    if (w >= plan.warps) return;
+    const uint32_t b0 = (uint32_t)plan.start(w), b1 = (uint32_t)plan.start(w + 1u);
     if (lane == 0) { mbar_init(bars, 1u); mbar_init(bars + 8u, 1u); mbar_init_fence(); }
     __syncwarp();
     /* byte span of block b inside data: [start, start + bytes), rounded out to 16; bytes == 0 means "does not fit a stage" */
@@ -582,7 +611,7 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
         if (b + 2u < b1) issue(b + 2u, words_after);              /* the stage just decoded is free again (all lanes passed the block's last __syncwarp) */
         words = words_next; words_next = words_after;
         if (++cb == g.CB || b + 1u == b1) {                       /* the warp's share of this row group is complete */
-            if (lane < 8u) emit_flat(a, plan, rb * 8u + lane, w - (uint32_t)(((uint64_t)rb * g.CB) / plan.per), row_sum);
+            if (lane < 8u) emit_flat(a, plan, rb * 8u + lane, w - plan.owner((uint64_t)rb * g.CB), row_sum);
             row_sum = 0.f;
             if (cb == g.CB) { cb = 0; rb++; }
         }
@@ -667,9 +696,8 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     cudaError_t err;
     FlatPlan plan;
     if (layout == 0 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
-        make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), 1u, plan);
-        const uint64_t used = ((uint64_t)g.nb + plan.per - 1) / plan.per;
-        const int rgrid = (int)((used + kPrefixThreads / 32u - 1) / (kPrefixThreads / 32u));
+        make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan);
+        const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
         if (elem == kFp8) { if (a.x_bf16) prefix_ring_kernel_layout0<kFp8, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kFp8, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
         else { if (a.x_bf16) prefix_ring_kernel_layout0<kBf16, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kBf16, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
         err = cudaGetLastError();
@@ -680,9 +708,8 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
         return err;
     }
     if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
-        make_flat_plan(g, g.slots, (uint64_t)sms * (kRingThreads / 32u), 2u * kRingSlots, plan);
-        const uint64_t total = (uint64_t)g.groups * g.slots, used = (total + plan.per - 1) / plan.per;
-        const int rgrid = (int)((used + kRingThreads / 32u - 1) / (kRingThreads / 32u));
+        make_flat_plan(g, g.slots, (uint64_t)sms * (kRingThreads / 32u), plan);
+        const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
         ring_kernel_layout2<<<rgrid, kRingThreads, (kRingThreads / 32u) * kRingWarpBytes, st>>>(a, plan);
         err = cudaGetLastError();
         if (err == cudaSuccess && !plan.direct) {
