@@ -95,6 +95,22 @@ int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, con
                    const uint8_t *low, const uint16_t *x, const uint16_t *bias, const float *scale, float *scratch,
                    uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem);
 
+/* nwc_linear_bf16 without the scratch argument, for hosts that cannot allocate device memory for us (a server whose
+   runtime owns all of HBM from start-up, a sandbox without access to the allocator).  It has no counterpart in the
+   reference.  The partial sums live in an area of NWC_STATIC_SCRATCH_FLOATS floats (4 MiB) built into the library; every
+   GPU that loads the library carries it until the process exits.  The call allocates and frees nothing.
+   Limit: padded rows x column blocks (the scratch size nwc_layout reports) must not exceed NWC_STATIC_SCRATCH_FLOATS,
+   otherwise nothing is launched and NWC_ERR_STATIC_SCRATCH is returned.  Other return codes as nwc_linear_bf16.
+   The first call on each device looks up the area's device address; make that first call with the device current and
+   before any stream capture begins.  All calls on a device share the one area and it keeps whatever the last call
+   left there: two calls whose kernels overlap on the GPU (different streams) race with each other, so keep calls on
+   one device in stream order.  Nothing in the area needs clearing between calls. */
+#define NWC_STATIC_SCRATCH_FLOATS 1048576
+#define NWC_ERR_STATIC_SCRATCH (-4)
+int nwc_linear_bf16_static(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr,
+                           const uint32_t *lut, const uint8_t *low, const float *x, const uint16_t *bias,
+                           const float *scale, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem);
+
 /* ---- decode-step kernels (the reference leaves these operations to Transformers eager code inside its CUDA graph,
    scripts/graph_decode.py:46-60; there is no reference library entry point for them) ------------------------------- */
 

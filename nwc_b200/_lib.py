@@ -39,6 +39,7 @@ _SIGNATURES = {
     "nwc_attention_decode": (I, [P, P, P, P, P, P, P, P, P, U32, U32, U32, U32, ctypes.c_float, P, P]),
     "nwc_swiglu": (I, [P, P, U32, P, P]),
     "nwc_argmax": (I, [P, P, U32, P, P, P, P]),
+    "nwc_linear_bf16_static": (I, [P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_matvec": (I, [P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_dequant": (I, [P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_gather": (I, [P, P, P, P, P, P, P, U32, P, U64, U32, U32, I]),
