@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--elem", default="bf16")
     ap.add_argument("--prompt", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     return ap.parse_args()
 
 
@@ -139,7 +140,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
-    eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16)
+    eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch))
     eng.capture()
     g = torch.Generator().manual_seed(1234 + rank)
     prompt = torch.randint(0, cfg.vocab, (a.prompt,), generator=g)
@@ -183,11 +184,11 @@ def main():
     w = weights.lm_head
     reps = 20
     side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side): eng._linear(w, eng.xn, eng.logits)
+    with torch.cuda.stream(side): eng._linear(w, eng.xtmp, eng.logits)
     torch.cuda.current_stream().wait_stream(side)
     kg = torch.cuda.CUDAGraph()
     with torch.cuda.graph(kg):
-        for _ in range(reps): eng._linear(w, eng.xn, eng.logits)
+        for _ in range(reps): eng._linear(w, eng.xtmp, eng.logits)
     for _ in range(3): kg.replay()
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -114,10 +114,33 @@ int nwc_linear_bf16_static(void *stream, const uint8_t *data, const uint32_t *ba
 /* ---- decode-step kernels (the reference leaves these operations to Transformers eager code inside its CUDA graph,
    scripts/graph_decode.py:46-60; there is no reference library entry point for them) ------------------------------- */
 
-/* h <- bf16(h + delta) (delta may be NULL); xn16 <- bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))); xn32 (may be NULL)
-   receives the same values as fp32.  All vectors have H elements. */
-int nwc_add_rmsnorm(void *stream, uint16_t *h, const uint16_t *delta, const uint16_t *weight, float eps, uint32_t H,
-                    uint16_t *xn16, float *xn32);
+/* h_out <- bf16(h_in + delta) (delta may be NULL; h_out may be h_in); xn16 <- bf16(weight * bf16(h_out * rsqrt(mean(h_out^2)
+   + eps))); xn32 (may be NULL) receives the same values as fp32.  All vectors have H elements. */
+int nwc_add_rmsnorm(void *stream, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out, const uint16_t *weight,
+                    float eps, uint32_t H, uint16_t *xn16, float *xn32);
+
+/* Token matvec with its activation prologue fused: y = bf16(scale * (W x) + bias) where x is
+     mode 0  the bf16 vector x (as nwc_linear_x16),
+     mode 1  RMSNorm of the residual stream: h_out <- bf16(h_in + delta) (delta may be NULL, h_out may be NULL but must
+             not be h_in), x = bf16(norm_w * bf16(h_out * rsqrt(mean(h_out^2) + eps))),
+     mode 2  SwiGLU of a fused projection: x = bf16(bf16(silu(gate_up[i])) * gate_up[K + i]).
+   Layout-0 matrices small enough that launch latency dominates run as ONE launch (prologue, decode, reduction and bf16
+   output in a single kernel); every other matrix runs the prologue kernel into xtmp (bf16, K rounded up to 32; needed
+   for modes 1 and 2) followed by the regular token path with `scratch`. */
+int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                     const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta,
+                     uint16_t *h_out, const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp,
+                     const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
+                     uint32_t K, int elem);
+
+/* Kernels one token-path call launches on the current device (for launch accounting): fused_mode -1 = nwc_linear_bf16 /
+   nwc_linear_x16, 0..2 = nwc_linear_fused with that mode.  -1 on a bad shape or without a device. */
+int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_mode);
+
+/* on != 0: the decode-step launches (nwc_linear_fused's single-launch kernel, nwc_add_rmsnorm, nwc_attention_decode,
+   nwc_swiglu, nwc_argmax) allow programmatic dependent launch, so each overlaps its set-up with the tail of the kernel
+   before it; the kernels order themselves with griddepcontrol.wait.  Off by default. */
+void nwc_set_dependent_launch(int on);
 
 /* One token of grouped-query attention.  qkv = [n_q | n_kv | n_kv] heads x head_dim (bf16) of the token at position
    *pos; q_norm / k_norm: per-head RMSNorm weights (bf16[head_dim]) or NULL; cos_t / sin_t: bf16[max positions][head_dim];

@@ -96,6 +96,51 @@ NWC_EXPORT int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t 
     return run_segments(0, stream, data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, n, block, K, elem, 0, 1);
 }
 
+/* Token matvec with the activation prologue fused where that pays (layout 0 matrices of at most two blocks per resident
+   warp: one launch in all); other matrices run the prologue kernel into xtmp and then the regular token path. */
+NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                                const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
+                                const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
+                                float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1 || mode < 0 || mode > 2) return -1;
+    if (!aligned16(data) || !aligned16(low) || !aligned16(lut)) return -1;
+    if (mode == kInputNorm && (!h_in || !norm_w || h_out == h_in)) return -1;
+    if (mode == kInputSwiglu && !gate_up) return -1;
+    if (mode == kInputPlain && (!x || !aligned16(x))) return -1;
+    const int sms = device_sms();
+    if (!sms) return (int)cudaErrorNoDevice;
+    const uint32_t M = (uint32_t)(n / K);
+    const Geometry g(M, K, layout_of(elem));
+    if (layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) {
+        SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
+        FusedInput in{mode, h_in, delta, h_out, norm_w, eps, gate_up};
+        return (int)launch_small_layout0(elem, sms, (cudaStream_t)stream, a, in);
+    }
+    const uint16_t *xin = x;
+    if (mode != kInputPlain) {
+        if (!xtmp || !aligned16(xtmp)) return -1;
+        const int e = mode == kInputNorm ? nwc_add_rmsnorm(stream, h_in, delta, h_out ? h_out : xtmp, norm_w, eps, K, xtmp, nullptr)
+                                         : nwc_swiglu(stream, gate_up, K, xtmp, nullptr);
+        if (e) return e;
+        xin = xtmp;
+    }
+    return run_segments(0, stream, data, bases, hdr, lut, low, xin, scratch, nullptr, bias, scale, y, n, block, K, elem, 0, 1);
+}
+
+/* number of kernels one token-path call launches on the current device: fused_mode -1 = nwc_linear_bf16 / nwc_linear_x16,
+   0..2 = nwc_linear_fused with that mode */
+NWC_EXPORT int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_mode) {
+    if (!shape_ok(n, kBlockWeights, K)) return -1;
+    const int sms = device_sms();
+    if (!sms) return -1;
+    const uint32_t M = (uint32_t)(n / K);
+    const Geometry g(M, K, layout_of(elem));
+    if (fused_mode >= 0 && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) return 1;
+    return count_token_launches(elem, sms, M, K) + (fused_mode > 0 ? 1 : 0);
+}
+
+NWC_EXPORT void nwc_set_dependent_launch(int on) { set_dependent_launch(on != 0); }
+
 NWC_EXPORT int nwc_matvec(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                           const uint8_t *low, const float *x, float *y, uint64_t n, uint32_t block, uint32_t K, int elem) {
     if (!shape_ok(n, block, K)) return -1;

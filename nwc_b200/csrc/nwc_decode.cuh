@@ -131,6 +131,13 @@ __device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t &hi, u
 __device__ __forceinline__ uint16_t bf16_round(float v) {          /* the reference's finalize rounding (no NaN case) */
     uint32_t u = __float_as_uint(v); u += 0x7FFFu + ((u >> 16) & 1u); return (uint16_t)(u >> 16);
 }
+/* round to nearest even, NaN kept: activations (unlike weights) may overflow */
+__device__ __forceinline__ uint16_t bf16_round_nan(float v) {
+    uint32_t u = __float_as_uint(v);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40u);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
 __device__ __forceinline__ float bf16_to_float(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
 /* fp8 e4m3 byte -> fp32 */

@@ -45,6 +45,11 @@ struct XFrag8 {
             head[0] = v.x; head[1] = v.y; head[2] = v.z; head[3] = v.w;
         }
     }
+    /* eight bf16 values from a vector staged in shared memory (bf16 only) */
+    __device__ __forceinline__ void load_shared(uint32_t addr) {
+        const uint4 v = lds128(addr);
+        head[0] = v.x; head[1] = v.y; head[2] = v.z; head[3] = v.w;
+    }
     __device__ __forceinline__ void zero() {
 #pragma unroll
         for (int i = 0; i < 4; i++) { head[i] = 0u; tail[i] = 0u; }
@@ -497,14 +502,16 @@ struct GlobalWindow : BitWindow<MAX_RANK> {
    rows as the "row r + 8" half, the other half is zero; after two rows the diagonal of D holds the quad's dot products. */
 template <class WIN, int ELEM, bool XF32>
 __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane,
-                                                      uint32_t table, uint32_t sym, uint32_t four, float *stash) {
+                                                      uint32_t table, uint32_t sym, uint32_t four, float *stash, uint32_t xs = 0u) {
     const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 8u, col0 = cb * kBlockCols + lane * 16u;
     const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
     const bool col_ok = col0 < g.K16, diag = q == (r >> 1);
     /* four distinct registers that hold zero (the compiler cannot tell): the unused halves of the A fragments */
     const uint32_t z0 = four >> 8, z1 = four >> 9, z2 = four >> 10, z3 = four >> 11;
     XFrag8<XF32> xa, xb;
-    if (col_ok) { xa.load(a.x, col0); xb.load(a.x, col0 + 8u); } else { xa.zero(); xb.zero(); }
+    if (!col_ok) { xa.zero(); xb.zero(); }
+    else if (!XF32 && xs) { xa.load_shared(xs + col0 * 2u); xb.load_shared(xs + col0 * 2u + 16u); }     /* x staged by the CTA */
+    else { xa.load(a.x, col0); xb.load(a.x, col0 + 8u); }
     const uint8_t *rawp = a.low + (uint64_t)row0 * stride + (ELEM == kFp8 ? (col0 >> 1) : col0);
     uint4 raw0 = raw_row16<ELEM>(rawp, col_ok && row0 < g.M), raw1 = raw_row16<ELEM>(rawp + stride, col_ok && row0 + 1u < g.M);
 #pragma unroll 1
@@ -618,6 +625,139 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
     }
 }
 
+/* ---- layout 0, small matrices of the decode step: one launch, activation prologue fused ------------------------------ */
+/* A decoder layer's matrices hold at most one block per resident warp on a B200, so their cost is launch latency plus
+   the serial decode of one block, and every extra launch (norm, activation, finalize) costs as much as the matvec.
+   Here a CTA of 8 warps owns whole row groups: the warps of a row group split its column blocks, add their row sums
+   through shared memory in warp order and write bf16 y themselves.  The activation vector is built once per CTA in
+   shared memory, optionally from the residual stream (h_out = h_in + delta, x = RMSNorm(h_out) * w) or from a fused
+   gate/up vector (x = silu(gate) * up), with the rounding steps of the separate kernels in nwc_model.cu.
+   Everything that does not depend on the previous kernel (table staging) runs before griddepcontrol.wait, so with
+   programmatic dependent launch it overlaps the predecessor's tail. */
+constexpr uint32_t kSmallThreads = 256, kSmallWarps = kSmallThreads / 32u;
+
+__device__ __forceinline__ float bf16_rt(float v) { return bf16_to_float(bf16_round_nan(v)); }
+
+template <int ELEM>
+__global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
+    constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
+    extern __shared__ __align__(128) uint8_t small_smem[];
+    uint32_t *tables = reinterpret_cast<uint32_t *>(small_smem);
+    float *stash_all = reinterpret_cast<float *>(small_smem + 16416u);                 /* [8 warps][64] */
+    float *red = stash_all + kSmallWarps * 64u;                                         /* [8 warps][8 rows] */
+    float *scal = red + kSmallWarps * 8u;                                               /* [8] block reduction scratch */
+    uint8_t *stage_all = reinterpret_cast<uint8_t *>(scal + 8u);                        /* [8 warps][kPrefixStageBytes] lane streams of one block */
+    uint64_t *bar_all = reinterpret_cast<uint64_t *>(stage_all + kSmallWarps * kPrefixStageBytes);
+    uint16_t *xs = reinterpret_cast<uint16_t *>(bar_all + kSmallWarps);
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const Geometry g(a.M, a.K, 0);
+    const uint32_t stage = smem_addr(stage_all) + warp * kPrefixStageBytes, bar = smem_addr(bar_all) + warp * 8u;
+    if (lane == 0) { mbar_init(bar, 1u); mbar_init_fence(); }
+    __syncwarp();
+    /* byte span of block b inside data, rounded out to 16 bytes, and the bulk copy of it into this warp's stage;
+       returns 0 (no copy) when the stream does not fit the stage */
+    auto fetch = [&](uint32_t b, uint32_t words_of_b, uint32_t &start) -> uint32_t {
+        const uint32_t base = __ldg(a.bases + b);
+        uint32_t len;
+        if (b + 1u < g.nb) len = __ldg(a.bases + b + 1u) - base;
+        else { uint32_t t; warp_exclusive_sum(words_of_b, lane, t); len = 4u * t; }
+        start = base & ~15u;
+        uint32_t bytes = (base + len + 16u - start + 15u) & ~15u;
+        if (bytes > kPrefixStageBytes) bytes = 0u;
+        if (bytes && lane == 0) { async_proxy_fence(); mbar_expect(bar, bytes); bulk_load(stage, a.data + start, bytes, bar); }
+        return bytes;
+    };
+    /* warps per row group and row groups per CTA pass */
+    const uint32_t wg = g.CB >= kSmallWarps ? kSmallWarps : (g.CB >= 4u ? 4u : (g.CB >= 2u ? 2u : 1u)), per_pass = kSmallWarps / wg;
+    const uint32_t my_group = warp / wg, j = warp - my_group * wg, passes = (g.groups + per_pass - 1u) / per_pass;
+    /* the weights do not depend on the kernel before this one: start the copy of this warp's first stream and pull its
+       raw rows towards L2 before anything else, so that both overlap the table staging, the wait and the prologue */
+    uint32_t first_b = 0xFFFFFFFFu, first_words = 0u, first_start = 0u, first_bytes = 0u;
+    {
+        const uint32_t rb = blockIdx.x * per_pass + my_group;
+        if (rb < g.groups && j < g.CB) {
+            first_b = rb * g.CB + j;
+            first_words = __ldg(a.hdr + (uint64_t)first_b * kLanes + lane);
+            first_bytes = fetch(first_b, first_words, first_start);
+            const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16, row = rb * 8u + (lane >> 2), off = j * (ELEM == kFp8 ? 256u : 512u) + (lane & 3u) * 128u;
+            if (row < g.M && off < stride) prefetch_l2(a.low + (uint64_t)row * stride + off);
+        }
+    }
+    stage_tables(tables, a.lut, tid, kSmallThreads);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    /* ---- activation vector -> shared memory (bf16, zero beyond K) ---- */
+    if (in.mode == kInputNorm) {
+        float ss = 0.f;
+        for (uint32_t i = tid; i < a.K; i += kSmallThreads) {
+            float v = bf16_to_float(in.h_in[i]);
+            if (in.delta) v = bf16_rt(v + bf16_to_float(in.delta[i]));
+            if (blockIdx.x == 0 && in.h_out) in.h_out[i] = bf16_round_nan(v);
+            xs[i] = bf16_round_nan(v);
+            ss += v * v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) scal[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (uint32_t i = 0; i < kSmallWarps; i++) tot += scal[i];
+        const float inv = rsqrtf(tot / (float)a.K + in.eps);
+        for (uint32_t i = tid; i < g.K16; i += kSmallThreads)
+            xs[i] = i < a.K ? bf16_round_nan(bf16_to_float(in.norm_w[i]) * bf16_rt(bf16_to_float(xs[i]) * inv)) : (uint16_t)0;
+    } else if (in.mode == kInputSwiglu) {
+        for (uint32_t i = tid; i < g.K16; i += kSmallThreads) {
+            uint16_t v = 0;
+            if (i < a.K) { const float gt = bf16_to_float(in.gate_up[i]), up = bf16_to_float(in.gate_up[a.K + i]); v = bf16_round_nan(bf16_rt(gt / (1.f + __expf(-gt))) * up); }
+            xs[i] = v;
+        }
+    } else {
+        for (uint32_t i = tid; i < g.K16; i += kSmallThreads) xs[i] = i < a.K ? static_cast<const uint16_t *>(a.x)[i] : (uint16_t)0;
+    }
+    __syncthreads();
+    const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords, xs_addr = smem_addr(xs);
+    float *stash = stash_all + warp * 64u;
+    uint32_t phase = 0;
+    for (uint32_t pass = blockIdx.x; pass < passes; pass += gridDim.x) {
+        const uint32_t rb = pass * per_pass + my_group;
+        float row_sum = 0.f;
+        if (rb < g.groups) {
+            for (uint32_t cb = j; cb < g.CB; cb += wg) {
+                const uint32_t b = rb * g.CB + cb;
+                uint32_t words, start, bytes, total;
+                if (b == first_b) { words = first_words; start = first_start; bytes = first_bytes; }
+                else { words = __ldg(a.hdr + (uint64_t)b * kLanes + lane); bytes = fetch(b, words, start); }
+                const uint32_t before = warp_exclusive_sum(words, lane, total), base = __ldg(a.bases + b);
+                if (bytes) {
+                    const bool landed = mbar_wait(bar, phase);    /* on a timeout the status word is set and the block is skipped; the CTA's barriers below still need this warp */
+                    phase ^= 1u;
+                    if (landed) {
+                        SmemWindow<MR> W; W.open(stage + (base - start) + 4u * before);
+                        row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, false>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
+                    }
+                } else {
+                    GlobalWindow<MR> W; W.sym_ptr = reinterpret_cast<const uint8_t *>(tables + kTableWords);
+                    W.open(reinterpret_cast<const uint32_t *>(a.data + base) + before);
+                    row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, false>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
+                }
+            }
+        }
+        if (lane < 8u) red[warp * 8u + lane] = row_sum;
+        __syncthreads();
+        if (j == 0u && lane < 8u && rb < g.groups) {
+            float v = 0.f;
+            for (uint32_t k = 0; k < wg; k++) v += red[(warp + k) * 8u + lane];
+            const uint32_t row = rb * 8u + lane;
+            if (row < a.M) {
+                if (a.scale) v *= __ldg(a.scale + row);
+                if (a.bias) v += bf16_to_float(__ldg(a.bias + row));
+                a.y[row] = bf16_round(v);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 /* ---- the persistent segment kernel -------------------------------------------------------------------------------- */
 template <int LAYOUT, int ELEM, int MODE, bool XF32>
 __global__ void __launch_bounds__(kSegmentThreads, 1) segment_kernel(const SegmentArgs a) {
@@ -665,6 +805,34 @@ static cudaError_t launch_modes(int mode, int grid, size_t smem, cudaStream_t st
 
 /* number of K splits: one segment per row group when there are enough row groups to give every resident warp work,
    otherwise the fewest splits (at most one per column block) that reach two segments per warp */
+static bool g_dependent_launch = false;
+void set_dependent_launch(bool on) { g_dependent_launch = on; }
+bool dependent_launch() { return g_dependent_launch; }
+
+/* kernel launch that may start before its stream predecessor has finished (the kernel orders itself with
+   griddepcontrol.wait) when dependent launch is switched on */
+template <class... Params, class... Args>
+static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_dependent_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
+constexpr uint32_t kSmallFixedSmem = 16416u + kSmallWarps * 64u * 4u + kSmallWarps * 8u * 4u + 32u + kSmallWarps * kPrefixStageBytes + kSmallWarps * 8u;
+cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in) {
+    const Geometry g(a.M, a.K, 0);
+    const uint32_t wg = g.CB >= kSmallWarps ? kSmallWarps : (g.CB >= 4u ? 4u : (g.CB >= 2u ? 2u : 1u)), per_pass = kSmallWarps / wg;
+    const uint32_t passes = (g.groups + per_pass - 1u) / per_pass;
+    const uint32_t grid = passes < 4u * (uint32_t)sms ? passes : 4u * (uint32_t)sms;
+    const size_t smem = kSmallFixedSmem + (size_t)g.K16 * 2u;
+    if (type_of(code) == kFp8) return launch_kernel(small_kernel_layout0<kFp8>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
+    return launch_kernel(small_kernel_layout0<kBf16>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
+}
+
 static bool g_disable_ring = false;
 void set_ring_kernels(bool on) { g_disable_ring = !on; }
 int read_kernel_status(bool clear) {
@@ -681,6 +849,16 @@ uint32_t choose_splits(const Geometry &g, int mode, int code, int sms) {
     if (g.groups >= 2u * warps || g.CB == 1u) return 1u;
     const uint64_t want = (2u * warps + g.groups - 1u) / g.groups;
     return (uint32_t)(want < g.CB ? want : g.CB);
+}
+
+/* kernels the token path launches for an M x K matrix (automatic splits) */
+int count_token_launches(int code, int sms, uint32_t M, uint32_t K) {
+    const int layout = layout_of(code), elem = type_of(code);
+    const Geometry g(M, K, layout);
+    FlatPlan plan;
+    if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
+    if (!g_disable_ring && layout == 2 && elem == kBf16) { make_flat_plan(g, g.slots, (uint64_t)sms * (kRingThreads / 32u), plan); return plan.direct ? 1 : 2; }
+    return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a) {
@@ -738,6 +916,8 @@ static void opt_in_smem() {
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeAtomic, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 void configure_segment_kernels() {
+    cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((kRingThreads / 32u) * kRingWarpBytes));
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);

@@ -27,11 +27,27 @@ struct SegmentArgs {
     uint32_t splits_forced;     /* the caller's own splits request (0 = none): forced splits take the plain kernels */
 };
 
+/* How the fused small-matrix kernel builds its activation vector. */
+enum FusedInputMode : int { kInputPlain = 0, kInputNorm = 1, kInputSwiglu = 2 };
+struct FusedInput {
+    int mode;
+    const uint16_t *h_in;       /* kInputNorm: residual stream in (bf16[K])                         */
+    const uint16_t *delta;      /* kInputNorm: added to h_in first, or null                         */
+    uint16_t *h_out;            /* kInputNorm: receives h_in + delta (must not alias h_in), or null */
+    const uint16_t *norm_w;     /* kInputNorm: RMSNorm weight                                       */
+    float eps;
+    const uint16_t *gate_up;    /* kInputSwiglu: [gate | up], 2 K values                            */
+};
+cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in);
+void set_dependent_launch(bool on);           /* programmatic dependent launch for the decode-step launches */
+bool dependent_launch();
+
 uint32_t choose_splits(const Geometry &g, int mode, int code, int sms);
 void set_ring_kernels(bool on);               /* tests: switch the bulk-copy ring kernels off to compare with the plain ones */
 int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gave up; synchronises */
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a);
 void configure_segment_kernels();
+int count_token_launches(int code, int sms, uint32_t M, uint32_t K);
 
 cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids);
 cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);

@@ -11,6 +11,7 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 #include "../../include/nwc_ops.h"
+#include "nwc_launch.h"
 
 #define NWC_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -25,6 +26,12 @@ __device__ __forceinline__ uint16_t f2bf(float v) {
     return (uint16_t)(u >> 16);
 }
 __device__ __forceinline__ float bfround(float v) { return bf2f(f2bf(v)); }
+/* let the next kernel of the stream start its own prologue, then wait until everything before this kernel is complete
+   (both are no-ops unless the launch allowed programmatic dependent launch) */
+__device__ __forceinline__ void dependency_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ float block_sum(float v, float *red) {
 #pragma unroll
@@ -49,14 +56,16 @@ __device__ __forceinline__ float block_max(float v, float *red) {
     return t;
 }
 
-/* h <- bf16(h + delta) (delta may be null); xn <- bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))); optional fp32 copy */
-__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(uint16_t *__restrict__ h, const uint16_t *__restrict__ delta, const uint16_t *__restrict__ weight,
+/* h <- bf16(h_in + delta) (delta may be null, h may alias h_in); xn <- bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))); optional fp32 copy */
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const uint16_t *h_in, const uint16_t *__restrict__ delta, uint16_t *h, const uint16_t *__restrict__ weight,
                                                             float eps, uint32_t H, uint16_t *__restrict__ xn16, float *__restrict__ xn32) {
     __shared__ float red[32];
+    dependency_sync();
     float ss = 0.f;
     for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = bf2f(h[i]);
-        if (delta) { v = bfround(v + bf2f(delta[i])); h[i] = f2bf(v); }
+        float v = bf2f(h_in[i]);
+        if (delta) v = bfround(v + bf2f(delta[i]));
+        if (delta || h != h_in) h[i] = f2bf(v);
         ss += v * v;
     }
     const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
@@ -77,6 +86,7 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const uint16_t *_
     float *qs = sm, *ks = sm + hd, *scores = sm + 2 * hd;          /* q, current k (fp32), scores [max_len] */
     __shared__ float red[32];
     const uint32_t head = blockIdx.x, kvh = head / (n_q / n_kv), tid = threadIdx.x;
+    dependency_sync();
     const int32_t pos = *pos_ptr;
     if (pos < 0 || (uint32_t)pos >= max_len) { if (tid == 0) atomicExch(status, 1); return; }
     const uint16_t *qp = qkv + (uint64_t)head * hd, *kp = qkv + (uint64_t)(n_q + kvh) * hd, *vp = qkv + (uint64_t)(n_q + n_kv + kvh) * hd;
@@ -126,17 +136,26 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const uint16_t *_
     float denom = 0.f;
     for (int32_t t = tid; t <= pos; t += blockDim.x) { const float e = __expf(scores[t] - best); scores[t] = e; denom += e; }
     denom = block_sum(denom, red);                                 /* also orders the score writes before the reads below */
-    /* out[d] = sum_t p[t] v[t][d]: thread (g, d) takes positions t = g mod groups; groups are added through shared memory */
-    const uint32_t groups = blockDim.x / hd, g = tid / hd, d = tid - g * hd;
+    /* out[d] = sum_t p[t] v[t][d]: hd / 8 threads cover one cached row with 128-bit loads, the thread groups take
+       positions t = g mod groups and are added through shared memory in group order */
+    const uint32_t per_row = hd >> 3, groups = blockDim.x / per_row, g = tid / per_row, c = tid - g * per_row;
     const uint16_t *vc = v_cache + (uint64_t)kvh * max_len * hd;
-    float acc = 0.f;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (g < groups) {
-        for (int32_t t = g; t < pos; t += groups) acc = fmaf(scores[t], bf2f(vc[(uint64_t)t * hd + d]), acc);
-        if (g == (uint32_t)pos % groups) acc = fmaf(scores[pos], bf2f(vp[d]), acc);
+        for (int32_t t = g; t <= pos; t += groups) {
+            const uint4 w = *reinterpret_cast<const uint4 *>((t == pos ? vp : vc + (uint64_t)t * hd) + 8u * c);
+            const float p = scores[t];
+            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) { acc[2 * j] = fmaf(p, __uint_as_float(u[j] << 16), acc[2 * j]); acc[2 * j + 1] = fmaf(p, __uint_as_float(u[j] & 0xFFFF0000u), acc[2 * j + 1]); }
+        }
     }
-    float *part = sm;                                              /* [groups][hd] over q, k and the head of scores: all dead now */
+    float *part = sm;                                              /* [groups][hd] over q, k and the scores: all dead now */
     __syncthreads();
-    if (g < groups) part[g * hd + d] = acc;
+    if (g < groups) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) part[g * hd + 8u * c + j] = acc[j];
+    }
     __syncthreads();
     if (tid < hd) {
         float o = 0.f;
@@ -148,6 +167,7 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const uint16_t *_
 /* a <- bf16(bf16(silu(gate)) * up), gate = gu[0..I), up = gu[I..2I); optional fp32 copy */
 __global__ void swiglu_kernel(const uint16_t *__restrict__ gu, uint32_t I, uint16_t *__restrict__ a16, float *__restrict__ a32) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    dependency_sync();
     if (i >= I) return;
     const float g = bf2f(gu[i]), u = bf2f(gu[I + i]);
     const float y = bfround(bfround(g / (1.f + __expf(-g))) * u);
@@ -155,58 +175,96 @@ __global__ void swiglu_kernel(const uint16_t *__restrict__ gu, uint32_t I, uint1
     if (a32) a32[i] = y;
 }
 
-/* Greedy choice: smallest index of the largest logit.  Writes the token for the next step, logs it, advances pos. */
-__global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t *__restrict__ logits, uint32_t V, int64_t *__restrict__ cur, int64_t *__restrict__ log,
-                                                       int32_t *__restrict__ pos, int32_t *__restrict__ step) {
-    __shared__ float bv[32]; __shared__ uint32_t bi[32];
-    float best = -INFINITY; uint32_t idx = 0xFFFFFFFFu;
-    for (uint32_t i = threadIdx.x; i < V; i += blockDim.x) { const float v = bf2f(logits[i]); if (v > best) { best = v; idx = i; } }
+/* Greedy choice: smallest index of the largest logit.  Every CTA folds its slice into one 64-bit key (order-preserving
+   image of the value in the high word, inverted index in the low word) and takes the maximum into a device word; the
+   CTA that arrives last writes the token for the next step, logs it, advances pos and step, and clears the two words
+   for the next call.  Calls on one device must not overlap (they share the two words). */
+static __device__ unsigned long long g_argmax_key;
+static __device__ unsigned int g_argmax_arrived;
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t i) {
+    uint32_t u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (0xFFFFFFFFu - i);
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const uint16_t *__restrict__ logits, uint32_t V, int64_t *__restrict__ cur, int64_t *__restrict__ log,
+                                                      int32_t *__restrict__ pos, int32_t *__restrict__ step) {
+    __shared__ unsigned long long best_of_warp[8];
+    dependency_sync();
+    unsigned long long best = 0ull;
+    const uint32_t chunks = V >> 3, stride = gridDim.x * blockDim.x;
+    for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < chunks; k += stride) {
+        const uint4 w = *reinterpret_cast<const uint4 *>(logits + 8ull * k);
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        for (int j = 0; j < 4; j++) {
+            const unsigned long long a = argmax_key(__uint_as_float(u[j] << 16), 8u * k + 2u * j), b = argmax_key(__uint_as_float(u[j] & 0xFFFF0000u), 8u * k + 2u * j + 1u);
+            best = a > best ? a : best; best = b > best ? b : best;
+        }
     }
-    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    if (blockIdx.x == 0 && threadIdx.x < (V & 7u)) { const uint32_t i = (V & ~7u) + threadIdx.x; const unsigned long long a = argmax_key(bf2f(logits[i]), i); best = a > best ? a : best; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o); best = other > best ? other : best; }
+    if ((threadIdx.x & 31) == 0) best_of_warp[threadIdx.x >> 5] = best;
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (uint32_t w = 1; w < (blockDim.x + 31) / 32; w++) if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
-        if (idx == 0xFFFFFFFFu) idx = 0;
-        cur[0] = (int64_t)idx;
-        if (log) log[*step] = (int64_t)idx;
-        *pos += 1; *step += 1;
+        for (uint32_t w = 1; w < (blockDim.x >> 5); w++) best = best_of_warp[w] > best ? best_of_warp[w] : best;
+        atomicMax(&g_argmax_key, best);
+        __threadfence();
+        if (atomicAdd(&g_argmax_arrived, 1u) == gridDim.x - 1u) {
+            __threadfence();
+            const unsigned long long key = atomicExch(&g_argmax_key, 0ull);
+            g_argmax_arrived = 0u;
+            const uint32_t idx = key ? 0xFFFFFFFFu - (uint32_t)key : 0u;
+            cur[0] = (int64_t)idx;
+            if (log) log[*step] = (int64_t)idx;
+            *pos += 1; *step += 1;
+        }
     }
+}
+
+template <class... Params, class... Args>
+cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, void *stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = nwc::dependent_launch() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
 }  // namespace
 
 /* ---- decode-step entry points (no counterpart in the reference's library; its decode step is Transformers code) --- */
 
-NWC_EXPORT int nwc_add_rmsnorm(void *stream, uint16_t *h, const uint16_t *delta, const uint16_t *weight, float eps, uint32_t H, uint16_t *xn16, float *xn32) {
+NWC_EXPORT int nwc_add_rmsnorm(void *stream, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out, const uint16_t *weight, float eps, uint32_t H,
+                               uint16_t *xn16, float *xn32) {
     if (!H) return -1;
-    add_rmsnorm_kernel<<<1, H >= 4096 ? 1024 : (H >= 1024 ? 512 : 256), 0, (cudaStream_t)stream>>>(h, delta, weight, eps, H, xn16, xn32);
-    return (int)cudaGetLastError();
+    return (int)launch(add_rmsnorm_kernel, dim3(1), dim3(H >= 4096 ? 1024 : (H >= 1024 ? 512 : 256)), 0, stream, h_in, delta, h_out, weight, eps, H, xn16, xn32);
 }
 
 NWC_EXPORT int nwc_attention_decode(void *stream, const uint16_t *qkv, const uint16_t *q_norm, const uint16_t *k_norm, const uint16_t *cos_t, const uint16_t *sin_t,
                                     uint16_t *k_cache, uint16_t *v_cache, const int32_t *pos, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_len,
                                     float eps, uint16_t *out, int *status) {
     if (!n_q || !n_kv || n_q % n_kv || head_dim % 8 || head_dim > 256 || head_dim < 32 || max_len == 0 || max_len > 8192) return -1;
-    const size_t smem = (2 * (size_t)head_dim + (max_len > 256u ? max_len : 256u)) * sizeof(float);
+    const size_t floats = 2 * (size_t)head_dim + max_len, need = (256u / (head_dim / 8u)) * (size_t)head_dim;   /* scores, or the group partials */
+    const size_t smem = (floats > need ? floats : need) * sizeof(float);
     static bool opted = false;
     if (smem > 48 * 1024 && !opted) { cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024); opted = true; }
-    attention_decode_kernel<<<n_q, 256, smem, (cudaStream_t)stream>>>(qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, head_dim, max_len, eps,
-                                                                     rsqrtf((float)head_dim), out, status);
-    return (int)cudaGetLastError();
+    return (int)launch(attention_decode_kernel, dim3(n_q), dim3(256), smem, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, head_dim,
+                       max_len, eps, 1.0f / sqrtf((float)head_dim), out, status);
 }
 
 NWC_EXPORT int nwc_swiglu(void *stream, const uint16_t *gate_up, uint32_t I, uint16_t *a16, float *a32) {
     if (!I) return -1;
-    swiglu_kernel<<<(I + 255) / 256, 256, 0, (cudaStream_t)stream>>>(gate_up, I, a16, a32);
-    return (int)cudaGetLastError();
+    return (int)launch(swiglu_kernel, dim3((I + 255) / 256), dim3(256), 0, stream, gate_up, I, a16, a32);
 }
 
 NWC_EXPORT int nwc_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step) {
     if (!V) return -1;
-    argmax_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(logits, V, cur, log, pos, step);
-    return (int)cudaGetLastError();
+    if (reinterpret_cast<uintptr_t>(logits) & 15u) return -1;
+    const uint32_t chunks = V >> 3, grid = chunks >= 256u * 64u ? 64u : (chunks + 255u) / 256u + (chunks ? 0u : 1u);
+    return (int)launch(argmax_kernel, dim3(grid ? grid : 1u), dim3(256), 0, stream, logits, V, cur, log, pos, step);
 }

@@ -98,15 +98,17 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda"):
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False):
         L.require_cuda()
+        self.dependent_launch = bool(dependent_launch)
         self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
         c = self.cfg
         bf = lambda n: torch.zeros(n, dtype=torch.bfloat16, device=device)
         pad32 = lambda n: (n + 31) // 32 * 32
-        self.h, self.xn = bf(pad32(c.hidden)), bf(pad32(c.hidden))
-        self.qkv, self.attn, self.proj = bf(c.qkv_rows), bf(pad32(c.n_q * c.head_dim)), bf(pad32(c.hidden))
-        self.gu, self.act = bf(2 * c.intermediate), bf(pad32(c.intermediate))
+        self.h, self.h2 = bf(pad32(c.hidden)), bf(pad32(c.hidden))
+        self.xtmp = bf(pad32(max(c.hidden, c.intermediate)))
+        self.qkv, self.attn, self.proj, self.proj2 = bf(c.qkv_rows), bf(pad32(c.n_q * c.head_dim)), bf(pad32(c.hidden)), bf(pad32(c.hidden))
+        self.gu = bf(2 * c.intermediate)
         self.logits = bf(c.vocab)
         self.k_cache = torch.zeros(c.layers, c.n_kv, max_len, c.head_dim, dtype=torch.bfloat16, device=device)
         self.v_cache = torch.zeros_like(self.k_cache)
@@ -124,46 +126,50 @@ class DecodeEngine:
         if weights.embed.scale is not None: raise NotImplementedError("fp8 embedding tables are not supported by the decode loop")
 
     # ---- one token, eager: every call below is one or two kernels of this library on the current stream ----
-    def _linear(self, w: NWCWeight, x, y):
-        err = L.lib.nwc_linear_x16(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(x), None,
-                                   L.ptr(w.scale), L.ptr(w.scratch), L.ptr(y), w.n, w.block, w.in_features, w.code)
-        if err: raise RuntimeError(f"nwc_linear_x16 error {err}")
-        self._count += 2 if self._needs_finalize(w) else 1
-
-    @staticmethod
-    def _needs_finalize(w):
-        rows = 16 if w.layout else 8
-        groups, cb = (w.out_features + rows - 1) // rows, (w.in_features + 511) // 512
-        return cb > 1 and groups < 2 * L.SM_COUNT * 16
+    def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None):
+        """y = W x with the activation prologue the mode names (0: x given; 1: x = RMSNorm(h_in + delta), h_out updated;
+        2: x = SwiGLU(gate_up)), through nwc_linear_fused."""
+        err = L.lib.nwc_linear_fused(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
+                                     L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), self.cfg.eps, L.ptr(gate_up), L.ptr(self.xtmp), None, L.ptr(w.scale),
+                                     L.ptr(w.scratch), L.ptr(y), w.n, w.block, w.in_features, w.code)
+        if err: raise RuntimeError(f"nwc_linear_fused error {err}")
+        self._count += L.lib.nwc_linear_launches(w.n, w.in_features, w.code, mode)
 
     def _check(self, err, what):
         if err: raise RuntimeError(f"{what} error {err}")
         self._count += 1
 
     def forward_token(self):
-        """Kernels of one decode step: reads self.cur / self.pos, leaves the greedy token in self.cur, advances pos."""
+        """Kernels of one decode step: reads self.cur / self.pos, leaves the greedy token in self.cur, advances pos.
+        The residual stream alternates between two buffers because the fused kernels read h while one CTA writes h + delta."""
         c, w, st = self.cfg, self.w, L.stream
         self._count = 0
         e = w.embed
-        self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(self.h),
+        h, h_next = self.h, self.h2
+        L.lib.nwc_set_dependent_launch(1 if self.dependent_launch else 0)
+        try:
+            self._forward(c, w, st, e, h, h_next)
+        finally:
+            L.lib.nwc_set_dependent_launch(0)
+        self.launches_per_step = self._count
+
+    def _forward(self, c, w, st, e, h, h_next):
+        self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(h),
                                      e.n, e.block, e.in_features, e.code), "nwc_gather")
         delta = None
         for i, l in enumerate(w.layers):
-            self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(self.h), L.ptr(delta), L.ptr(l["in_norm"]), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
-            self._linear(l["qkv"], self.xn, self.qkv)
+            self._linear(l["qkv"], None, self.qkv, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=l["in_norm"])
+            h, h_next = h_next, h
             self._check(L.lib.nwc_attention_decode(st(), L.ptr(self.qkv), L.ptr(l["q_norm"]), L.ptr(l["k_norm"]), L.ptr(self.cos), L.ptr(self.sin),
                                                    L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
                                                    c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
             self._linear(l["o"], self.attn, self.proj)
-            self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(self.h), L.ptr(self.proj), L.ptr(l["post_norm"]), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
-            self._linear(l["gate_up"], self.xn, self.gu)
-            self._check(L.lib.nwc_swiglu(st(), L.ptr(self.gu), c.intermediate, L.ptr(self.act), None), "nwc_swiglu")
-            self._linear(l["down"], self.act, self.proj)
-            delta = self.proj
-        self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(self.h), L.ptr(delta), L.ptr(w.final_norm), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
-        self._linear(w.lm_head, self.xn, self.logits)
+            self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, delta=self.proj, h_out=h_next, norm_w=l["post_norm"])
+            h, h_next = h_next, h
+            self._linear(l["down"], None, self.proj2, mode=2, gate_up=self.gu)
+            delta = self.proj2
+        self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=w.final_norm)
         self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits), c.vocab, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
-        self.launches_per_step = self._count
 
     # ---- graph ----
     def capture(self, warmup=3):

@@ -66,8 +66,10 @@ def test_teacher_forced_tokens_match_transformers(layout):
     assert agree >= (len(seq) - 1) - 4, (agree, ties)
 
 
-def test_graph_replay_equals_eager_and_step_api():
+@pytest.mark.parametrize("dependent", [False, True])
+def test_graph_replay_equals_eager_and_step_api(dependent):
     model, eng = build_pair(0)
+    eng.dependent_launch = dependent
     prompt = list(range(7, 19))
     eng.prefill(prompt)
     eager = eng.generate(24).tolist()
