@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--elem", default="bf16")
     ap.add_argument("--prompt", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"], help="N > 1: independent replicas (weak scaling) or tensor parallel with NCCL all-reduce (strong scaling)")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     return ap.parse_args()
 
@@ -139,10 +140,15 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
-    eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch))
+    tp = a.parallel == "tp" and world > 1
+    if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence
+        weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=0, tp_rank=rank, tp_world=world)
+        eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD)
+    else:
+        weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
+        eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch))
     eng.capture()
-    g = torch.Generator().manual_seed(1234 + rank)
+    g = torch.Generator().manual_seed(1234 + (0 if tp else rank))
     prompt = torch.randint(0, cfg.vocab, (a.prompt,), generator=g)
 
     def barrier():
@@ -204,10 +210,12 @@ def main():
         threads = os.cpu_count() or 1
         times, what = cpu_sample(cfg, a.layout, 1 if a.elem == "fp8" else 0, threads, repeats=2)
         cpu = {"value": 1.0 / min(times), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what}
-    line = {"metric": "decode_tokens_per_s", "value": world * a.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
-            "config": dict(workload(a, cfg), parallelism="replicas x%d (no data-path collective)" % world if world > 1 else "1 GPU"),
-            "e2e": {"value": world * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+    streams = 1 if tp else world          # sequences decoded at once
+    line = {"metric": "decode_tokens_per_s", "value": streams * a.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
+            "config": dict(workload(a, cfg), parallelism=("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, NCCL all-reduce after o and down" % world if tp
+                                                 else "replicas x%d (no data-path collective)" % world) if world > 1 else "1 GPU"),
+            "e2e": {"value": streams * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": a.steps * eng.launches_per_step, "launches_per_step": eng.launches_per_step,
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line))

@@ -13,6 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib as L
+from . import tp as TP
 from .weight import NWCWeight
 
 
@@ -54,28 +55,41 @@ class DecoderWeights:
     """Compressed matrices and norm vectors of a decoder.  `source(name, rows, cols)` returns the bf16 matrix to
     compress; `vector(name, n)` a bf16 norm weight."""
 
-    def __init__(self, cfg: DecoderConfig, source, vector, layout=0, elem="bf16", device="cuda"):
-        self.cfg = cfg
-        mk = lambda name, r, c, e=elem: NWCWeight(source(name, r, c), device, elem=e, layout=layout)
-        self.embed = mk("embed", cfg.vocab, cfg.hidden, "bf16" if not cfg.tied else elem)
-        self.lm_head = self.embed if cfg.tied else mk("lm_head", cfg.vocab, cfg.hidden)
+    def __init__(self, cfg: DecoderConfig, source, vector, layout=0, elem="bf16", device="cuda", tp_rank=0, tp_world=1):
+        """cfg is the FULL model; with tp_world > 1 `source` still returns full matrices and this rank keeps its shard."""
+        self.full_cfg, self.tp_rank, self.tp_world = cfg, tp_rank, tp_world
+        self.cfg = lc = TP.local_config(cfg, tp_world) if tp_world > 1 else cfg
+
+        def mk(name, kind, e=elem):
+            full = source(name, *TP.full_shape(kind, cfg))
+            part = TP.shard(kind, full, cfg, tp_rank, tp_world) if tp_world > 1 and kind != "embed" else full
+            return NWCWeight(part, device, elem=e, layout=layout)
+
+        if tp_world == 1:
+            self.embed = mk("embed", "embed", "bf16" if not cfg.tied else elem)
+            self.lm_head = self.embed if cfg.tied else mk("lm_head", "lm_head")
+        else:                       # the lookup needs every row, the logits only this rank's rows
+            self.embed = mk("embed", "embed", "bf16")
+            self.lm_head = mk("embed" if cfg.tied else "lm_head", "lm_head")
         self.layers = []
         for i in range(cfg.layers):
             self.layers.append({
                 "in_norm": vector(f"l{i}.in_norm", cfg.hidden), "post_norm": vector(f"l{i}.post_norm", cfg.hidden),
                 "q_norm": vector(f"l{i}.q_norm", cfg.head_dim) if cfg.qk_norm else None,
                 "k_norm": vector(f"l{i}.k_norm", cfg.head_dim) if cfg.qk_norm else None,
-                "qkv": mk(f"l{i}.qkv", cfg.qkv_rows, cfg.hidden), "o": mk(f"l{i}.o", cfg.hidden, cfg.n_q * cfg.head_dim),
-                "gate_up": mk(f"l{i}.gate_up", 2 * cfg.intermediate, cfg.hidden), "down": mk(f"l{i}.down", cfg.hidden, cfg.intermediate)})
+                "qkv": mk(f"l{i}.qkv", "qkv"), "o": mk(f"l{i}.o", "o"), "gate_up": mk(f"l{i}.gate_up", "gate_up"), "down": mk(f"l{i}.down", "down")})
         self.final_norm = vector("final_norm", cfg.hidden)
+        assert lc.qkv_rows == self.layers[0]["qkv"].out_features
 
     @classmethod
-    def synthetic(cls, cfg, layout=0, elem="bf16", device="cuda", seed=0):
-        counter = [seed * 100003]
+    def synthetic(cls, cfg, layout=0, elem="bf16", device="cuda", seed=0, tp_rank=0, tp_world=1):
+        """Seeded random-init model; every tensor has its own seed (derived from its name), so all ranks of a
+        tensor-parallel group generate the same full matrices and keep different shards."""
+        names = {}
         def source(name, r, c):
-            counter[0] += 1
-            return synthetic_matrix(r, c, counter[0], device)
-        return cls(cfg, source, lambda name, n: torch.ones(n, dtype=torch.bfloat16, device=device), layout, elem, device)
+            if name not in names: names[name] = len(names) + 1
+            return synthetic_matrix(r, c, seed * 100003 + names[name], device)
+        return cls(cfg, source, lambda name, n: torch.ones(n, dtype=torch.bfloat16, device=device), layout, elem, device, tp_rank, tp_world)
 
     def matrices(self):
         seen, out = set(), []
@@ -98,9 +112,12 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False):
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None):
+        """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None."""
         L.require_cuda()
         self.dependent_launch = bool(dependent_launch)
+        self.tp_group, self.tp_world = tp_group, weights.tp_world
+        if self.tp_world > 1 and tp_group is None: raise ValueError("sharded weights need the process group of their ranks")
         self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
         c = self.cfg
         bf = lambda n: torch.zeros(n, dtype=torch.bfloat16, device=device)
@@ -109,7 +126,8 @@ class DecodeEngine:
         self.xtmp = bf(pad32(max(c.hidden, c.intermediate)))
         self.qkv, self.attn, self.proj, self.proj2 = bf(c.qkv_rows), bf(pad32(c.n_q * c.head_dim)), bf(pad32(c.hidden)), bf(pad32(c.hidden))
         self.gu = bf(2 * c.intermediate)
-        self.logits = bf(c.vocab)
+        self.logits = bf(c.vocab)                                   # this rank's vocabulary rows
+        self.logits_all = bf(c.vocab * self.tp_world) if self.tp_world > 1 else self.logits
         self.k_cache = torch.zeros(c.layers, c.n_kv, max_len, c.head_dim, dtype=torch.bfloat16, device=device)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(c, max_len, device)
@@ -134,6 +152,13 @@ class DecodeEngine:
                                      L.ptr(w.scratch), L.ptr(y), w.n, w.block, w.in_features, w.code)
         if err: raise RuntimeError(f"nwc_linear_fused error {err}")
         self._count += L.lib.nwc_linear_launches(w.n, w.in_features, w.code, mode)
+
+    def _all_reduce(self, t):
+        """Sum the row-parallel partial outputs over the tensor-parallel ranks (one NCCL all-reduce over NVLink)."""
+        if self.tp_world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.tp_group)
+            self._count += 1
 
     def _check(self, err, what):
         if err: raise RuntimeError(f"{what} error {err}")
@@ -164,12 +189,18 @@ class DecodeEngine:
                                                    L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
                                                    c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
             self._linear(l["o"], self.attn, self.proj)
+            self._all_reduce(self.proj)
             self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, delta=self.proj, h_out=h_next, norm_w=l["post_norm"])
             h, h_next = h_next, h
             self._linear(l["down"], None, self.proj2, mode=2, gate_up=self.gu)
+            self._all_reduce(self.proj2)
             delta = self.proj2
         self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=w.final_norm)
-        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits), c.vocab, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
+        if self.tp_world > 1:                                        # vocabulary-sharded logits: gather, then every rank picks the same token
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.tp_group)
+            self._count += 1
+        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits_all), c.vocab * self.tp_world, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
 
     # ---- graph ----
     def capture(self, warmup=3):
