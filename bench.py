@@ -123,6 +123,22 @@ def workload(a, cfg):
 
 # ---------------------------------------------------------------------------------------------------------------------
 
+def trace(msg):
+    """Phase markers on stderr (NWC_BENCH_TRACE=1) for diagnosing a multi-rank run that stops."""
+    if os.environ.get("NWC_BENCH_TRACE"): print(f"[bench rank {os.environ.get('RANK', 0)}] {msg}", file=sys.stderr, flush=True)
+
+
+def finish(eng, dist):
+    """Orderly multi-rank exit: CUDA graphs that hold NCCL kernels are released before the communicator goes away."""
+    if dist is None: return
+    import gc
+    import torch
+    eng.graph = None
+    gc.collect(); torch.cuda.synchronize()
+    dist.barrier(); torch.cuda.synchronize()
+    dist.destroy_process_group()
+
+
 def main():
     a = parse()
     from nwc_b200.decode import PRESETS  # the package import fails loudly when the CUDA library is missing
@@ -138,16 +154,20 @@ def main():
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
+        import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     tp = a.parallel == "tp" and world > 1
+    if tp: a.dependent_launch = 0         # NCCL kernels sit in the chain: keep plain stream order around them
     if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=0, tp_rank=rank, tp_world=world)
         eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD)
     else:
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
         eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch))
+    trace("weights built")
     eng.capture()
+    trace("graph captured")
     g = torch.Generator().manual_seed(1234 + (0 if tp else rank))
     prompt = torch.randint(0, cfg.vocab, (a.prompt,), generator=g)
 
@@ -158,6 +178,7 @@ def main():
 
     # ---- value: K graph replays, device-timed ----
     eng.prefill(prompt)
+    trace("prefill done")
     for _ in range(a.warmup): eng._run()
     sampler = ClockSampler(local) if rank == 0 else None
     barrier()
@@ -167,6 +188,7 @@ def main():
     t1.record()
     barrier()
     ms = t0.elapsed_time(t1)
+    trace("timed region done")
     clocks = sampler.stop() if sampler else None
     if int(eng.status.item()): raise RuntimeError("decode position left the KV cache")
     # ---- e2e: host token in, host token out, every step ----
@@ -178,13 +200,15 @@ def main():
     for _ in range(a.steps): tok = eng.step(tok)
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - w0) * 1e3
+    trace("e2e done")
     if dist is not None:
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
-    if rank != 0:
-        if dist is not None: dist.destroy_process_group()
+    if rank != 0:                          # rank 0 alone measures the kernel roofline and the CPU baseline; the others wait for it
+        finish(eng, dist)
         return
+    trace("reduced over ranks")
     # ---- roofline of the dominant kernel: lm_head matvec back to back inside one graph ----
     peak, peak_kind = measured_peak()
     w = weights.lm_head
@@ -218,8 +242,8 @@ def main():
             "e2e": {"value": streams * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": a.steps * eng.launches_per_step, "launches_per_step": eng.launches_per_step,
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
-    print(json.dumps(line))
-    if dist is not None: dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    finish(eng, dist)
 
 
 if __name__ == "__main__":
