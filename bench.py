@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--elem", default="bf16")
     ap.add_argument("--prompt", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default="", help="time one token matvec alone: lm_head | qkv | o | gate_up | down | MxK (small case for ncu)")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"], help="N > 1: independent replicas (weak scaling) or tensor parallel with NCCL all-reduce (strong scaling)")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     return ap.parse_args()
@@ -128,6 +129,46 @@ def trace(msg):
     if os.environ.get("NWC_BENCH_TRACE"): print(f"[bench rank {os.environ.get('RANK', 0)}] {msg}", file=sys.stderr, flush=True)
 
 
+def kernel_only(a, cfg):
+    """The token matvec on synthetic matrices of one shape, back to back inside a CUDA graph over enough rotating copies
+    that no launch finds its matrix in L2.  Prints one JSON line with the roofline of one call."""
+    import torch
+    from nwc_b200 import NWCWeight, _lib as L
+    from nwc_b200.decode import synthetic_matrix
+    shapes = {"lm_head": (cfg.vocab, cfg.hidden), "qkv": (cfg.qkv_rows, cfg.hidden), "o": (cfg.hidden, cfg.n_q * cfg.head_dim),
+              "gate_up": (2 * cfg.intermediate, cfg.hidden), "down": (cfg.hidden, cfg.intermediate)}
+    M, K = shapes[a.kernel] if a.kernel in shapes else tuple(int(v) for v in a.kernel.lower().split("x"))
+    torch.cuda.set_device(0)
+    first = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
+    copies = max(1, min(64, -(-(320 << 20) // first.bytes)))          # rotate over > 320 MB so that no launch finds its matrix in L2
+    mats = [first] + [NWCWeight(synthetic_matrix(M, K, 1 + i), layout=a.layout, elem=a.elem) for i in range(1, copies)]
+    nw = first
+    x = torch.randn((K + 31) // 32 * 32, device="cuda").to(torch.bfloat16); x[K:] = 0
+    y = torch.empty(M, dtype=torch.bfloat16, device="cuda")
+    def launch(w):
+        err = L.lib.nwc_linear_x16(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(x), None, L.ptr(w.scale),
+                                   L.ptr(w.scratch), L.ptr(y), w.n, w.block, K, w.code)
+        if err: raise RuntimeError(f"nwc_linear_x16 error {err}")
+    reps = max(copies, 8)
+    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side): launch(nw)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(reps): launch(mats[i % copies])
+    times = []
+    for i in range(a.warmup + a.steps):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(); graph.replay(); t1.record(); torch.cuda.synchronize()
+        if i >= a.warmup: times.append(t0.elapsed_time(t1) / reps)
+    if L.lib.nwc_kernel_status(1): raise RuntimeError("a bounded wait inside a kernel gave up")
+    ms = statistics.median(times); peak, kind = measured_peak()
+    print(json.dumps({"kernel": f"token matvec {M}x{K} {a.elem} layout {a.layout}", "launches_per_call": L.lib.nwc_linear_launches(nw.n, K, nw.code, -1), "us_per_call": ms * 1e3,
+                      "bytes_per_call": nw.bytes, "bits_per_weight": 8 * nw.bytes / nw.n,
+                      "roofline": {"bound": "hbm", "achieved": nw.bytes / ms / 1e6, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": nw.bytes / ms / 1e6 / peak},
+                      "note": "%d calls on %d rotating copies replayed as one CUDA graph, CUDA events around the replay (a call includes its finalize launch when it needs one)" % (reps, copies)}))
+
+
 def finish(eng, dist):
     """Orderly multi-rank exit: CUDA graphs that hold NCCL kernels are released before the communicator goes away."""
     if dist is None: return
@@ -146,6 +187,9 @@ def main():
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if a.impl == "reference":
         if rank == 0: run_reference(a, cfg)
+        return
+    if a.kernel:
+        if rank == 0: kernel_only(a, cfg)
         return
     import torch
     from nwc_b200.decode import DecodeEngine, DecoderWeights
