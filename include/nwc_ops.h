@@ -133,6 +133,15 @@ int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, c
                      const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
                      uint32_t K, int elem);
 
+/* Prefill (T tokens at once): Y[t][m] = bf16(scale[m] * sum_k X[t][k] W[m][k] + bias[m]); X bf16 [T][ldx] (ldx a multiple
+   of 8, 16-byte aligned), Y bf16 [T][ldy].  W is decoded tile by tile into the shared-memory operands of a tcgen05 /
+   tensor-memory GEMM; no decompressed copy is written.  The reference dequantises into a temporary and calls a dense
+   matmul instead (nwc/nwc_torch.py:320-323).  Returns 0, -1 bad arguments, -2 when the element type / layout is not
+   covered by this path yet (layout 2 bf16 is), or a CUDA error. */
+int nwc_linear_prefill(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                       const uint8_t *low, const uint16_t *X, uint32_t T, uint32_t ldx, const uint16_t *bias,
+                       const float *scale, uint16_t *Y, uint32_t ldy, uint64_t n, uint32_t block, uint32_t K, int elem);
+
 /* Kernels one token-path call launches on the current device (for launch accounting): fused_mode -1 = nwc_linear_bf16 /
    nwc_linear_x16, 0..2 = nwc_linear_fused with that mode.  -1 on a bad shape or without a device. */
 int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_mode);

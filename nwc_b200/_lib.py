@@ -39,6 +39,7 @@ _SIGNATURES = {
     "nwc_linear_fused": (I, [P, P, P, P, P, P, I, P, P, P, P, P, ctypes.c_float, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_set_dependent_launch": (None, [I]),
     "nwc_linear_launches": (I, [U64, U32, I, I]),
+    "nwc_linear_prefill": (I, [P, P, P, P, P, P, P, U32, U32, P, P, P, U32, U64, U32, U32, I]),
     "nwc_attention_decode": (I, [P, P, P, P, P, P, P, P, P, U32, U32, U32, U32, ctypes.c_float, P, P]),
     "nwc_swiglu": (I, [P, P, U32, P, P]),
     "nwc_argmax": (I, [P, P, U32, P, P, P, P]),

@@ -172,6 +172,22 @@ NWC_EXPORT int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, c
 
 NWC_EXPORT int nwc_setup(void) { return device_sms(); }
 
-NWC_EXPORT int nwc_kernel_status(int clear) { return read_kernel_status(clear != 0); }
+NWC_EXPORT int nwc_kernel_status(int clear) {
+    const int a = read_kernel_status(clear != 0), b = read_prefill_status(clear != 0);
+    return a > b ? a : b;
+}
+
+/* Prefill: Y[T][ldy] = bf16(scale * (X[T][ldx] W^T) + bias) on the tcgen05 tensor cores, W decoded tile by tile.
+   Returns -2 for element types / layouts this path does not cover yet (the caller then dequantises and calls a matmul). */
+NWC_EXPORT int nwc_linear_prefill(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                                  const uint8_t *low, const uint16_t *X, uint32_t T, uint32_t ldx, const uint16_t *bias, const float *scale,
+                                  uint16_t *Y, uint32_t ldy, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    if (!shape_ok(n, block, K) || !T || ldx < K || ldy < n / K) return -1;
+    if (layout_of(elem) != 2 || type_of(elem) != kBf16) return -2;
+    if (!aligned16(data) || !aligned16(low) || !aligned16(lut) || !aligned16(X) || (ldx & 7u)) return -1;
+    if (!device_sms()) return (int)cudaErrorNoDevice;
+    SegmentArgs a{data, bases, hdr, lut, low, nullptr, nullptr, nullptr, bias, scale, nullptr, (uint32_t)(n / K), K, 1, 1, 0};
+    return (int)launch_prefill_layout2((cudaStream_t)stream, a, X, Y, T, ldx, ldy);
+}
 
 NWC_EXPORT void nwc_set_ring_kernels(int on) { set_ring_kernels(on != 0); }

@@ -49,6 +49,8 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
 void configure_segment_kernels();
 int count_token_launches(int code, int sms, uint32_t M, uint32_t K);
 
+cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy);
+int read_prefill_status(bool clear);
 cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids);
 cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);
 

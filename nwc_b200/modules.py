@@ -26,7 +26,10 @@ class NWCLinear(nn.Module):
         if x.numel() == self.in_features and x.dtype == torch.bfloat16:            # one token: fused kernel
             y = self.w.linear_bf16(x.contiguous().view(-1), None if self.bias is None else self.bias.data)
             return y.view(*x.shape[:-1], self.out_features)
-        if self.w.scale is None: return F.linear(x, self.w.dequant(), self.bias)    # prefill: temporary dequantisation
+        if x.dtype == torch.bfloat16:                                                # prefill: decode tile-wise into the tensor-core GEMM where covered
+            y = self.w.linear_prefill(x.reshape(-1, self.in_features), None if self.bias is None else self.bias.data)
+            if y is not None: return y.view(*x.shape[:-1], self.out_features)
+        if self.w.scale is None: return F.linear(x, self.w.dequant(), self.bias)    # otherwise: temporary dequantisation
         y = F.linear(x, self.w.dequant()).float() * self.w.scale                     # fp8: unscaled matmul, then the row scale
         if self.bias is not None: y = y + self.bias.float()
         return y.to(x.dtype)

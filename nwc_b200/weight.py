@@ -158,6 +158,20 @@ class NWCWeight:
         if err: raise RuntimeError(f"nwc_linear_bf16 error {err}")
         return y
 
+    def linear_prefill(self, x: torch.Tensor, bias=None):
+        """Many tokens at once: x bf16 [T, in] -> bf16 [T, out] on the tcgen05 GEMM with tile-wise decoding, or None when
+        this matrix's layout / element type is not covered by that path (the caller then dequantises)."""
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features: return None
+        T, K = x.shape
+        if K % 8: x = F.pad(x, (0, 8 - K % 8))
+        x = x.contiguous()
+        y = torch.empty(T, self.out_features, dtype=torch.bfloat16, device=x.device)
+        err = L.lib.nwc_linear_prefill(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low), L.ptr(x), T,
+                                       x.shape[1], L.ptr(bias), L.ptr(self.scale), L.ptr(y), self.out_features, self.n, self.block, self.in_features, self.code)
+        if err == -2: return None
+        if err: raise RuntimeError(f"nwc_linear_prefill error {err}")
+        return y
+
     def gather(self, ids: torch.Tensor) -> torch.Tensor:
         """Rows ids -> bf16[..., in] (embedding lookup straight from the compressed matrix)."""
         flat = ids.reshape(-1).to(device=self.data.device, dtype=torch.int64).contiguous()
