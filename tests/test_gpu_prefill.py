@@ -32,7 +32,7 @@ def test_prefill_matches_dequant_matmul(M, K, T):
     assert torch.equal(back.t().contiguous().view(torch.int16).cpu(), torch.from_numpy(values[:, : min(T, K)].view(np.int16).copy()))
     if finite:
         err = ((y.float() - ref).norm() / ref.norm()).item()
-        assert err <= 2e-3, err
+        assert err <= (2e-3 if M * T >= 1024 else 2.0 ** -8), err      # a handful of outputs: one bf16 rounding (half an ulp, up to 2^-8) can dominate the norm
         assert (y.float() - ref).abs().max().item() <= 2.0 ** -7 * ref.abs().max().item() + 1e-3
     # the same through the module: tokens batched -> prefill path, one token -> fused matvec; both agree with each other
     one = nw.linear_bf16(x[0], bias).float()
