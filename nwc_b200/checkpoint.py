@@ -119,6 +119,24 @@ def _materialize(model, name, value, device):
     else: raise KeyError(f"{name} is not a parameter or buffer of the model")
 
 
+def _rebuild_meta_buffers(model, hf_config, device):
+    """Buffers that checkpoints do not store (rotary inv_freq and the like) are still on the meta device after loading:
+    re-create the modules that own them from the config and take their freshly computed buffers."""
+    for path, mod in list(model.named_modules()):
+        names = [n for n, b in mod.named_buffers(recurse=False) if b.device.type == "meta"]
+        if not names: continue
+        fresh = None
+        for build in (lambda: type(mod)(config=hf_config, device="cpu"), lambda: type(mod)(config=hf_config), lambda: type(mod)(hf_config)):
+            try:
+                fresh = build(); break
+            except TypeError:
+                continue
+        if fresh is None: raise RuntimeError(f"buffer {path}.{names[0]} is not in the checkpoint and its module cannot be rebuilt from the config")
+        for n in names: mod._buffers[n] = dict(fresh.named_buffers(recurse=False))[n].detach().clone().to(device)
+        for k, v in vars(fresh).items():             # plain attributes computed next to the buffers (e.g. original_inv_freq)
+            if isinstance(v, torch.Tensor) and isinstance(getattr(mod, k, None), torch.Tensor) and getattr(mod, k).device.type == "meta": setattr(mod, k, v.to(device))
+
+
 def load_pretrained(path: str, device="cuda", verbose=True):
     """Load an NWC checkpoint: the model on `device` with NWC modules in place; no bf16 originals are ever created."""
     from transformers import AutoConfig, AutoModelForCausalLM
@@ -143,14 +161,7 @@ def load_pretrained(path: str, device="cuda", verbose=True):
             for i, (name, size) in enumerate(zip(m["names"], m["sizes"])):
                 _set(model, f"{m['path']}.{name}" if m["path"] else name, _FusedHead(shared, i, start, start + size)); start += size
     for k, v in tensors.items(): _materialize(model, k, v, device)
-    # buffers that are not stored in checkpoints (rotary inv_freq ...) are recomputed from the config on the device
-    fresh = None
-    for name, buf in list(model.named_buffers()):
-        if buf.device.type != "meta": continue
-        if fresh is None:
-            try: fresh = AutoModelForCausalLM.from_config(hf_config.__class__.from_dict({**hf_config.to_dict(), "num_hidden_layers": 1}), dtype=torch.bfloat16)
-            except TypeError: fresh = AutoModelForCausalLM.from_config(hf_config.__class__.from_dict({**hf_config.to_dict(), "num_hidden_layers": 1}), torch_dtype=torch.bfloat16)
-        _materialize(model, name, dict(fresh.named_buffers())[name].detach().clone(), device)
+    _rebuild_meta_buffers(model, hf_config, device)
     for n, p in model.named_parameters():
         if p.device.type == "meta": raise RuntimeError(f"parameter {n} missing in the checkpoint")
     model.to(device).eval()
