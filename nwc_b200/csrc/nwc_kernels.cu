@@ -292,9 +292,18 @@ __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geom
    falls inside a row group the warp writes bf16 y itself.
    Data path.  A stage holds kRingSlots slots of both planes (256 B of nibbles and 512 B of low bytes per slot, each slot
    lane-contiguous).  The warp keeps kRingStages stages in flight, so it never waits for HBM once the ring is full. */
-constexpr uint32_t kRingThreads = 1024, kRingSlots = 2, kRingStages = 4;
+#ifndef NWC_RING_SLOTS
+#define NWC_RING_SLOTS 3
+#define NWC_RING_STAGES 2
+#endif
+constexpr uint32_t kRingThreads = 1024, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES;
 constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
-constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes + kRingStages * 8u;
+constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes;
+constexpr uint32_t kRingBarrierBytes = (kRingThreads / 32u) * kRingStages * 8u;
+constexpr uint32_t kRingMaxSmem = 232448u;                       /* 227 KB opt-in limit of a CTA */
+/* shared memory of the layout-2 ring kernel: x (32 columns per slot, bf16), the barriers, then the per-warp rings */
+__host__ __device__ static inline uint32_t ring_x_bytes(const Geometry &g) { return (g.slots * 64u + 127u) & ~127u; }
+static inline uint32_t ring_smem_bytes(const Geometry &g) { return ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
 
 struct FlatPlan {
     uint32_t units_per_group;   /* slots (layout 2) or blocks (layouts 0, 1) per row group                              */
@@ -316,80 +325,178 @@ __device__ __forceinline__ void emit_flat(const SegmentArgs &a, const FlatPlan &
     a.y[row] = bf16_round(v);
 }
 
+/* Exceptions of one block (column block cb) for this lane: sum of value * x over the lane's `count` entries, split by
+   fragment half; `base` is the block's offset in `data`.  Called once per 16 slots, so it stays out of line to keep the
+   slot loop short. */
+__device__ __noinline__ float2 ring_exceptions(uint32_t count, uint32_t base, const uint8_t *__restrict__ data, uint32_t xs, uint32_t cb, uint32_t lane) {
+    float lo = 0.f, hi = 0.f;
+    uint32_t sum;
+    const uint32_t before = warp_exclusive_sum(count, lane, sum);
+    if (sum) {
+        const uint8_t *ep = data + base + (uint64_t)before * 3u;
+        for (uint32_t k = 0; k < count; k++, ep += 3) {
+            const uint32_t i = ep[0], jj = i & 15u, col = cb * kBlockCols + (i >> 4) * 32u + frag_col(lane, jj);
+            const float wv = __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
+            uint16_t xb;
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(xb) : "r"(xs + col * 2u));
+            const float xv = bf16_to_float(xb);
+            if ((jj >> 1) & 1u) hi = fmaf(wv, xv, hi); else lo = fmaf(wv, xv, lo);
+        }
+    }
+    return make_float2(lo, hi);
+}
+
+/* Shared memory behind the rings: what each warp contributes to row groups it shares with other warps of its CTA.
+   A warp's run is contiguous, so only its first and its last row group can be shared: entry 2 * warp is the first one
+   ("head"), entry 2 * warp + 1 the last one ("tail", used only when it differs from the head's group). */
+constexpr uint32_t kRingEntries = 2u * (kRingThreads / 32u);
+constexpr uint32_t kRingShareBytes = kRingEntries * 4u + kRingEntries * 16u * 4u;
+constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
+
 __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan) {
     extern __shared__ __align__(128) uint8_t ring_smem[];
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, r = lane >> 2, q = lane & 3u;
-    const uint32_t ring = smem_addr(ring_smem) + warp * kRingWarpBytes, bars = ring + kRingStages * kRingStageBytes;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Geometry g(a.M, a.K, 2);
-    const uint32_t w = warp * gridDim.x + blockIdx.x;           /* interleaved: a short plan still spreads over all SMs */
-    if (w >= plan.warps) return;
-    const uint64_t u0 = plan.start(w);
-    const uint32_t u1 = (uint32_t)plan.start(w + 1u), n_stage = (u1 - (uint32_t)u0 + kRingSlots - 1u) / kRingSlots;
-    if (lane == 0) { for (uint32_t b = 0; b < kRingStages; b++) mbar_init(bars + b * 8u, 1u); mbar_init_fence(); }
-    __syncwarp();
-    const uint8_t *nib_plane = a.low + u0 * 256u, *raw_plane = a.low + g.nibble_plane_bytes() + u0 * 512u;
-    auto issue = [&](uint32_t st) {                              /* lane 0: arm the barrier of stage st and start its two copies */
-        const uint32_t buf = st % kRingStages, first = st * kRingSlots, n = min(kRingSlots, u1 - (uint32_t)u0 - first);
-        const uint32_t bar = bars + buf * 8u, dst = ring + buf * kRingStageBytes;
-        mbar_expect(bar, n * 768u);
-        bulk_load(dst, nib_plane + (uint64_t)first * 256u, n * 256u, bar);
-        bulk_load(dst + kRingSlots * 256u, raw_plane + (uint64_t)first * 512u, n * 512u, bar);
-    };
-    if (lane == 0) for (uint32_t st = 0; st < min(n_stage, kRingStages); st++) issue(st);
+    const uint32_t xs = smem_addr(ring_smem), x_bytes = ring_x_bytes(g);
+    uint32_t *share_group = reinterpret_cast<uint32_t *>(ring_smem + x_bytes);
+    float *share_value = reinterpret_cast<float *>(ring_smem + x_bytes + kRingEntries * 4u);
+    const uint32_t bars = xs + x_bytes + kRingShareBytes + warp * (kRingStages * 8u);
+    const uint32_t ring = xs + x_bytes + kRingShareBytes + kRingBarrierBytes + warp * kRingWarpBytes;
+    /* the CTA's run of slots, then this warp's equal share of it */
+    const uint64_t c0 = plan.start(blockIdx.x), c1 = plan.start(blockIdx.x + 1u);
+    const uint32_t cn = (uint32_t)(c1 - c0), w0 = (uint32_t)((uint64_t)cn * warp / (kRingThreads / 32u)), w1 = (uint32_t)((uint64_t)cn * (warp + 1u) / (kRingThreads / 32u));
+    const uint64_t u0 = c0 + w0;
+    const uint32_t count = w1 - w0, n_stage = (count + kRingSlots - 1u) / kRingSlots;
+    const uint8_t *nib_next = a.low + u0 * 256u, *raw_next = a.low + g.nibble_plane_bytes() + u0 * 512u;
+    uint32_t left = count;                                       /* slots not yet requested */
+    if (lane == 0) {
+        for (uint32_t b = 0; b < kRingStages; b++) mbar_init(bars + b * 8u, 1u);
+        mbar_init_fence();
+        for (uint32_t b = 0; b < kRingStages && left; b++) {     /* fill the ring before anything else */
+            const uint32_t n = min(kRingSlots, left), dst = ring + b * kRingStageBytes;
+            mbar_expect(bars + b * 8u, n * 768u);
+            bulk_load(dst, nib_next, n * 256u, bars + b * 8u);
+            bulk_load(dst + kRingSlots * 256u, raw_next, n * 512u, bars + b * 8u);
+            nib_next += n * 256u; raw_next += n * 512u; left -= n;
+        }
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     FixedTables t; t.load(a.lut);
-    uint32_t rb = (uint32_t)(u0 / g.slots), s = (uint32_t)(u0 - (uint64_t)rb * g.slots);      /* row group and slot inside it */
+    const uint32_t slots = g.slots;
+    uint32_t rb = (uint32_t)(u0 / slots), s = (uint32_t)(u0 - (uint64_t)rb * slots);      /* row group and slot inside it */
+    /* exception count of this lane and data offset of the next block to start in this run, fetched one block ahead */
+    uint32_t next_block = rb * g.CB + ((s + 15u) >> 4), next_count = 0, next_base = 0;
+    if (next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
+    /* The weights do not depend on the kernel before this one, x does.  x goes into shared memory, zero beyond K16
+       (the last slot may cover 16 columns more). */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t i = threadIdx.x * 16u; i < x_bytes; i += kRingThreads * 16u) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (i < g.K16 * 2u) v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(a.x) + i));
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xs + i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+    if (threadIdx.x < kRingEntries) share_group[threadIdx.x] = kNoGroup;
+    __syncthreads();
+    const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * 16u, xq = xs + (lane & 3u) * 16u;
+    uint32_t seg_first = s, entry = 2u * warp;                   /* first slot of the current segment; where a shared one goes */
     float d[4] = {0.f, 0.f, 0.f, 0.f}, ex_lo = 0.f, ex_hi = 0.f;
-    auto flush = [&]() {                                         /* the warp's share of row group rb is complete */
+    /* the segment [seg_first, s) of row group rb is complete */
+    auto flush = [&]() {
         ex_lo += __shfl_xor_sync(0xffffffffu, ex_lo, 1); ex_lo += __shfl_xor_sync(0xffffffffu, ex_lo, 2);
         ex_hi += __shfl_xor_sync(0xffffffffu, ex_hi, 1); ex_hi += __shfl_xor_sync(0xffffffffu, ex_hi, 2);
-        if (q == 0u) {
-            const uint32_t part = w - plan.owner((uint64_t)rb * g.slots);
-            emit_flat(a, plan, rb * 16u + r, part, d[0] + ex_lo); emit_flat(a, plan, rb * 16u + r + 8u, part, d[2] + ex_hi);
+        const float lo = d[0] + ex_lo, hi = d[2] + ex_hi;
+        const uint32_t r = lane >> 2;
+        if (seg_first == 0u && s == slots) {                     /* a whole row group: nobody else adds to it */
+            if ((lane & 3u) == 0u) {
+                const uint32_t part = blockIdx.x - plan.owner((uint64_t)rb * slots);
+                emit_flat(a, plan, rb * 16u + r, part, lo); emit_flat(a, plan, rb * 16u + r + 8u, part, hi);
+            }
+        } else {
+            if ((lane & 3u) == 0u) { share_value[entry * 16u + r] = lo; share_value[entry * 16u + r + 8u] = hi; }
+            if (lane == 0) share_group[entry] = rb;
+            entry = 2u * warp + 1u;
         }
         d[0] = d[1] = d[2] = d[3] = 0.f; ex_lo = ex_hi = 0.f;
     };
-    uint32_t phase_bits = 0;
+    uint32_t buf = 0, parity = 0, todo = count;
+#pragma unroll 1
     for (uint32_t st = 0; st < n_stage; st++) {
-        const uint32_t buf = st % kRingStages, bar = bars + buf * 8u, src = ring + buf * kRingStageBytes;
-        if (!mbar_wait(bar, (phase_bits >> buf) & 1u)) {         /* gave up: let copies already issued land, then leave */
-            for (uint32_t b = 0; b < kRingStages; b++) for (uint32_t i = 0; i < 64u && !mbar_poll(bars + b * 8u, (phase_bits >> b) & 1u); i++) {}
-            return;
+        const uint32_t bar = bars + buf * 8u, src = ring + buf * kRingStageBytes;
+        if (!mbar_wait(bar, parity)) {                           /* gave up (status word set): let copies already issued land, then stop */
+            for (uint32_t b = 0; b < kRingStages; b++) for (uint32_t i = 0; i < 64u && !mbar_poll(bars + b * 8u, parity ^ (b < buf ? 1u : 0u)); i++) {}
+            break;
         }
-        phase_bits ^= 1u << buf;
-        const uint32_t n = min(kRingSlots, u1 - (uint32_t)u0 - st * kRingSlots);
+        /* one slot: 16 weights per lane against 32 columns of x */
+        auto slot = [&](uint32_t j, uint32_t column_slot) {
+            const uint2 nib = lds64(src + j * 256u + lane8);
+            const uint4 raw = lds128(src + j * 512u + lane16);
+            const uint4 xv = lds128(xq + column_slot * 64u);
+            uint32_t a0, a1, a2, a3;
+            fixed_half<kBf16, 0>(t, nib.x, raw.x, raw.y, 0u, 0u, 0u, a0, a1, a2, a3);
+            mma_bf16(d, a0, a1, a2, a3, xv.x, xv.y);
+            fixed_half<kBf16, 2>(t, nib.y, raw.z, raw.w, 0u, 0u, 0u, a0, a1, a2, a3);
+            mma_bf16(d, a0, a1, a2, a3, xv.z, xv.w);
+        };
+        /* the block whose first slot is f starts here: this warp adds the block's exceptions */
+        auto exceptions = [&](uint32_t f) {
+#ifdef NWC_KO_EXC
+            const float2 e = make_float2(0.f, 0.f);
+#else
+            const float2 e = ring_exceptions(next_count, next_base, a.data, xs, f >> 4, lane);
+#endif
+            ex_lo += e.x; ex_hi += e.y;
+            if (++next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
+        };
+        if (todo >= kRingSlots && s + kRingSlots <= slots) {     /* a full stage inside one row group: no per-slot checks */
 #pragma unroll
-        for (uint32_t j = 0; j < kRingSlots; j++) {
-            if (j < n) {
-                const uint2 nib = lds64(src + j * 256u + lane * 8u);
-                const uint4 raw = lds128(src + kRingSlots * 256u + j * 512u + lane * 16u);
-                if ((s & 15u) == 0u) {                           /* first slot of a block: this warp adds the block's exceptions */
-                    const uint32_t cb = s >> 4, b = rb * g.CB + cb;
-                    uint32_t sum;
-                    const uint32_t count = __ldg(a.hdr + (uint64_t)b * kLanes + lane), before = warp_exclusive_sum(count, lane, sum);
-                    if (sum) {
-                        const uint8_t *ep = a.data + __ldg(a.bases + b) + (uint64_t)before * 3u;
-                        for (uint32_t k = 0; k < count; k++, ep += 3) {
-                            const uint32_t i = ep[0], jj = i & 15u, col = cb * kBlockCols + (i >> 4) * 32u + frag_col(lane, jj);
-                            const float wv = __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
-                            const float xv = bf16_to_float(__ldg(static_cast<const uint16_t *>(a.x) + col));
-                            if ((jj >> 1) & 1u) ex_hi = fmaf(wv, xv, ex_hi); else ex_lo = fmaf(wv, xv, ex_lo);
-                        }
-                    }
-                }
-                fixed_super_chunk<kBf16, kModeLinear, false, 0>(a, g, t, nib, raw, 0u, 0u, 0u, rb * 16u, r, s * 32u + 8u * q, d);
-                if (++s == g.slots) { flush(); s = 0; rb++; }
+            for (uint32_t j = 0; j < kRingSlots; j++) slot(j, s + j);
+            const uint32_t to_block = (0u - s) & 15u;            /* slots from s to the next first slot of a block */
+            if (to_block < kRingSlots) exceptions(s + to_block);
+            s += kRingSlots;
+            if (s == slots) { flush(); s = 0; seg_first = 0; rb++; }
+        } else {
+            const uint32_t n = min(todo, kRingSlots);
+#pragma unroll 1
+            for (uint32_t j = 0; j < n; j++) {
+                slot(j, s);
+                if ((s & 15u) == 0u) exceptions(s);
+                if (++s == slots) { flush(); s = 0; seg_first = 0; rb++; }
             }
         }
+        todo -= min(todo, kRingSlots);
         __syncwarp();
-        if (lane == 0 && st + kRingStages < n_stage) { async_proxy_fence(); issue(st + kRingStages); }
+        if (lane == 0 && left) {                                 /* refill the stage just read */
+            const uint32_t n = min(kRingSlots, left);
+            async_proxy_fence();
+            mbar_expect(bar, n * 768u);
+            bulk_load(src, nib_next, n * 256u, bar);
+            bulk_load(src + kRingSlots * 256u, raw_next, n * 512u, bar);
+            nib_next += n * 256u; raw_next += n * 512u; left -= n;
+        }
+        if (++buf == kRingStages) { buf = 0; parity ^= 1u; }
     }
-    if (s != 0u) flush();
+    if (s != seg_first) flush();
+    __syncthreads();
+    /* Shared row groups: entries of one group are adjacent in entry order.  The first entry of each group adds the
+       others in that order (so the sum does not depend on timing) and writes the CTA's value for the group. */
+    {
+        const uint32_t e = threadIdx.x >> 4, row = threadIdx.x & 15u, grp = share_group[e];
+        if (grp == kNoGroup) return;
+        for (uint32_t p = e; p-- > 0u;) { const uint32_t gp = share_group[p]; if (gp == grp) return; if (gp != kNoGroup) break; }
+        float v = share_value[e * 16u + row];
+        for (uint32_t n = e + 1u; n < kRingEntries; n++) {
+            const uint32_t gn = share_group[n];
+            if (gn == grp) v += share_value[n * 16u + row]; else if (gn != kNoGroup) break;
+        }
+        emit_flat(a, plan, grp * 16u + row, blockIdx.x - plan.owner((uint64_t)grp * slots), v);
+    }
 }
 
 /* y[i] = bf16((sum of the partials of the warps that shared row i's row group, in warp order) * scale[i] + bias[i]) */
 __global__ void finalize_flat_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ bias, const float *__restrict__ scale,
                                      uint16_t *__restrict__ y, uint32_t M, uint32_t rows, const FlatPlan plan) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (i >= M) return;
     const uint64_t first_unit = (uint64_t)(i / rows) * plan.units_per_group;
     const uint32_t n = plan.owner(first_unit + plan.units_per_group - 1u) - plan.owner(first_unit) + 1u;
@@ -403,10 +510,10 @@ __global__ void finalize_flat_kernel(const float *__restrict__ partial, const ui
 /* Equal contiguous runs (they differ by at most one grain) for up to `warps` warps.  Fewer warps take part when the
    warps that could share one row group would not fit the caller's scratch (CB floats per row); with a single column
    block no row group may be cut at all. */
-static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t warps, FlatPlan &p) {
+static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t warps, FlatPlan &p, bool whole_groups = false) {
     const uint64_t total = (uint64_t)g.groups * units_per_group;
     p.units_per_group = units_per_group;
-    p.grain = g.CB == 1u ? units_per_group : 1u;
+    p.grain = g.CB == 1u || whole_groups ? units_per_group : 1u;
     p.chunks = (uint32_t)(total / p.grain);
     uint64_t use = warps < p.chunks ? warps : p.chunks;
     if (p.grain == 1u && g.CB > 1u) {
@@ -417,6 +524,20 @@ static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t
     p.direct = p.grain % units_per_group == 0u ? 1u : 0u;
     p.parts = p.direct ? 1u : (uint32_t)((units_per_group - 1u) / (total / use)) + 2u;
     if (p.parts > g.CB) p.parts = g.CB;                                        /* bound above guarantees the true count fits */
+}
+
+/* Layout 2: the plan's "warps" are CTAs (the 32 warps of a CTA split its run evenly and add up in shared memory).
+   Whole row groups per CTA need no second launch but leave some CTAs one group short; equal runs of slots keep every
+   CTA busy to the end but need the finalize launch; measured on B200 that second launch and its kernel boundary cost
+   4 to 5 us, the time one CTA streams about kFinalizeSlots slots. */
+#ifndef NWC_FINALIZE_SLOTS
+#define NWC_FINALIZE_SLOTS 256
+#endif
+constexpr uint64_t kFinalizeSlots = NWC_FINALIZE_SLOTS;
+static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p) {
+    const uint64_t total = (uint64_t)g.groups * g.slots, ctas = (uint64_t)sms;
+    const uint64_t whole = ((g.groups + ctas - 1u) / ctas) * g.slots, cut = (total + ctas - 1u) / ctas + kFinalizeSlots;
+    make_flat_plan(g, g.slots, ctas, p, whole <= cut);
 }
 
 /* ---- layouts 0 and 1, token path: lane streams staged in shared memory by bulk copies -------------------------------- */
@@ -857,7 +978,7 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K) {
     const Geometry g(M, K, layout);
     FlatPlan plan;
     if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
-    if (!g_disable_ring && layout == 2 && elem == kBf16) { make_flat_plan(g, g.slots, (uint64_t)sms * (kRingThreads / 32u), plan); return plan.direct ? 1 : 2; }
+    if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { make_cta_plan_layout2(g, sms, plan); return plan.direct ? 1 : 2; }
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
@@ -885,15 +1006,11 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
         }
         return err;
     }
-    if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
-        make_flat_plan(g, g.slots, (uint64_t)sms * (kRingThreads / 32u), plan);
-        const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
-        ring_kernel_layout2<<<rgrid, kRingThreads, (kRingThreads / 32u) * kRingWarpBytes, st>>>(a, plan);
-        err = cudaGetLastError();
-        if (err == cudaSuccess && !plan.direct) {
-            finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
-            err = cudaGetLastError();
-        }
+    if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_smem_bytes(g) <= kRingMaxSmem) {
+        make_cta_plan_layout2(g, sms, plan);
+        err = launch_kernel(ring_kernel_layout2, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g), st, a, plan);
+        if (err == cudaSuccess && !plan.direct)
+            err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
     }
     if (layout == 0) err = elem == kFp8 ? launch_modes<0, kFp8>(mode, grid, smem, st, a) : launch_modes<0, kBf16>(mode, grid, smem, st, a);
@@ -918,7 +1035,7 @@ static void opt_in_smem() {
 void configure_segment_kernels() {
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((kRingThreads / 32u) * kRingWarpBytes));
+    cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
