@@ -105,7 +105,8 @@ NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_
     if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1 || mode < 0 || mode > 2) return -1;
     if (!aligned16(data) || !aligned16(low) || !aligned16(lut)) return -1;
     if (mode == kInputNorm && (!h_in || !norm_w || h_out == h_in)) return -1;
-    if (mode == kInputSwiglu && !gate_up) return -1;
+    if (mode == kInputNorm && (!aligned16(h_in) || !aligned16(delta) || !aligned16(h_out) || !aligned16(norm_w))) return -1;   /* read as 16-byte vectors */
+    if (mode == kInputSwiglu && (!gate_up || !aligned16(gate_up))) return -1;
     if (mode == kInputPlain && (!x || !aligned16(x))) return -1;
     const int sms = device_sms();
     if (!sms) return (int)cudaErrorNoDevice;

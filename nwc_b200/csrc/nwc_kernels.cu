@@ -756,8 +756,14 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
    Everything that does not depend on the previous kernel (table staging) runs before griddepcontrol.wait, so with
    programmatic dependent launch it overlaps the predecessor's tail. */
 constexpr uint32_t kSmallThreads = 256, kSmallWarps = kSmallThreads / 32u;
+/* warps that share one row group: the smallest power of two that covers its column blocks (at most the CTA) */
+__host__ __device__ static inline uint32_t small_group_warps(uint32_t CB) { return CB > 4u ? 8u : (CB > 2u ? 4u : (CB > 1u ? 2u : 1u)); }
 
 __device__ __forceinline__ float bf16_rt(float v) { return bf16_to_float(bf16_round_nan(v)); }
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) { return (uint32_t)bf16_round_nan(lo) | ((uint32_t)bf16_round_nan(hi) << 16); }
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) { asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
 
 template <int ELEM>
 __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
@@ -767,17 +773,18 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
     float *stash_all = reinterpret_cast<float *>(small_smem + 16416u);                 /* [8 warps][64] */
     float *red = stash_all + kSmallWarps * 64u;                                         /* [8 warps][8 rows] */
     float *scal = red + kSmallWarps * 8u;                                               /* [8] block reduction scratch */
-    uint8_t *stage_all = reinterpret_cast<uint8_t *>(scal + 8u);                        /* [8 warps][kPrefixStageBytes] lane streams of one block */
-    uint64_t *bar_all = reinterpret_cast<uint64_t *>(stage_all + kSmallWarps * kPrefixStageBytes);
-    uint16_t *xs = reinterpret_cast<uint16_t *>(bar_all + kSmallWarps);
+    uint8_t *stage_all = reinterpret_cast<uint8_t *>(scal + 8u);                        /* [8 warps][2][kPrefixStageBytes] lane streams of a block */
+    uint64_t *bar_all = reinterpret_cast<uint64_t *>(stage_all + kSmallWarps * 2u * kPrefixStageBytes);
+    uint16_t *xs = reinterpret_cast<uint16_t *>(bar_all + 2u * kSmallWarps);            /* [K16] activation vector */
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, tid = threadIdx.x;
     const Geometry g(a.M, a.K, 0);
-    const uint32_t stage = smem_addr(stage_all) + warp * kPrefixStageBytes, bar = smem_addr(bar_all) + warp * 8u;
-    if (lane == 0) { mbar_init(bar, 1u); mbar_init_fence(); }
+    uint16_t *nw = xs + g.K16;                                                         /* [K16] RMSNorm weight (kInputNorm only) */
+    const uint32_t stage0 = smem_addr(stage_all) + warp * 2u * kPrefixStageBytes, bar0 = smem_addr(bar_all) + warp * 16u;
+    if (lane == 0) { mbar_init(bar0, 1u); mbar_init(bar0 + 8u, 1u); mbar_init_fence(); }
     __syncwarp();
-    /* byte span of block b inside data, rounded out to 16 bytes, and the bulk copy of it into this warp's stage;
-       returns 0 (no copy) when the stream does not fit the stage */
-    auto fetch = [&](uint32_t b, uint32_t words_of_b, uint32_t &start) -> uint32_t {
+    /* byte span of block b inside data, rounded out to 16 bytes, and the bulk copy of it into stage `which` of this
+       warp; returns 0 (no copy) when the stream does not fit the stage */
+    auto fetch = [&](uint32_t b, uint32_t words_of_b, uint32_t which, uint32_t &start) -> uint32_t {
         const uint32_t base = __ldg(a.bases + b);
         uint32_t len;
         if (b + 1u < g.nb) len = __ldg(a.bases + b + 1u) - base;
@@ -785,30 +792,80 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
         start = base & ~15u;
         uint32_t bytes = (base + len + 16u - start + 15u) & ~15u;
         if (bytes > kPrefixStageBytes) bytes = 0u;
-        if (bytes && lane == 0) { async_proxy_fence(); mbar_expect(bar, bytes); bulk_load(stage, a.data + start, bytes, bar); }
+        if (bytes && lane == 0) { async_proxy_fence(); mbar_expect(bar0 + 8u * which, bytes); bulk_load(stage0 + which * kPrefixStageBytes, a.data + start, bytes, bar0 + 8u * which); }
         return bytes;
     };
-    /* warps per row group and row groups per CTA pass */
-    const uint32_t wg = g.CB >= kSmallWarps ? kSmallWarps : (g.CB >= 4u ? 4u : (g.CB >= 2u ? 2u : 1u)), per_pass = kSmallWarps / wg;
+    /* warps per row group and row groups per CTA pass; warp j of a row group takes column blocks j, j + wg, ... */
+    const uint32_t wg = small_group_warps(g.CB), per_pass = kSmallWarps / wg;
     const uint32_t my_group = warp / wg, j = warp - my_group * wg, passes = (g.groups + per_pass - 1u) / per_pass;
+    /* this warp's blocks in the order it decodes them: (pass, cb) -> the next one, false after the last */
+    auto settle = [&](uint32_t &pass, uint32_t &cb) -> bool {
+        while (pass < passes) {
+            if (pass * per_pass + my_group < g.groups && cb < g.CB) return true;
+            pass += gridDim.x; cb = j;
+        }
+        return false;
+    };
+    /* the stream of the block after the current one is always in flight: issued before the current block is decoded */
+    struct Ahead { uint32_t pass, cb, b, words, start, bytes; bool valid; } next;
+    auto prefetch_block = [&](uint32_t pass, uint32_t cb, uint32_t which) {
+        next.pass = pass; next.cb = cb; next.valid = settle(next.pass, next.cb);
+        if (!next.valid) return;
+        const uint32_t rb = next.pass * per_pass + my_group;
+        next.b = rb * g.CB + next.cb;
+        next.words = __ldg(a.hdr + (uint64_t)next.b * kLanes + lane);
+        next.bytes = fetch(next.b, next.words, which, next.start);
+        const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16, row = rb * 8u + (lane >> 2), off = next.cb * (ELEM == kFp8 ? 256u : 512u) + (lane & 3u) * 128u;
+        if (row < g.M && off < stride) prefetch_l2(a.low + (uint64_t)row * stride + off);
+    };
     /* the weights do not depend on the kernel before this one: start the copy of this warp's first stream and pull its
        raw rows towards L2 before anything else, so that both overlap the table staging, the wait and the prologue */
-    uint32_t first_b = 0xFFFFFFFFu, first_words = 0u, first_start = 0u, first_bytes = 0u;
-    {
-        const uint32_t rb = blockIdx.x * per_pass + my_group;
-        if (rb < g.groups && j < g.CB) {
-            first_b = rb * g.CB + j;
-            first_words = __ldg(a.hdr + (uint64_t)first_b * kLanes + lane);
-            first_bytes = fetch(first_b, first_words, first_start);
-            const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16, row = rb * 8u + (lane >> 2), off = j * (ELEM == kFp8 ? 256u : 512u) + (lane & 3u) * 128u;
-            if (row < g.M && off < stride) prefetch_l2(a.low + (uint64_t)row * stride + off);
-        }
-    }
+    prefetch_block(blockIdx.x, j, 0u);
     stage_tables(tables, a.lut, tid, kSmallThreads);
+    const uint32_t xs_addr = smem_addr(xs), nw_addr = smem_addr(nw), chunks = g.K16 >> 3, live = a.K >> 3;   /* chunks of eight values */
+    const bool vec = (a.K & 7u) == 0u;
+    if (in.mode == kInputNorm && vec)
+        for (uint32_t c = tid; c < live; c += kSmallThreads) sts128(nw_addr + c * 16u, __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c));
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     /* ---- activation vector -> shared memory (bf16, zero beyond K) ---- */
-    if (in.mode == kInputNorm) {
+    if (in.mode == kInputNorm && vec) {
+        float ss = 0.f;
+        for (uint32_t c = tid; c < chunks; c += kSmallThreads) {
+            uint4 o = make_uint4(0u, 0u, 0u, 0u);
+            if (c < live) {
+                const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
+                const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+                uint32_t dw[4] = {0u, 0u, 0u, 0u}, ow[4];
+                if (in.delta) { const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c); dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w; }
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    float v0 = bf16_lo(hw[k]), v1 = bf16_hi(hw[k]);
+                    if (in.delta) { v0 = bf16_rt(v0 + bf16_lo(dw[k])); v1 = bf16_rt(v1 + bf16_hi(dw[k])); }
+                    ss += v0 * v0; ss += v1 * v1;
+                    ow[k] = bf16_pack(v0, v1);
+                }
+                o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                if (blockIdx.x == 0 && in.h_out) *(reinterpret_cast<uint4 *>(in.h_out) + c) = o;
+            }
+            sts128(xs_addr + c * 16u, o);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) scal[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (uint32_t i = 0; i < kSmallWarps; i++) tot += scal[i];
+        const float inv = rsqrtf(tot / (float)a.K + in.eps);
+        for (uint32_t c = tid; c < live; c += kSmallThreads) {
+            const uint4 v = lds128(xs_addr + c * 16u), w = lds128(nw_addr + c * 16u);
+            const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, ww[4] = {w.x, w.y, w.z, w.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) ow[k] = bf16_pack(bf16_lo(ww[k]) * bf16_rt(bf16_lo(vw[k]) * inv), bf16_hi(ww[k]) * bf16_rt(bf16_hi(vw[k]) * inv));
+            sts128(xs_addr + c * 16u, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+    } else if (in.mode == kInputNorm) {
         float ss = 0.f;
         for (uint32_t i = tid; i < a.K; i += kSmallThreads) {
             float v = bf16_to_float(in.h_in[i]);
@@ -826,34 +883,54 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
         const float inv = rsqrtf(tot / (float)a.K + in.eps);
         for (uint32_t i = tid; i < g.K16; i += kSmallThreads)
             xs[i] = i < a.K ? bf16_round_nan(bf16_to_float(in.norm_w[i]) * bf16_rt(bf16_to_float(xs[i]) * inv)) : (uint16_t)0;
+    } else if (in.mode == kInputSwiglu && vec) {
+        const uint4 *gate = reinterpret_cast<const uint4 *>(in.gate_up), *up = reinterpret_cast<const uint4 *>(in.gate_up + a.K);
+#pragma unroll 2
+        for (uint32_t c = tid; c < chunks; c += kSmallThreads) {
+            uint4 o = make_uint4(0u, 0u, 0u, 0u);
+            if (c < live) {
+                const uint4 gv = gate[c], uv = up[c];
+                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float g0 = bf16_lo(gw[k]), g1 = bf16_hi(gw[k]);
+                    ow[k] = bf16_pack(bf16_rt(g0 / (1.f + __expf(-g0))) * bf16_lo(uw[k]), bf16_rt(g1 / (1.f + __expf(-g1))) * bf16_hi(uw[k]));
+                }
+                o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+            sts128(xs_addr + c * 16u, o);
+        }
     } else if (in.mode == kInputSwiglu) {
         for (uint32_t i = tid; i < g.K16; i += kSmallThreads) {
             uint16_t v = 0;
             if (i < a.K) { const float gt = bf16_to_float(in.gate_up[i]), up = bf16_to_float(in.gate_up[a.K + i]); v = bf16_round_nan(bf16_rt(gt / (1.f + __expf(-gt))) * up); }
             xs[i] = v;
         }
+    } else if (vec) {
+        for (uint32_t c = tid; c < chunks; c += kSmallThreads)
+            sts128(xs_addr + c * 16u, c < live ? *(reinterpret_cast<const uint4 *>(a.x) + c) : make_uint4(0u, 0u, 0u, 0u));
     } else {
         for (uint32_t i = tid; i < g.K16; i += kSmallThreads) xs[i] = i < a.K ? static_cast<const uint16_t *>(a.x)[i] : (uint16_t)0;
     }
     __syncthreads();
-    const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords, xs_addr = smem_addr(xs);
+    const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords;
     float *stash = stash_all + warp * 64u;
-    uint32_t phase = 0;
+    uint32_t phases = 0, which = 0;                              /* parity per stage; the stage that holds the current block */
     for (uint32_t pass = blockIdx.x; pass < passes; pass += gridDim.x) {
         const uint32_t rb = pass * per_pass + my_group;
         float row_sum = 0.f;
         if (rb < g.groups) {
             for (uint32_t cb = j; cb < g.CB; cb += wg) {
-                const uint32_t b = rb * g.CB + cb;
-                uint32_t words, start, bytes, total;
-                if (b == first_b) { words = first_words; start = first_start; bytes = first_bytes; }
-                else { words = __ldg(a.hdr + (uint64_t)b * kLanes + lane); bytes = fetch(b, words, start); }
-                const uint32_t before = warp_exclusive_sum(words, lane, total), base = __ldg(a.bases + b);
-                if (bytes) {
-                    const bool landed = mbar_wait(bar, phase);    /* on a timeout the status word is set and the block is skipped; the CTA's barriers below still need this warp */
-                    phase ^= 1u;
+                const Ahead cur = next;                           /* by construction (pass, cb) == (cur.pass, cur.cb) */
+                prefetch_block(pass, cb + wg, which ^ 1u);
+                uint32_t total;
+                const uint32_t before = warp_exclusive_sum(cur.words, lane, total), base = __ldg(a.bases + cur.b);
+                if (cur.bytes) {
+                    const bool landed = mbar_wait(bar0 + 8u * which, (phases >> which) & 1u);    /* on a timeout the status word is set and the block is skipped; the CTA's barriers below still need this warp */
+                    phases ^= 1u << which;
                     if (landed) {
-                        SmemWindow<MR> W; W.open(stage + (base - start) + 4u * before);
+                        SmemWindow<MR> W; W.open(stage0 + which * kPrefixStageBytes + (base - cur.start) + 4u * before);
                         row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, false>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
                     }
                 } else {
@@ -861,6 +938,7 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
                     W.open(reinterpret_cast<const uint32_t *>(a.data + base) + before);
                     row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, false>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
                 }
+                which ^= 1u;
             }
         }
         if (lane < 8u) red[warp * 8u + lane] = row_sum;
@@ -943,13 +1021,13 @@ static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 bloc
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
-constexpr uint32_t kSmallFixedSmem = 16416u + kSmallWarps * 64u * 4u + kSmallWarps * 8u * 4u + 32u + kSmallWarps * kPrefixStageBytes + kSmallWarps * 8u;
+constexpr uint32_t kSmallFixedSmem = 16416u + kSmallWarps * 64u * 4u + kSmallWarps * 8u * 4u + 32u + kSmallWarps * 2u * kPrefixStageBytes + kSmallWarps * 16u;
 cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in) {
     const Geometry g(a.M, a.K, 0);
-    const uint32_t wg = g.CB >= kSmallWarps ? kSmallWarps : (g.CB >= 4u ? 4u : (g.CB >= 2u ? 2u : 1u)), per_pass = kSmallWarps / wg;
+    const uint32_t wg = small_group_warps(g.CB), per_pass = kSmallWarps / wg;
     const uint32_t passes = (g.groups + per_pass - 1u) / per_pass;
     const uint32_t grid = passes < 4u * (uint32_t)sms ? passes : 4u * (uint32_t)sms;
-    const size_t smem = kSmallFixedSmem + (size_t)g.K16 * 2u;
+    const size_t smem = kSmallFixedSmem + (size_t)g.K16 * (in.mode == kInputNorm ? 4u : 2u);
     if (type_of(code) == kFp8) return launch_kernel(small_kernel_layout0<kFp8>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
     return launch_kernel(small_kernel_layout0<kBf16>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
 }
@@ -1033,8 +1111,8 @@ static void opt_in_smem() {
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeAtomic, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 void configure_segment_kernels() {
-    cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
