@@ -620,15 +620,14 @@ struct GlobalWindow : BitWindow<MAX_RANK> {
 };
 
 /* One layout-0 block: 8 rows x 16 columns per lane.  Even rows enter the mma as the "row r" half of the A fragment, odd
-   rows as the "row r + 8" half, the other half is zero; after two rows the diagonal of D holds the quad's dot products. */
+   rows as the "row r + 8" half (both rows meet the same columns of x); after two rows the diagonal of D holds the lane
+   quads' dot products. */
 template <class WIN, int ELEM, bool XF32>
 __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane,
                                                       uint32_t table, uint32_t sym, uint32_t four, float *stash, uint32_t xs = 0u) {
     const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 8u, col0 = cb * kBlockCols + lane * 16u;
     const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
     const bool col_ok = col0 < g.K16, diag = q == (r >> 1);
-    /* four distinct registers that hold zero (the compiler cannot tell): the unused halves of the A fragments */
-    const uint32_t z0 = four >> 8, z1 = four >> 9, z2 = four >> 10, z3 = four >> 11;
     XFrag8<XF32> xa, xb;
     if (!col_ok) { xa.zero(); xb.zero(); }
     else if (!XF32 && xs) { xa.load_shared(xs + col0 * 2u); xb.load_shared(xs + col0 * 2u + 16u); }     /* x staged by the CTA */
@@ -644,14 +643,12 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
         }
         float d[4] = {0.f, 0.f, 0.f, 0.f};
         const uint32_t wa[4] = {rawA.x, rawA.y, rawA.z, rawA.w}, wb[4] = {rawB.x, rawB.y, rawB.z, rawB.w};
+        /* the even row's fragments wait in registers until the odd row is decoded: one mma then takes both rows */
+        uint32_t even0[4], even1[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             uint32_t e01, e23; W.quad(table, sym, four, e01, e23);
-            const XFrag8<XF32> &xf = k < 2 ? xa : xb;
-            const int w = 2 * (k & 1);
-            const uint32_t p0 = weave<0>(wa[k], e01), p1 = weave<2>(wa[k], e23);
-            mma_bf16(d, p0, z1, p1, z3, xf.head[w], xf.head[w + 1]);
-            if (XF32) mma_bf16(d, p0, z1, p1, z3, xf.tail[w], xf.tail[w + 1]);
+            even0[k] = weave<0>(wa[k], e01); even1[k] = weave<2>(wa[k], e23);
         }
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -659,8 +656,8 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
             const XFrag8<XF32> &xf = k < 2 ? xa : xb;
             const int w = 2 * (k & 1);
             const uint32_t p0 = weave<0>(wb[k], e01), p1 = weave<2>(wb[k], e23);
-            mma_bf16(d, z0, p0, z2, p1, xf.head[w], xf.head[w + 1]);
-            if (XF32) mma_bf16(d, z0, p0, z2, p1, xf.tail[w], xf.tail[w + 1]);
+            mma_bf16(d, even0[k], p0, even1[k], p1, xf.head[w], xf.head[w + 1]);
+            if (XF32) mma_bf16(d, even0[k], p0, even1[k], p1, xf.tail[w], xf.tail[w + 1]);
         }
         if (diag) {
             stash[(2u * rp) * 8u + r] = (r & 1u) ? d[1] : d[0];

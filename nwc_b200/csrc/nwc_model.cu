@@ -86,23 +86,28 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const uint16_t *_
     float *qs = sm, *ks = sm + hd, *scores = sm + 2 * hd;          /* q, current k (fp32), scores [max_len] */
     __shared__ float red[32];
     const uint32_t head = blockIdx.x, kvh = head / (n_q / n_kv), tid = threadIdx.x;
+    /* the norm weights do not depend on earlier kernels: fetch them while the predecessor finishes */
+    float qw = 0.f, kw = 0.f;
+    if (q_norm && tid < hd) { qw = bf2f(q_norm[tid]); kw = bf2f(k_norm[tid]); }
     dependency_sync();
-    const int32_t pos = *pos_ptr;
-    if (pos < 0 || (uint32_t)pos >= max_len) { if (tid == 0) atomicExch(status, 1); return; }
+    /* one round trip for everything that needs no position, a second one for the rotary row */
     const uint16_t *qp = qkv + (uint64_t)head * hd, *kp = qkv + (uint64_t)(n_q + kvh) * hd, *vp = qkv + (uint64_t)(n_q + n_kv + kvh) * hd;
-    const uint16_t *cs = cos_t + (uint64_t)pos * hd, *sn = sin_t + (uint64_t)pos * hd;
-    /* per-head RMSNorm of q and k (Qwen3), then rotary embedding with bf16 rounding per operation */
     float qv = 0.f, kv = 0.f;
     if (tid < hd) { qv = bf2f(qp[tid]); kv = bf2f(kp[tid]); }
+    const int32_t pos = *pos_ptr;
+    if (pos < 0 || (uint32_t)pos >= max_len) { if (tid == 0) atomicExch(status, 1); return; }
+    float rc = 0.f, rs = 0.f;
+    if (tid < hd) { rc = bf2f(cos_t[(uint64_t)pos * hd + tid]); rs = bf2f(sin_t[(uint64_t)pos * hd + tid]); }
+    /* per-head RMSNorm of q and k (Qwen3), then rotary embedding with bf16 rounding per operation */
     if (q_norm) {
         const float qi = rsqrtf(block_sum(qv * qv, red) / (float)hd + eps), ki = rsqrtf(block_sum(kv * kv, red) / (float)hd + eps);
-        if (tid < hd) { qv = bfround(bf2f(q_norm[tid]) * bfround(qv * qi)); kv = bfround(bf2f(k_norm[tid]) * bfround(kv * ki)); }
+        if (tid < hd) { qv = bfround(qw * bfround(qv * qi)); kv = bfround(kw * bfround(kv * ki)); }
     }
     if (tid < hd) { qs[tid] = qv; ks[tid] = kv; }
     __syncthreads();
     if (tid < hd) {
         const uint32_t half = hd >> 1, other = tid < half ? tid + half : tid - half;
-        const float sgn = tid < half ? -1.f : 1.f, c = bf2f(cs[tid]), s = bf2f(sn[tid]);
+        const float sgn = tid < half ? -1.f : 1.f, c = rc, s = rs;
         qv = bfround(bfround(qs[tid] * c) + bfround(sgn * qs[other] * s));
         kv = bfround(bfround(ks[tid] * c) + bfround(sgn * ks[other] * s));
     }
