@@ -117,9 +117,23 @@ def run_reference(a, cfg):
     print(json.dumps(line))
 
 
-def workload(a, cfg):
+def workload(a, cfg, token_bytes=None, lm_head_bytes=None):
+    policy = "no flush: the compressed weights streamed per token and the lm_head matrix of the roofline leg are each larger than the 126 MB L2"
+    if token_bytes is not None:
+        policy = "no flush: weights streamed per token (%.2f GB) and the roofline kernel's matrix (lm_head, %.0f MB) exceed the 126 MB L2" % (token_bytes / 1e9, lm_head_bytes / 1e6)
     return {"workload": f"{cfg.name}-architecture decoder, random init, NWC {a.elem} layout {a.layout}, batch 1, {a.prompt} random prompt ids, greedy decode as a CUDA graph",
-            "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "l2_policy": "weights streamed per token (0.8 GB) exceed the 126 MB L2; roofline kernel input (lm_head, 214 MB) exceeds L2"}
+            "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "l2_policy": policy}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the lm_head kernel, from the ncu captures summarised
+# under profiles/ (same command line as `--kernel lm_head`); other workloads report null
+NCU_TRAFFIC = {("qwen3-0.6b", 0, "bf16"): 217.5e6, ("qwen3-0.6b", 2, "bf16"): 239.1e6}
+
+
+def token_kernel_name(layout, elem):
+    if layout == 0: return "prefix_ring_kernel_layout0"
+    if layout == 2 and elem == "bf16": return "ring_kernel_layout2"
+    return "segment_kernel<layout %d, %s>" % (layout, elem)
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -269,8 +283,9 @@ def main():
     k0.record(); kg.replay(); k1.record(); torch.cuda.synchronize()
     kernel_ms = k0.elapsed_time(k1) / reps
     achieved = w.bytes / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "segment_kernel (fused decode-matvec), lm_head %dx%d layout %d" % (w.out_features, w.in_features, w.layout),
-                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+    roofline = {"bound": "hbm", "kernel": "%s (fused decode-matvec), lm_head %dx%d layout %d" % (token_kernel_name(w.layout, a.elem), w.out_features, w.in_features, w.layout),
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC.get((a.model, a.layout, a.elem)) if not tp else None,
                 "bytes_per_launch": w.bytes, "us_per_launch": kernel_ms * 1e3,
                 "model_bytes_per_token": weights.bytes_per_token(), "model_frac_of_roofline": weights.bytes_per_token() / (ms / a.steps * 1e-3) / 1e9 / peak}
     cpu = None
@@ -281,7 +296,7 @@ def main():
     streams = 1 if tp else world          # sequences decoded at once
     line = {"metric": "decode_tokens_per_s", "value": streams * a.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
-            "config": dict(workload(a, cfg), parallelism=("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, NCCL all-reduce after o and down" % world if tp
+            "config": dict(workload(a, cfg, weights.bytes_per_token(), w.bytes), parallelism=("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, NCCL all-reduce after o and down" % world if tp
                                                  else "replicas x%d (no data-path collective)" % world) if world > 1 else "1 GPU"),
             "e2e": {"value": streams * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": a.steps * eng.launches_per_step, "launches_per_step": eng.launches_per_step,

@@ -117,6 +117,11 @@ NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_
         FusedInput in{mode, h_in, delta, h_out, norm_w, eps, gate_up};
         return (int)launch_small_layout0(elem, sms, (cudaStream_t)stream, a, in);
     }
+    if (mode != kInputPlain && token_path_fuses_input(elem, M, K, mode)) {
+        SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
+        const FusedInput in{mode, h_in, delta, h_out, norm_w, eps, gate_up};
+        return (int)launch_segments(0, elem, sms, (cudaStream_t)stream, a, &in);
+    }
     const uint16_t *xin = x;
     if (mode != kInputPlain) {
         if (!xtmp || !aligned16(xtmp)) return -1;
@@ -137,7 +142,7 @@ NWC_EXPORT int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_m
     const uint32_t M = (uint32_t)(n / K);
     const Geometry g(M, K, layout_of(elem));
     if (fused_mode >= 0 && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) return 1;
-    return count_token_launches(elem, sms, M, K) + (fused_mode > 0 ? 1 : 0);
+    return count_token_launches(elem, sms, M, K) + (fused_mode > 0 && !token_path_fuses_input(elem, M, K, fused_mode) ? 1 : 0);
 }
 
 NWC_EXPORT void nwc_set_dependent_launch(int on) { set_dependent_launch(on != 0); }

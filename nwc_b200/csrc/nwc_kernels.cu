@@ -284,26 +284,143 @@ __device__ __forceinline__ void segment_layout2(const SegmentArgs &a, const Geom
     }
 }
 
+/* ---- activation vector of a token matvec, built in shared memory --------------------------------------------------- */
+/* x (bf16, `cols` values, zero beyond K) comes from one of three sources: a plain vector, the residual stream
+   (h_out = h_in + delta, x = RMSNorm(h_out) * w) or a fused gate/up vector (x = silu(gate) * up), with the rounding
+   steps of the separate kernels in nwc_model.cu.  Every CTA builds its own copy; CTA 0 writes h_out.  K % 8 == 0 takes
+   16-byte vectors (the entry point checks the pointers), other K one value at a time. */
+__device__ __forceinline__ float bf16_rt(float v) { return bf16_to_float(bf16_round_nan(v)); }
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) { return (uint32_t)bf16_round_nan(lo) | ((uint32_t)bf16_round_nan(hi) << 16); }
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) { asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
+
+/* before the dependency wait: the RMSNorm weight (a constant) goes to shared memory */
+template <uint32_t THREADS>
+__device__ __forceinline__ void stage_norm_weight(const FusedInput &in, uint32_t K, uint16_t *nw) {
+    if (in.mode != kInputNorm || (K & 7u) != 0u) return;
+    const uint32_t nw_addr = smem_addr(nw);
+    for (uint32_t c = threadIdx.x; c < (K >> 3); c += THREADS) sts128(nw_addr + c * 16u, __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c));
+}
+
+/* after the dependency wait; ends with __syncthreads().  scal: THREADS / 32 floats of shared memory. */
+template <uint32_t THREADS>
+__device__ __forceinline__ void build_activation(const FusedInput &in, const void *x, uint32_t K, uint32_t cols, uint16_t *xs, uint16_t *nw, float *scal) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t xs_addr = smem_addr(xs), nw_addr = smem_addr(nw), chunks = cols >> 3, live = K >> 3;   /* chunks of eight values */
+    const bool vec = (K & 7u) == 0u;
+    if (in.mode == kInputNorm) {
+        float ss = 0.f;
+        if (vec) {
+            for (uint32_t c = tid; c < chunks; c += THREADS) {
+                uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                if (c < live) {
+                    const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
+                    const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+                    uint32_t dw[4] = {0u, 0u, 0u, 0u}, ow[4];
+                    if (in.delta) { const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c); dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w; }
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        float v0 = bf16_lo(hw[k]), v1 = bf16_hi(hw[k]);
+                        if (in.delta) { v0 = bf16_rt(v0 + bf16_lo(dw[k])); v1 = bf16_rt(v1 + bf16_hi(dw[k])); }
+                        ss += v0 * v0; ss += v1 * v1;
+                        ow[k] = bf16_pack(v0, v1);
+                    }
+                    o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    if (blockIdx.x == 0 && in.h_out) *(reinterpret_cast<uint4 *>(in.h_out) + c) = o;
+                }
+                sts128(xs_addr + c * 16u, o);
+            }
+        } else {
+            for (uint32_t i = tid; i < K; i += THREADS) {
+                float v = bf16_to_float(in.h_in[i]);
+                if (in.delta) v = bf16_rt(v + bf16_to_float(in.delta[i]));
+                if (blockIdx.x == 0 && in.h_out) in.h_out[i] = bf16_round_nan(v);
+                xs[i] = bf16_round_nan(v);
+                ss += v * v;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) scal[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (uint32_t i = 0; i < THREADS / 32u; i++) tot += scal[i];
+        const float inv = rsqrtf(tot / (float)K + in.eps);
+        if (vec) {
+            for (uint32_t c = tid; c < live; c += THREADS) {
+                const uint4 v = lds128(xs_addr + c * 16u), w = lds128(nw_addr + c * 16u);
+                const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, ww[4] = {w.x, w.y, w.z, w.w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) ow[k] = bf16_pack(bf16_lo(ww[k]) * bf16_rt(bf16_lo(vw[k]) * inv), bf16_hi(ww[k]) * bf16_rt(bf16_hi(vw[k]) * inv));
+                sts128(xs_addr + c * 16u, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+            }
+        } else {
+            for (uint32_t i = tid; i < cols; i += THREADS)
+                xs[i] = i < K ? bf16_round_nan(bf16_to_float(in.norm_w[i]) * bf16_rt(bf16_to_float(xs[i]) * inv)) : (uint16_t)0;
+        }
+    } else if (in.mode == kInputSwiglu) {
+        if (vec) {
+            const uint4 *gate = reinterpret_cast<const uint4 *>(in.gate_up), *up = reinterpret_cast<const uint4 *>(in.gate_up + K);
+#pragma unroll 2
+            for (uint32_t c = tid; c < chunks; c += THREADS) {
+                uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                if (c < live) {
+                    const uint4 gv = gate[c], uv = up[c];
+                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+                    uint32_t ow[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float g0 = bf16_lo(gw[k]), g1 = bf16_hi(gw[k]);
+                        ow[k] = bf16_pack(bf16_rt(g0 / (1.f + __expf(-g0))) * bf16_lo(uw[k]), bf16_rt(g1 / (1.f + __expf(-g1))) * bf16_hi(uw[k]));
+                    }
+                    o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                }
+                sts128(xs_addr + c * 16u, o);
+            }
+        } else {
+            for (uint32_t i = tid; i < cols; i += THREADS) {
+                uint16_t v = 0;
+                if (i < K) { const float gt = bf16_to_float(in.gate_up[i]), up = bf16_to_float(in.gate_up[K + i]); v = bf16_round_nan(bf16_rt(gt / (1.f + __expf(-gt))) * up); }
+                xs[i] = v;
+            }
+        }
+    } else if (vec) {
+        for (uint32_t c = tid; c < chunks; c += THREADS)
+            sts128(xs_addr + c * 16u, c < live ? *(reinterpret_cast<const uint4 *>(x) + c) : make_uint4(0u, 0u, 0u, 0u));
+    } else {
+        for (uint32_t i = tid; i < cols; i += THREADS) xs[i] = i < K ? static_cast<const uint16_t *>(x)[i] : (uint16_t)0;
+    }
+    __syncthreads();
+}
+
 /* ---- layout 2, token path, bf16: planes streamed through a per-warp ring of bulk copies ------------------------------ */
 /* Work split.  The matrix is one flat sequence of super-chunk slots (row-group-major; both planes are contiguous in that
-   order).  Every warp of the persistent grid takes an equal, contiguous run of `per` slots, so all warps finish together
-   whatever the shape.  A row group that is cut by a run boundary gets one fp32 partial per warp that touched it (at most
-   `parts` per row, in the caller's scratch) and a small finalize kernel adds them in warp order; when no run boundary
-   falls inside a row group the warp writes bf16 y itself.
+   order).  Every CTA of the grid (one per SM) takes a contiguous run of slots and its warps split that run evenly.  A
+   warp writes a row group it covers alone straight to the output; the row groups it shares with other warps of the CTA
+   (at most its first and its last one) are added up in shared memory in warp order.  The CTA runs are whole row groups
+   when that leaves little imbalance (one launch, bf16 y written here); otherwise they are equal runs of slots, a row
+   group cut by a CTA boundary gets one fp32 partial per CTA in the caller's scratch and finalize_flat_kernel adds them.
    Data path.  A stage holds kRingSlots slots of both planes (256 B of nibbles and 512 B of low bytes per slot, each slot
-   lane-contiguous).  The warp keeps kRingStages stages in flight, so it never waits for HBM once the ring is full. */
+   lane-contiguous) and every warp keeps kRingStages stages in flight.  Measured on B200 (4096 x 4096 up to
+   151936 x 2560): 16 warps with 6-slot stages beat 32 warps with 2- or 3-slot stages and 8 warps with 12-slot stages,
+   because the per-stage work (barrier wait, refill, bulk-copy operands) is issue-slot cost, not hidden latency. */
 #ifndef NWC_RING_SLOTS
-#define NWC_RING_SLOTS 3
+#define NWC_RING_SLOTS 6
 #define NWC_RING_STAGES 2
 #endif
-constexpr uint32_t kRingThreads = 1024, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES;
+#ifndef NWC_RING_THREADS
+#define NWC_RING_THREADS 512
+#endif
+constexpr uint32_t kRingThreads = NWC_RING_THREADS, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES;
 constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
 constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes;
 constexpr uint32_t kRingBarrierBytes = (kRingThreads / 32u) * kRingStages * 8u;
 constexpr uint32_t kRingMaxSmem = 232448u;                       /* 227 KB opt-in limit of a CTA */
 /* shared memory of the layout-2 ring kernel: x (32 columns per slot, bf16), the barriers, then the per-warp rings */
 __host__ __device__ static inline uint32_t ring_x_bytes(const Geometry &g) { return (g.slots * 64u + 127u) & ~127u; }
-static inline uint32_t ring_smem_bytes(const Geometry &g) { return ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
+static inline uint32_t ring_smem_bytes(const Geometry &g, int input_mode = kInputPlain) { return (input_mode == kInputNorm ? 2u : 1u) * ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + 128u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
 
 struct FlatPlan {
     uint32_t units_per_group;   /* slots (layout 2) or blocks (layouts 0, 1) per row group                              */
@@ -353,15 +470,17 @@ constexpr uint32_t kRingEntries = 2u * (kRingThreads / 32u);
 constexpr uint32_t kRingShareBytes = kRingEntries * 4u + kRingEntries * 16u * 4u;
 constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 
-__global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan) {
+__global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
     extern __shared__ __align__(128) uint8_t ring_smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Geometry g(a.M, a.K, 2);
-    const uint32_t xs = smem_addr(ring_smem), x_bytes = ring_x_bytes(g);
-    uint32_t *share_group = reinterpret_cast<uint32_t *>(ring_smem + x_bytes);
-    float *share_value = reinterpret_cast<float *>(ring_smem + x_bytes + kRingEntries * 4u);
-    const uint32_t bars = xs + x_bytes + kRingShareBytes + warp * (kRingStages * 8u);
-    const uint32_t ring = xs + x_bytes + kRingShareBytes + kRingBarrierBytes + warp * kRingWarpBytes;
+    /* shared memory: x | RMSNorm weight (kInputNorm only) | shared row groups | reduction scratch | barriers | rings */
+    const uint32_t xs = smem_addr(ring_smem), x_bytes = ring_x_bytes(g), front = in.mode == kInputNorm ? 2u * x_bytes : x_bytes;
+    uint32_t *share_group = reinterpret_cast<uint32_t *>(ring_smem + front);
+    float *share_value = reinterpret_cast<float *>(ring_smem + front + kRingEntries * 4u);
+    float *scal = reinterpret_cast<float *>(ring_smem + front + kRingShareBytes);
+    const uint32_t bars = xs + front + kRingShareBytes + 128u + warp * (kRingStages * 8u);
+    const uint32_t ring = xs + front + kRingShareBytes + 128u + kRingBarrierBytes + warp * kRingWarpBytes;
     /* the CTA's run of slots, then this warp's equal share of it */
     const uint64_t c0 = plan.start(blockIdx.x), c1 = plan.start(blockIdx.x + 1u);
     const uint32_t cn = (uint32_t)(c1 - c0), w0 = (uint32_t)((uint64_t)cn * warp / (kRingThreads / 32u)), w1 = (uint32_t)((uint64_t)cn * (warp + 1u) / (kRingThreads / 32u));
@@ -387,16 +506,12 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
     /* exception count of this lane and data offset of the next block to start in this run, fetched one block ahead */
     uint32_t next_block = rb * g.CB + ((s + 15u) >> 4), next_count = 0, next_base = 0;
     if (next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
-    /* The weights do not depend on the kernel before this one, x does.  x goes into shared memory, zero beyond K16
-       (the last slot may cover 16 columns more). */
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (uint32_t i = threadIdx.x * 16u; i < x_bytes; i += kRingThreads * 16u) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (i < g.K16 * 2u) v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(a.x) + i));
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xs + i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-    }
+    /* The weights do not depend on the kernel before this one, the activation vector does.  It is built in shared
+       memory, zero beyond K (the last slot may cover columns past K16). */
+    stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes));
     if (threadIdx.x < kRingEntries) share_group[threadIdx.x] = kNoGroup;
-    __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal);
     const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * 16u, xq = xs + (lane & 3u) * 16u;
     uint32_t seg_first = s, entry = 2u * warp;                   /* first slot of the current segment; where a shared one goes */
     float d[4] = {0.f, 0.f, 0.f, 0.f}, ex_lo = 0.f, ex_hi = 0.f;
@@ -756,12 +871,6 @@ constexpr uint32_t kSmallThreads = 256, kSmallWarps = kSmallThreads / 32u;
 /* warps that share one row group: the smallest power of two that covers its column blocks (at most the CTA) */
 __host__ __device__ static inline uint32_t small_group_warps(uint32_t CB) { return CB > 4u ? 8u : (CB > 2u ? 4u : (CB > 1u ? 2u : 1u)); }
 
-__device__ __forceinline__ float bf16_rt(float v) { return bf16_to_float(bf16_round_nan(v)); }
-__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xFFFF0000u); }
-__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) { return (uint32_t)bf16_round_nan(lo) | ((uint32_t)bf16_round_nan(hi) << 16); }
-__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) { asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
-
 template <int ELEM>
 __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
@@ -819,98 +928,11 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
        raw rows towards L2 before anything else, so that both overlap the table staging, the wait and the prologue */
     prefetch_block(blockIdx.x, j, 0u);
     stage_tables(tables, a.lut, tid, kSmallThreads);
-    const uint32_t xs_addr = smem_addr(xs), nw_addr = smem_addr(nw), chunks = g.K16 >> 3, live = a.K >> 3;   /* chunks of eight values */
-    const bool vec = (a.K & 7u) == 0u;
-    if (in.mode == kInputNorm && vec)
-        for (uint32_t c = tid; c < live; c += kSmallThreads) sts128(nw_addr + c * 16u, __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c));
+    stage_norm_weight<kSmallThreads>(in, a.K, nw);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    /* ---- activation vector -> shared memory (bf16, zero beyond K) ---- */
-    if (in.mode == kInputNorm && vec) {
-        float ss = 0.f;
-        for (uint32_t c = tid; c < chunks; c += kSmallThreads) {
-            uint4 o = make_uint4(0u, 0u, 0u, 0u);
-            if (c < live) {
-                const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
-                const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
-                uint32_t dw[4] = {0u, 0u, 0u, 0u}, ow[4];
-                if (in.delta) { const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c); dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w; }
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    float v0 = bf16_lo(hw[k]), v1 = bf16_hi(hw[k]);
-                    if (in.delta) { v0 = bf16_rt(v0 + bf16_lo(dw[k])); v1 = bf16_rt(v1 + bf16_hi(dw[k])); }
-                    ss += v0 * v0; ss += v1 * v1;
-                    ow[k] = bf16_pack(v0, v1);
-                }
-                o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                if (blockIdx.x == 0 && in.h_out) *(reinterpret_cast<uint4 *>(in.h_out) + c) = o;
-            }
-            sts128(xs_addr + c * 16u, o);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) scal[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (uint32_t i = 0; i < kSmallWarps; i++) tot += scal[i];
-        const float inv = rsqrtf(tot / (float)a.K + in.eps);
-        for (uint32_t c = tid; c < live; c += kSmallThreads) {
-            const uint4 v = lds128(xs_addr + c * 16u), w = lds128(nw_addr + c * 16u);
-            const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, ww[4] = {w.x, w.y, w.z, w.w};
-            uint32_t ow[4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) ow[k] = bf16_pack(bf16_lo(ww[k]) * bf16_rt(bf16_lo(vw[k]) * inv), bf16_hi(ww[k]) * bf16_rt(bf16_hi(vw[k]) * inv));
-            sts128(xs_addr + c * 16u, make_uint4(ow[0], ow[1], ow[2], ow[3]));
-        }
-    } else if (in.mode == kInputNorm) {
-        float ss = 0.f;
-        for (uint32_t i = tid; i < a.K; i += kSmallThreads) {
-            float v = bf16_to_float(in.h_in[i]);
-            if (in.delta) v = bf16_rt(v + bf16_to_float(in.delta[i]));
-            if (blockIdx.x == 0 && in.h_out) in.h_out[i] = bf16_round_nan(v);
-            xs[i] = bf16_round_nan(v);
-            ss += v * v;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) scal[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (uint32_t i = 0; i < kSmallWarps; i++) tot += scal[i];
-        const float inv = rsqrtf(tot / (float)a.K + in.eps);
-        for (uint32_t i = tid; i < g.K16; i += kSmallThreads)
-            xs[i] = i < a.K ? bf16_round_nan(bf16_to_float(in.norm_w[i]) * bf16_rt(bf16_to_float(xs[i]) * inv)) : (uint16_t)0;
-    } else if (in.mode == kInputSwiglu && vec) {
-        const uint4 *gate = reinterpret_cast<const uint4 *>(in.gate_up), *up = reinterpret_cast<const uint4 *>(in.gate_up + a.K);
-#pragma unroll 2
-        for (uint32_t c = tid; c < chunks; c += kSmallThreads) {
-            uint4 o = make_uint4(0u, 0u, 0u, 0u);
-            if (c < live) {
-                const uint4 gv = gate[c], uv = up[c];
-                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-                uint32_t ow[4];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const float g0 = bf16_lo(gw[k]), g1 = bf16_hi(gw[k]);
-                    ow[k] = bf16_pack(bf16_rt(g0 / (1.f + __expf(-g0))) * bf16_lo(uw[k]), bf16_rt(g1 / (1.f + __expf(-g1))) * bf16_hi(uw[k]));
-                }
-                o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-            }
-            sts128(xs_addr + c * 16u, o);
-        }
-    } else if (in.mode == kInputSwiglu) {
-        for (uint32_t i = tid; i < g.K16; i += kSmallThreads) {
-            uint16_t v = 0;
-            if (i < a.K) { const float gt = bf16_to_float(in.gate_up[i]), up = bf16_to_float(in.gate_up[a.K + i]); v = bf16_round_nan(bf16_rt(gt / (1.f + __expf(-gt))) * up); }
-            xs[i] = v;
-        }
-    } else if (vec) {
-        for (uint32_t c = tid; c < chunks; c += kSmallThreads)
-            sts128(xs_addr + c * 16u, c < live ? *(reinterpret_cast<const uint4 *>(a.x) + c) : make_uint4(0u, 0u, 0u, 0u));
-    } else {
-        for (uint32_t i = tid; i < g.K16; i += kSmallThreads) xs[i] = i < a.K ? static_cast<const uint16_t *>(a.x)[i] : (uint16_t)0;
-    }
-    __syncthreads();
+    build_activation<kSmallThreads>(in, a.x, a.K, g.K16, xs, nw, scal);
+    const uint32_t xs_addr = smem_addr(xs);
     const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords;
     float *stash = stash_all + warp * 64u;
     uint32_t phases = 0, which = 0;                              /* parity per stage; the stage that holds the current block */
@@ -1057,7 +1079,13 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K) {
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
-cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a) {
+/* the token path of this matrix builds its activation vector itself (nwc_linear_fused needs no prologue launch) */
+bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode) {
+    const Geometry g(M, K, layout_of(code));
+    return layout_of(code) == 2 && type_of(code) == kBf16 && !g_disable_ring && ring_smem_bytes(g, input_mode) <= kRingMaxSmem;
+}
+
+cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(a.M, a.K, layout);
     a.splits_forced = a.splits;
@@ -1081,9 +1109,11 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
         }
         return err;
     }
-    if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_smem_bytes(g) <= kRingMaxSmem) {
+    FusedInput in{kInputPlain, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr};
+    if (input) in = *input;
+    if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_smem_bytes(g, in.mode) <= kRingMaxSmem) {
         make_cta_plan_layout2(g, sms, plan);
-        err = launch_kernel(ring_kernel_layout2, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g), st, a, plan);
+        err = launch_kernel(ring_kernel_layout2, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
         if (err == cudaSuccess && !plan.direct)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;

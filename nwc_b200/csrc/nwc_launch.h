@@ -45,7 +45,9 @@ bool dependent_launch();
 uint32_t choose_splits(const Geometry &g, int mode, int code, int sms);
 void set_ring_kernels(bool on);               /* tests: switch the bulk-copy ring kernels off to compare with the plain ones */
 int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gave up; synchronises */
-cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a);
+/* input: how the token path builds its activation vector; only where token_path_fuses_input() says so, else null */
+cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input = nullptr);
+bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode);
 void configure_segment_kernels();
 int count_token_launches(int code, int sms, uint32_t M, uint32_t K);
 

@@ -10,7 +10,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("M,K,layout,elem", [(4096, 1024, 0, 0), (1024, 2048, 0, 0), (1024, 3072, 0, 0), (6144, 1024, 0, 0), (100, 1000, 0, 0), (13, 40, 0, 0),
-                                             (1024, 5120, 0, 0), (256, 1024, 0, 1), (512, 1024, 2, 0), (512, 1024, 1, 0)])
+                                             (1024, 5120, 0, 0), (256, 1024, 0, 1), (512, 1024, 2, 0), (512, 1024, 1, 0),
+                                             (6144, 2560, 2, 0), (2560, 9728, 2, 0), (100, 1000, 2, 0), (13, 40, 2, 0), (48, 1004, 2, 0)])
 def test_fused_modes_match_separate_kernels(M, K, layout, elem):
     from gpu_helpers import bits, bf16_tensor, make_case, to_weight
     from nwc_b200 import _lib as L
