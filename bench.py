@@ -153,6 +153,7 @@ def kernel_only(a, cfg):
               "gate_up": (2 * cfg.intermediate, cfg.hidden), "down": (cfg.hidden, cfg.intermediate)}
     M, K = shapes[a.kernel] if a.kernel in shapes else tuple(int(v) for v in a.kernel.lower().split("x"))
     torch.cuda.set_device(0)
+    L.lib.nwc_set_dependent_launch(int(a.dependent_launch))
     first = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
     copies = max(1, min(64, -(-(320 << 20) // first.bytes)))          # rotate over > 320 MB so that no launch finds its matrix in L2
     mats = [first] + [NWCWeight(synthetic_matrix(M, K, 1 + i), layout=a.layout, elem=a.elem) for i in range(1, copies)]
@@ -164,21 +165,31 @@ def kernel_only(a, cfg):
                                    L.ptr(w.scratch), L.ptr(y), w.n, w.block, K, w.code)
         if err: raise RuntimeError(f"nwc_linear_x16 error {err}")
     reps = max(copies, 8)
-    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side): launch(nw)
-    torch.cuda.current_stream().wait_stream(side)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for i in range(reps): launch(mats[i % copies])
-    times = []
-    for i in range(a.warmup + a.steps):
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record(); graph.replay(); t1.record(); torch.cuda.synchronize()
-        if i >= a.warmup: times.append(t0.elapsed_time(t1) / reps)
+    def timed(call, n_copies):
+        side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side): call(0)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps): call(i % n_copies)
+        times = []
+        for i in range(a.warmup + a.steps):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(); graph.replay(); t1.record(); torch.cuda.synchronize()
+            if i >= a.warmup: times.append(t0.elapsed_time(t1) / reps)
+        return statistics.median(times)
+    ms = timed(lambda i: launch(mats[i]), copies)
     if L.lib.nwc_kernel_status(1): raise RuntimeError("a bounded wait inside a kernel gave up")
-    ms = statistics.median(times); peak, kind = measured_peak()
+    peak, kind = measured_peak()
+    # the same product as a dense bf16 GEMV from the vendor library, same timing method (a reported comparison only)
+    dense_ms = None
+    if a.elem == "bf16" and a.steps > 1:
+        dense_copies = max(1, min(16, -(-(320 << 20) // (2 * M * K))))
+        dense = [synthetic_matrix(M, K, 1 + i).cuda() for i in range(dense_copies)]
+        dense_ms = timed(lambda i: torch.nn.functional.linear(x[:K], dense[i]), dense_copies)
+        del dense
     print(json.dumps({"kernel": f"token matvec {M}x{K} {a.elem} layout {a.layout}", "launches_per_call": L.lib.nwc_linear_launches(nw.n, K, nw.code, -1), "us_per_call": ms * 1e3,
-                      "bytes_per_call": nw.bytes, "bits_per_weight": 8 * nw.bytes / nw.n,
+                      "bytes_per_call": nw.bytes, "bits_per_weight": 8 * nw.bytes / nw.n, "dense_bf16_gemv_us": None if dense_ms is None else dense_ms * 1e3,
                       "roofline": {"bound": "hbm", "achieved": nw.bytes / ms / 1e6, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": nw.bytes / ms / 1e6 / peak},
                       "note": "%d calls on %d rotating copies replayed as one CUDA graph, CUDA events around the replay (a call includes its finalize launch when it needs one)" % (reps, copies)}))
 
