@@ -789,18 +789,45 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
     return sum;
 }
 
-template <int ELEM, bool XF32>
-__global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(const SegmentArgs a, const FlatPlan plan, const uint32_t four) {
+/* One layout-1 block (16 rows x 512 columns, stored in A-fragment order): `nsc` super-chunks of 16 weights per lane, raw
+   low bytes one slot ahead from the plane, the sums stay in the mma accumulators d (rows r and r + 8 of lane group r). */
+template <class WIN, int ELEM>
+__device__ __forceinline__ void prefix_block_layout1(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane,
+                                                     uint32_t table, uint32_t sym, uint32_t four, float (&d)[4]) {
+    constexpr uint32_t RB = ELEM == kFp8 ? 8u : 16u;             /* raw bytes per lane and super-chunk */
+    const uint32_t q = lane & 3u, nsc = g.supers_in(cb);
+    const uint8_t *rp = a.low + ((uint64_t)(rb * g.slots + cb * 16u) * kLanes + lane) * RB;
+    uint4 ahead = ELEM == kFp8 ? expand_nibbles(ldg_stream64(rp)) : ldg_stream128(rp);
+#pragma unroll 1
+    for (uint32_t sc = 0; sc < nsc; sc++) {
+        const uint4 cw = ahead;
+        rp += kLanes * RB;                                       /* one slot ahead, unguarded: the plane carries 512 B of slack */
+        ahead = ELEM == kFp8 ? expand_nibbles(ldg_stream64(rp)) : ldg_stream128(rp);
+        XFrag8<false> xf; xf.load(a.x, cb * kBlockCols + sc * 32u + 8u * q);
+        const uint32_t c[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t e0, e1, e2, e3;
+            W.quad(table, sym, four, e0, e1); W.quad(table, sym, four, e2, e3);
+            mma_bf16(d, weave<0>(c[2 * h], e0), weave<2>(c[2 * h], e1), weave<0>(c[2 * h + 1], e2), weave<2>(c[2 * h + 1], e3), xf.head[2 * h], xf.head[2 * h + 1]);
+        }
+    }
+    __syncwarp();                                                /* all lanes are done with the stage that held this block */
+}
+
+template <int LAYOUT, int ELEM, bool XF32, uint32_t THREADS, uint32_t STAGE>
+__device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const FlatPlan &plan, const uint32_t four) {
+    constexpr uint32_t kWarpBytes = 2u * STAGE + 256u + 16u;
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
     extern __shared__ __align__(128) uint8_t ring_smem[];
     uint32_t *tables = reinterpret_cast<uint32_t *>(ring_smem);
-    stage_tables(tables, a.lut, threadIdx.x, kPrefixThreads);
+    stage_tables(tables, a.lut, threadIdx.x, THREADS);
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords;
-    uint8_t *mine = ring_smem + 16416u + warp * kPrefixWarpBytes;
-    const uint32_t stages = smem_addr(mine), bars = stages + 2u * kPrefixStageBytes + 256u;
-    float *stash = reinterpret_cast<float *>(mine + 2u * kPrefixStageBytes);
-    const Geometry g(a.M, a.K, 0);
+    uint8_t *mine = ring_smem + 16416u + warp * kWarpBytes;
+    const uint32_t stages = smem_addr(mine), bars = stages + 2u * STAGE + 256u;
+    float *stash = reinterpret_cast<float *>(mine + 2u * STAGE);
+    const Geometry g(a.M, a.K, LAYOUT);
     const uint32_t w = warp * gridDim.x + blockIdx.x;           /* interleaved: a short plan still spreads over all SMs */
     if (w >= plan.warps) return;
     const uint32_t b0 = (uint32_t)plan.start(w), b1 = (uint32_t)plan.start(w + 1u);
@@ -814,7 +841,7 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
         else { uint32_t t; warp_exclusive_sum(words_of_b, lane, t); len = 4u * t; }
         start = base & ~15u;
         bytes = (base + len + 16u - start + 15u) & ~15u;          /* + 16: the windows read up to three words past a stream */
-        if (bytes > kPrefixStageBytes) bytes = 0u;
+        if (bytes > STAGE) bytes = 0u;
     };
     auto issue = [&](uint32_t b, uint32_t words_of_b) {
         uint32_t start, bytes; span(b, words_of_b, start, bytes);
@@ -822,7 +849,7 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
             const uint32_t buf = (b - b0) & 1u;
             async_proxy_fence();
             mbar_expect(bars + buf * 8u, bytes);
-            bulk_load(stages + buf * kPrefixStageBytes, a.data + start, bytes, bars + buf * 8u);
+            bulk_load(stages + buf * STAGE, a.data + start, bytes, bars + buf * 8u);
         }
     };
     uint32_t words = __ldg(a.hdr + (uint64_t)b0 * kLanes + lane);
@@ -830,7 +857,7 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
     issue(b0, words);
     if (b0 + 1u < b1) issue(b0 + 1u, words_next);
     uint32_t rb = b0 / g.CB, cb = b0 - rb * g.CB, phase_bits = 0;
-    float row_sum = 0.f;
+    float row_sum = 0.f, d[4] = {0.f, 0.f, 0.f, 0.f};     /* layout 0: the 8 row sums in lanes 0..7; layout 1: mma accumulators */
     for (uint32_t b = b0; b < b1; b++) {
         const uint32_t words_after = b + 2u < b1 ? __ldg(a.hdr + (uint64_t)(b + 2u) * kLanes + lane) : 0u;
         uint32_t start, bytes, total; span(b, words, start, bytes);
@@ -841,21 +868,37 @@ __global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(
                 return;
             }
             phase_bits ^= 1u << buf;
-            SmemWindow<MR> W; W.open(stages + buf * kPrefixStageBytes + (base - start) + 4u * before);
-            row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
+            SmemWindow<MR> W; W.open(stages + buf * STAGE + (base - start) + 4u * before);
+            if (LAYOUT == 0) row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
+            else prefix_block_layout1<SmemWindow<MR>, ELEM>(W, a, g, rb, cb, lane, table, sym, four, d);
         } else {
             GlobalWindow<MR> W; W.sym_ptr = reinterpret_cast<const uint8_t *>(tables + kTableWords);
             W.open(reinterpret_cast<const uint32_t *>(a.data + base) + before);
-            row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
+            if (LAYOUT == 0) row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
+            else prefix_block_layout1<GlobalWindow<MR>, ELEM>(W, a, g, rb, cb, lane, table, sym, four, d);
         }
         if (b + 2u < b1) issue(b + 2u, words_after);              /* the stage just decoded is free again (all lanes passed the block's last __syncwarp) */
         words = words_next; words_next = words_after;
         if (++cb == g.CB || b + 1u == b1) {                       /* the warp's share of this row group is complete */
-            if (lane < 8u) emit_flat(a, plan, rb * 8u + lane, w - plan.owner((uint64_t)rb * g.CB), row_sum);
-            row_sum = 0.f;
+            const uint32_t part = w - plan.owner((uint64_t)rb * g.CB);
+            if (LAYOUT == 0) { if (lane < 8u) emit_flat(a, plan, rb * 8u + lane, part, row_sum); }
+            else if ((lane & 3u) == 0u) { emit_flat(a, plan, rb * 16u + (lane >> 2), part, d[0]); emit_flat(a, plan, rb * 16u + (lane >> 2) + 8u, part, d[2]); }
+            row_sum = 0.f; d[0] = d[1] = d[2] = d[3] = 0.f;
             if (cb == g.CB) { cb = 0; rb++; }
         }
     }
+}
+
+template <int ELEM, bool XF32>
+__global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(const SegmentArgs a, const FlatPlan plan, const uint32_t four) {
+    prefix_ring_body<0, ELEM, XF32, kPrefixThreads, kPrefixStageBytes>(a, plan, four);
+}
+/* layout 1: a block is 16 x 512 (twice the stream), so half as many warps with stages twice as large; x is bf16 */
+constexpr uint32_t kPrefix1Threads = 512, kPrefix1StageBytes = 4608;
+constexpr uint32_t kPrefix1SmemBytes = 16416u + (kPrefix1Threads / 32u) * (2u * kPrefix1StageBytes + 256u + 16u);
+template <int ELEM>
+__global__ void __launch_bounds__(kPrefix1Threads, 1) prefix_ring_kernel_layout1(const SegmentArgs a, const FlatPlan plan, const uint32_t four) {
+    prefix_ring_body<1, ELEM, false, kPrefix1Threads, kPrefix1StageBytes>(a, plan, four);
 }
 
 /* ---- layout 0, small matrices of the decode step: one launch, activation prologue fused ------------------------------ */
@@ -1075,6 +1118,7 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K) {
     const Geometry g(M, K, layout);
     FlatPlan plan;
     if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
+    if (!g_disable_ring && layout == 1) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan); return plan.direct ? 1 : 2; }
     if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { make_cta_plan_layout2(g, sms, plan); return plan.direct ? 1 : 2; }
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
@@ -1102,6 +1146,18 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
         const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
         if (elem == kFp8) { if (a.x_bf16) prefix_ring_kernel_layout0<kFp8, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kFp8, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
         else { if (a.x_bf16) prefix_ring_kernel_layout0<kBf16, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kBf16, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
+        err = cudaGetLastError();
+        if (err == cudaSuccess && !plan.direct) {
+            finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
+            err = cudaGetLastError();
+        }
+        return err;
+    }
+    if (layout == 1 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
+        make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan);
+        const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
+        if (elem == kFp8) prefix_ring_kernel_layout1<kFp8><<<rgrid, kPrefix1Threads, kPrefix1SmemBytes, st>>>(a, plan, 4u);
+        else prefix_ring_kernel_layout1<kBf16><<<rgrid, kPrefix1Threads, kPrefix1SmemBytes, st>>>(a, plan, 4u);
         err = cudaGetLastError();
         if (err == cudaSuccess && !plan.direct) {
             finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
@@ -1141,6 +1197,8 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout1<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout1<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
