@@ -112,17 +112,21 @@ def run_reference(a, cfg):
     sec = statistics.mean(times)
     line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": a.gpus, "steps": steps, "warmup": min(a.warmup, 1),
             "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
-            "config": workload(a, cfg), "cpu_baseline": {"value": 1.0 / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what},
+            "config": workload(a, cfg, a.gpus, a.parallel == "tp"), "cpu_baseline": {"value": 1.0 / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what},
             "e2e": {"value": 1.0 / sec, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def workload(a, cfg, token_bytes=None, lm_head_bytes=None):
-    policy = "no flush: the compressed weights streamed per token and the lm_head matrix of the roofline leg are each larger than the 126 MB L2"
-    if token_bytes is not None:
-        policy = "no flush: weights streamed per token (%.2f GB) and the roofline kernel's matrix (lm_head, %.0f MB) exceed the 126 MB L2" % (token_bytes / 1e9, lm_head_bytes / 1e6)
+def workload(a, cfg, world=1, tp=False):
+    """The `config` object; identical in both arms so that their lines can be compared key by key."""
+    par = "1 GPU"
+    if world > 1:
+        par = ("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, NCCL all-reduce after o and down" % world if tp
+               else "replicas x%d (no data-path collective)" % world)
     return {"workload": f"{cfg.name}-architecture decoder, random init, NWC {a.elem} layout {a.layout}, batch 1, {a.prompt} random prompt ids, greedy decode as a CUDA graph",
-            "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "l2_policy": policy}
+            "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab,
+            "l2_policy": "no flush: the compressed weights streamed per token and the lm_head matrix of the roofline leg are each larger than the 126 MB L2",
+            "parallelism": par}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the lm_head kernel, from the ncu captures summarised
@@ -132,6 +136,7 @@ NCU_TRAFFIC = {("qwen3-0.6b", 0, "bf16"): 217.5e6, ("qwen3-0.6b", 2, "bf16"): 23
 
 def token_kernel_name(layout, elem):
     if layout == 0: return "prefix_ring_kernel_layout0"
+    if layout == 1: return "prefix_ring_kernel_layout1"
     if layout == 2 and elem == "bf16": return "ring_kernel_layout2"
     return "segment_kernel<layout %d, %s>" % (layout, elem)
 
@@ -307,8 +312,7 @@ def main():
     streams = 1 if tp else world          # sequences decoded at once
     line = {"metric": "decode_tokens_per_s", "value": streams * a.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
-            "config": dict(workload(a, cfg, weights.bytes_per_token(), w.bytes), parallelism=("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, NCCL all-reduce after o and down" % world if tp
-                                                 else "replicas x%d (no data-path collective)" % world) if world > 1 else "1 GPU"),
+            "config": workload(a, cfg, world, tp),
             "e2e": {"value": streams * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": a.steps * eng.launches_per_step, "launches_per_step": eng.launches_per_step,
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}

@@ -413,6 +413,12 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
 #ifndef NWC_RING_THREADS
 #define NWC_RING_THREADS 512
 #endif
+#ifndef NWC_RING_RESIDENT
+#define NWC_RING_RESIDENT 1
+#endif
+#ifndef NWC_RING_GRID_MULT
+#define NWC_RING_GRID_MULT 1
+#endif
 constexpr uint32_t kRingThreads = NWC_RING_THREADS, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES;
 constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
 constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes;
@@ -470,7 +476,7 @@ constexpr uint32_t kRingEntries = 2u * (kRingThreads / 32u);
 constexpr uint32_t kRingShareBytes = kRingEntries * 4u + kRingEntries * 16u * 4u;
 constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 
-__global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
+__global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
     extern __shared__ __align__(128) uint8_t ring_smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Geometry g(a.M, a.K, 2);
@@ -650,7 +656,7 @@ static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t
 #endif
 constexpr uint64_t kFinalizeSlots = NWC_FINALIZE_SLOTS;
 static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p) {
-    const uint64_t total = (uint64_t)g.groups * g.slots, ctas = (uint64_t)sms;
+    const uint64_t total = (uint64_t)g.groups * g.slots, ctas = (uint64_t)sms * NWC_RING_GRID_MULT;
     const uint64_t whole = ((g.groups + ctas - 1u) / ctas) * g.slots, cut = (total + ctas - 1u) / ctas + kFinalizeSlots;
     make_flat_plan(g, g.slots, ctas, p, whole <= cut);
 }
