@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="", help="time one token matvec alone: lm_head | qkv | o | gate_up | down | MxK (small case for ncu)")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"], help="N > 1: independent replicas (weak scaling) or tensor parallel with NCCL all-reduce (strong scaling)")
+    ap.add_argument("--tp-reduce", default="peer", choices=["peer", "nccl"], help="--parallel tp: sum partial outputs with this library's NVLink peer-memory kernel or with NCCL")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     return ap.parse_args()
 
@@ -121,7 +122,7 @@ def workload(a, cfg, world=1, tp=False):
     """The `config` object; identical in both arms so that their lines can be compared key by key."""
     par = "1 GPU"
     if world > 1:
-        par = ("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, NCCL all-reduce after o and down" % world if tp
+        par = ("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, partial sums added after o and down (%s)" % (world, "NVLink peer-memory kernel" if a.tp_reduce == "peer" else "NCCL all-reduce") if tp
                else "replicas x%d (no data-path collective)" % world)
     return {"workload": f"{cfg.name}-architecture decoder, random init, NWC {a.elem} layout {a.layout}, batch 1, {a.prompt} random prompt ids, greedy decode as a CUDA graph",
             "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab,
@@ -207,6 +208,7 @@ def finish(eng, dist):
     eng.graph = None
     gc.collect(); torch.cuda.synchronize()
     dist.barrier(); torch.cuda.synchronize()
+    eng.close()
     dist.destroy_process_group()
 
 
@@ -232,10 +234,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     tp = a.parallel == "tp" and world > 1
-    if tp: a.dependent_launch = 0         # NCCL kernels sit in the chain: keep plain stream order around them
+    if tp and a.tp_reduce == "nccl": a.dependent_launch = 0         # NCCL kernels sit in the chain: keep plain stream order around them
     if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=0, tp_rank=rank, tp_world=world)
-        eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD)
+        eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD, tp_reduce=a.tp_reduce)
     else:
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
         eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch))

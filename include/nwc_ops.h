@@ -81,9 +81,29 @@ int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const uint32_t *ba
                            const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K,
                            int elem, uint32_t splits);
 
-/* Status word of the kernels' bounded waits: 0, or 2 when a warp gave up waiting for a bulk copy (its rows are then
-   missing from y).  Synchronises the device; clear != 0 resets the word. */
+/* Status word of the kernels' bounded waits: 0, 2 when a warp gave up waiting for a bulk copy (its rows are then
+   missing from y), 3 when nwc_allreduce_add_rmsnorm gave up waiting for a peer rank.  Synchronises the device;
+   clear != 0 resets the word. */
 int nwc_kernel_status(int clear);
+
+/* ---- tensor-parallel decode on one node (no counterpart in the reference, which is single-GPU) ------------------------
+   Each rank allocates one exchange buffer (nwc_comm_alloc; device memory of nwc_comm_bytes(H) bytes, zeroed), exports it
+   as a 64-byte CUDA IPC handle, and opens the handles of the other ranks (nwc_comm_import; peer access is enabled on
+   first use).  Row-parallel matvecs (o, down) write their bf16 partial output into nwc_comm_slot(buffer, H, slot), slot 0
+   and 1 in turn.  nwc_allreduce_add_rmsnorm then is one kernel per rank: it announces the call to the peers, waits
+   (bounded) for theirs, adds the `world` partials of `slot` in rank order in fp32 with plain peer loads over NVLink,
+   and writes h_out = bf16(h_in + bf16(sum)) and xn = RMSNorm(h_out) * norm_w (H % 8 == 0, 16-byte aligned pointers,
+   h_out != h_in).  `buffers` is a host array of `world` device pointers: this rank's own buffer at [rank], the imported
+   ones elsewhere.  All ranks must make the same sequence of calls. */
+uint64_t nwc_comm_bytes(uint32_t H);
+int nwc_comm_alloc(void **buffer, uint32_t H);
+int nwc_comm_free(void *buffer);
+int nwc_comm_export(void *buffer, uint8_t *handle64);
+int nwc_comm_import(const uint8_t *handle64, void **peer_buffer);
+int nwc_comm_release(void *peer_buffer);
+uint16_t *nwc_comm_slot(void *buffer, uint32_t H, int slot);
+int nwc_allreduce_add_rmsnorm(void *stream, void *const *buffers, int rank, int world, int slot, const uint16_t *h_in,
+                              uint16_t *h_out, const uint16_t *norm_w, float eps, uint32_t H, uint16_t *xn);
 
 /* on = 0 routes every call through the kernels that load with plain vector loads instead of bulk-copy rings (A/B
    tests); on = 1 (default) restores the rings. */

@@ -51,6 +51,14 @@ _SIGNATURES = {
     "nwc_setup": (I, []),
     "nwc_kernel_status": (I, [I]),
     "nwc_set_ring_kernels": (None, [I]),
+    "nwc_comm_bytes": (U64, [U32]),
+    "nwc_comm_alloc": (I, [P, U32]),
+    "nwc_comm_free": (I, [P]),
+    "nwc_comm_export": (I, [P, P]),
+    "nwc_comm_import": (I, [P, P]),
+    "nwc_comm_release": (I, [P]),
+    "nwc_comm_slot": (P, [P, U32, I]),
+    "nwc_allreduce_add_rmsnorm": (I, [P, P, I, I, I, P, P, P, ctypes.c_float, U32, P]),
 }
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)            # AttributeError here = a library that does not implement the C-ABI

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "lib", "nwc_ops.so")
-SOURCES = ["nwc_abi.cu", "nwc_kernels.cu", "nwc_gather.cu", "nwc_encode.cu", "nwc_model.cu", "nwc_static.cu", "nwc_prefill.cu"]
+SOURCES = ["nwc_abi.cu", "nwc_kernels.cu", "nwc_gather.cu", "nwc_encode.cu", "nwc_model.cu", "nwc_static.cu", "nwc_prefill.cu", "nwc_comm.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared", "-Xcompiler", "-fPIC",
          "-Xcompiler", "-fvisibility=hidden"]
 

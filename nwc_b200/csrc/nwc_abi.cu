@@ -179,8 +179,8 @@ NWC_EXPORT int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, c
 NWC_EXPORT int nwc_setup(void) { return device_sms(); }
 
 NWC_EXPORT int nwc_kernel_status(int clear) {
-    const int a = read_kernel_status(clear != 0), b = read_prefill_status(clear != 0);
-    return a > b ? a : b;
+    const int a = read_kernel_status(clear != 0), b = read_prefill_status(clear != 0), c = read_comm_status(clear != 0);
+    return a > b ? (a > c ? a : c) : (b > c ? b : c);
 }
 
 /* Prefill: Y[T][ldy] = bf16(scale * (X[T][ldx] W^T) + bias) on the tcgen05 tensor cores, W decoded tile by tile.

@@ -53,6 +53,7 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K);
 
 cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy);
 int read_prefill_status(bool clear);
+int read_comm_status(bool clear);            /* 0, or 3 when a rank gave up waiting for its peers */
 cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids);
 cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);
 

@@ -10,6 +10,8 @@ Architectures: Qwen3 (per-head q/k RMSNorm, tied or untied embeddings) and Llama
 """
 from dataclasses import dataclass
 
+import ctypes
+
 import torch
 
 from . import _lib as L
@@ -112,18 +114,26 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None):
-        """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None."""
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="peer"):
+        """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None.
+        tp_reduce: "peer" sums the ranks' partial o / down outputs with this library's kernel over NVLink peer memory
+        (fused with the residual add and the RMSNorm that follow); "nccl" uses one NCCL all-reduce instead."""
         L.require_cuda()
         self.dependent_launch = bool(dependent_launch)
         self.tp_group, self.tp_world = tp_group, weights.tp_world
         if self.tp_world > 1 and tp_group is None: raise ValueError("sharded weights need the process group of their ranks")
+        if tp_reduce not in ("peer", "nccl"): raise ValueError("tp_reduce is 'peer' or 'nccl'")
+        self.peers = None
+        if self.tp_world > 1 and tp_reduce == "peer":
+            from .comm import PeerBuffers
+            self.peers = PeerBuffers(tp_group, weights.cfg.hidden)
         self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
         c = self.cfg
         bf = lambda n: torch.zeros(n, dtype=torch.bfloat16, device=device)
         pad32 = lambda n: (n + 31) // 32 * 32
         self.h, self.h2 = bf(pad32(c.hidden)), bf(pad32(c.hidden))
         self.xtmp = bf(pad32(max(c.hidden, c.intermediate)))
+        self.xn = bf(pad32(c.hidden))                               # normalised activations (peer-reduce path)
         self.qkv, self.attn, self.proj, self.proj2 = bf(c.qkv_rows), bf(pad32(c.n_q * c.head_dim)), bf(pad32(c.hidden)), bf(pad32(c.hidden))
         self.gu = bf(2 * c.intermediate)
         self.logits = bf(c.vocab)                                   # this rank's vocabulary rows
@@ -147,9 +157,10 @@ class DecodeEngine:
     def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None):
         """y = W x with the activation prologue the mode names (0: x given; 1: x = RMSNorm(h_in + delta), h_out updated;
         2: x = SwiGLU(gate_up)), through nwc_linear_fused."""
+        out = y if isinstance(y, ctypes.c_void_p) else L.ptr(y)      # a raw device pointer: this rank's slot of the exchange buffer
         err = L.lib.nwc_linear_fused(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
                                      L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), self.cfg.eps, L.ptr(gate_up), L.ptr(self.xtmp), None, L.ptr(w.scale),
-                                     L.ptr(w.scratch), L.ptr(y), w.n, w.block, w.in_features, w.code)
+                                     L.ptr(w.scratch), out, w.n, w.block, w.in_features, w.code)
         if err: raise RuntimeError(f"nwc_linear_fused error {err}")
         self._count += L.lib.nwc_linear_launches(w.n, w.in_features, w.code, mode)
 
@@ -178,7 +189,37 @@ class DecodeEngine:
             L.lib.nwc_set_dependent_launch(0)
         self.launches_per_step = self._count
 
+    def _forward_peer(self, c, w, st, e, h, h_next):
+        """Tensor-parallel step with the partial sums exchanged through peer memory: every linear takes a ready x, the
+        kernel after o / down adds the ranks' partials, the residual and applies the next RMSNorm."""
+        self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(h),
+                                     e.n, e.block, e.in_features, e.code), "nwc_gather")
+        self._check(L.lib.nwc_add_rmsnorm(st(), L.ptr(h), None, L.ptr(h), L.ptr(w.layers[0]["in_norm"]), c.eps, c.hidden, L.ptr(self.xn), None), "nwc_add_rmsnorm")
+        for i, l in enumerate(w.layers):
+            self._linear(l["qkv"], self.xn, self.qkv)
+            self._check(L.lib.nwc_attention_decode(st(), L.ptr(self.qkv), L.ptr(l["q_norm"]), L.ptr(l["k_norm"]), L.ptr(self.cos), L.ptr(self.sin),
+                                                   L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
+                                                   c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
+            self._linear(l["o"], self.attn, self.peers.slot(0))
+            self.peers.allreduce_add_rmsnorm(0, h, h_next, l["post_norm"], c.eps, self.xn); self._count += 1
+            h, h_next = h_next, h
+            self._linear(l["gate_up"], self.xn, self.gu)
+            self._linear(l["down"], None, self.peers.slot(1), mode=2, gate_up=self.gu)
+            nxt = w.layers[i + 1]["in_norm"] if i + 1 < len(w.layers) else w.final_norm
+            self.peers.allreduce_add_rmsnorm(1, h, h_next, nxt, c.eps, self.xn); self._count += 1
+            h, h_next = h_next, h
+        self._linear(w.lm_head, self.xn, self.logits)
+        import torch.distributed as dist
+        dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.tp_group)
+        self._count += 1
+        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits_all), c.vocab * self.tp_world, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
+
+    def close(self):
+        """Release the exchange buffers (all ranks: after synchronising and a barrier)."""
+        if self.peers is not None: self.peers.close(); self.peers = None
+
     def _forward(self, c, w, st, e, h, h_next):
+        if self.peers is not None: return self._forward_peer(c, w, st, e, h, h_next)
         self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(h),
                                      e.n, e.block, e.in_features, e.code), "nwc_gather")
         delta = None

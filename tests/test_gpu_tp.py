@@ -1,7 +1,8 @@
 """Tensor-parallel decode on two GPUs (skipped with fewer): the sharded engine must follow the single-GPU engine
 token for token under teacher forcing, apart from steps where the single-GPU top-2 logits are within bf16 resolution
-(row-parallel partial sums are rounded to bf16 before the all-reduce, so the summation differs).  Ranks are child
-processes; NVLS is off so a failing rank cannot disturb its peer's GPU."""
+(row-parallel partial sums are rounded to bf16 before the all-reduce, so the summation differs).  Both reductions
+run: this library's kernel over NVLink peer memory (plain peer loads) and NCCL.  Ranks are child processes; NVLS is off
+so a failing rank cannot disturb its peer's GPU."""
 import os
 import subprocess
 import sys
@@ -21,26 +22,34 @@ torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 cfg = DecoderConfig("tiny-tp", 2, 256, 1024, 4, 2, 64, 2048, True, True)
 ref = DecodeEngine(DecoderWeights.synthetic(cfg, layout=0, seed=3), max_len=96)
-tp = DecodeEngine(DecoderWeights.synthetic(cfg, layout=0, seed=3, tp_rank=rank, tp_world=world), max_len=96, tp_group=dist.group.WORLD)
+shards = DecoderWeights.synthetic(cfg, layout=0, seed=3, tp_rank=rank, tp_world=world)
 prompt = list(range(5, 17))
 ref.prefill(prompt); want = ref.generate(32).tolist()
 seq = prompt + want
-ref.reset(); tp.reset(); agree = close = 0
-for t in range(len(seq) - 1):
-    ref.cur.fill_(seq[t]); tp.cur.fill_(seq[t]); ref.forward_token(); tp.forward_token()
-    a, b = ref.logits.float(), tp.logits_all.float()
-    assert (a - b).abs().max().item() <= 0.05 * a.abs().max().item() + 0.05, t
-    if int(ref.cur) == int(tp.cur): agree += 1
-    else:
-        top = a.topk(2).values
-        assert (top[0] - top[1]).item() <= 2.0 ** -6 * abs(top[0].item()) + 1e-3, (t, top)
-        close += 1
-assert agree >= len(seq) - 1 - 4, (agree, close)
-tp.capture(); tp.prefill(prompt); replay = tp.generate(16).tolist()
-tp.graph = None; tp.prefill(prompt); eager = tp.generate(16).tolist()
-assert replay == eager
-toks = torch.tensor(replay, device="cuda"); other = toks.clone(); dist.broadcast(other, 0)
-assert torch.equal(toks, other)                       # every rank decodes the same sequence
+sequences = {}
+for how, pdl in (("peer", True), ("peer", False), ("nccl", False)):        # this library's NVLink reduce (with and without dependent launch), NCCL
+    tp = DecodeEngine(shards, max_len=96, tp_group=dist.group.WORLD, tp_reduce=how, dependent_launch=pdl)
+    ref.reset(); tp.reset(); agree = close = 0
+    for t in range(len(seq) - 1):
+        ref.cur.fill_(seq[t]); tp.cur.fill_(seq[t]); ref.forward_token(); tp.forward_token()
+        a, b = ref.logits.float(), tp.logits_all.float()
+        assert (a - b).abs().max().item() <= 0.05 * a.abs().max().item() + 0.05, (how, t)
+        if int(ref.cur) == int(tp.cur): agree += 1
+        else:
+            top = a.topk(2).values
+            assert (top[0] - top[1]).item() <= 2.0 ** -6 * abs(top[0].item()) + 1e-3, (how, t, top)
+            close += 1
+    assert agree >= len(seq) - 1 - 4, (how, agree, close)
+    tp.capture(); tp.prefill(prompt); replay = tp.generate(16).tolist()
+    tp.graph = None; tp.prefill(prompt); eager = tp.generate(16).tolist()
+    assert replay == eager, how
+    toks = torch.tensor(replay, device="cuda"); other = toks.clone(); dist.broadcast(other, 0)
+    assert torch.equal(toks, other), how                  # every rank decodes the same sequence
+    sequences[(how, pdl)] = replay
+    from nwc_b200 import _lib as L
+    assert L.lib.nwc_kernel_status(1) == 0, how           # no rank gave up waiting for a peer
+    torch.cuda.synchronize(); dist.barrier(); tp.close()
+assert sequences[("peer", True)] == sequences[("peer", False)]
 dist.destroy_process_group()
 print("TP OK", rank, agree, close)
 """
