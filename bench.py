@@ -194,8 +194,21 @@ def kernel_only(a, cfg):
         dense = [synthetic_matrix(M, K, 1 + i).cuda() for i in range(dense_copies)]
         dense_ms = timed(lambda i: torch.nn.functional.linear(x[:K], dense[i]), dense_copies)
         del dense
+    # fp8: the library's uncompressed fp8 weight-only matvec (one byte per weight) on the same quantised matrix
+    native_fp8_ms = None
+    if a.elem == "fp8" and a.steps > 1:
+        from nwc_b200.weight import quantize_fp8
+        n8 = max(1, min(16, -(-(320 << 20) // (M * K))))
+        q8 = [quantize_fp8(synthetic_matrix(M, K, 1 + i)) for i in range(n8)]
+        xf, y8 = x.float().contiguous(), torch.empty(M, dtype=torch.bfloat16, device="cuda")
+        def native(i):
+            err = L.lib.nwc_ref_fp8(L.stream(), L.ptr(q8[i][0].view(torch.uint8)), L.ptr(q8[i][1]), L.ptr(xf), L.ptr(y8), M, K)
+            if err: raise RuntimeError(f"nwc_ref_fp8 error {err}")
+        native_fp8_ms = timed(native, n8)
+        del q8
     print(json.dumps({"kernel": f"token matvec {M}x{K} {a.elem} layout {a.layout}", "launches_per_call": L.lib.nwc_linear_launches(nw.n, K, nw.code, -1), "us_per_call": ms * 1e3,
                       "bytes_per_call": nw.bytes, "bits_per_weight": 8 * nw.bytes / nw.n, "dense_bf16_gemv_us": None if dense_ms is None else dense_ms * 1e3,
+                      "native_fp8_matvec_us": None if native_fp8_ms is None else native_fp8_ms * 1e3,
                       "roofline": {"bound": "hbm", "achieved": nw.bytes / ms / 1e6, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": nw.bytes / ms / 1e6 / peak},
                       "note": "%d calls on %d rotating copies replayed as one CUDA graph, CUDA events around the replay (a call includes its finalize launch when it needs one)" % (reps, copies)}))
 
