@@ -174,7 +174,10 @@ void nwc_set_dependent_launch(int on);
 /* One token of grouped-query attention.  qkv = [n_q | n_kv | n_kv] heads x head_dim (bf16) of the token at position
    *pos; q_norm / k_norm: per-head RMSNorm weights (bf16[head_dim]) or NULL; cos_t / sin_t: bf16[max positions][head_dim];
    k_cache / v_cache: bf16[n_kv][max_len][head_dim], appended at *pos; out: bf16[n_q * head_dim].
-   *status is set to 1 (and nothing is written) when *pos is outside [0, max_len). */
+   *status is set to 1 (and nothing is written) when *pos is outside [0, max_len).
+   With dependent launch on, *pos and the cache rows below it are read while the kernel before this one may still run:
+   they must come from work that completed earlier (in the decode loop: from the previous token, whose last kernel is
+   followed by an ordinary launch, the embedding gather). */
 int nwc_attention_decode(void *stream, const uint16_t *qkv, const uint16_t *q_norm, const uint16_t *k_norm,
                          const uint16_t *cos_t, const uint16_t *sin_t, uint16_t *k_cache, uint16_t *v_cache,
                          const int32_t *pos, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_len, float eps,

@@ -86,18 +86,29 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const uint16_t *_
     float *qs = sm, *ks = sm + hd, *scores = sm + 2 * hd;          /* q, current k (fp32), scores [max_len] */
     __shared__ float red[32];
     const uint32_t head = blockIdx.x, kvh = head / (n_q / n_kv), tid = threadIdx.x;
-    /* the norm weights do not depend on earlier kernels: fetch them while the predecessor finishes */
+    /* Before the dependency wait: everything that the kernels of this token do not write.  The norm weights and the
+       rotary tables are constants.  The position and the cache rows below it were written while earlier tokens were
+       decoded, and the step's first kernel (the embedding gather) is an ordinary launch, so all of that is complete
+       before any kernel of this token starts.  The cached rows are pulled towards L1 for the score and value loops. */
     float qw = 0.f, kw = 0.f;
     if (q_norm && tid < hd) { qw = bf2f(q_norm[tid]); kw = bf2f(k_norm[tid]); }
+    const int32_t pos = *pos_ptr;
+    const bool pos_ok = pos >= 0 && (uint32_t)pos < max_len;
+    float rc = 0.f, rs = 0.f;
+    if (pos_ok) {
+        if (tid < hd) { rc = bf2f(cos_t[(uint64_t)pos * hd + tid]); rs = bf2f(sin_t[(uint64_t)pos * hd + tid]); }
+        const uint32_t lines_per_row = (hd * 2u + 127u) >> 7, lines = (uint32_t)pos * lines_per_row;
+        const uint8_t *kbase = reinterpret_cast<const uint8_t *>(k_cache + (uint64_t)kvh * max_len * hd), *vbase = reinterpret_cast<const uint8_t *>(v_cache + (uint64_t)kvh * max_len * hd);
+        for (uint32_t i = tid; i < lines && i < 1024u; i += blockDim.x) {      /* up to 128 KB of each: what L1 can hold */
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(kbase + (uint64_t)i * 128u));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(vbase + (uint64_t)i * 128u));
+        }
+    }
     dependency_sync();
-    /* one round trip for everything that needs no position, a second one for the rotary row */
+    if (!pos_ok) { if (tid == 0) atomicExch(status, 1); return; }
     const uint16_t *qp = qkv + (uint64_t)head * hd, *kp = qkv + (uint64_t)(n_q + kvh) * hd, *vp = qkv + (uint64_t)(n_q + n_kv + kvh) * hd;
     float qv = 0.f, kv = 0.f;
     if (tid < hd) { qv = bf2f(qp[tid]); kv = bf2f(kp[tid]); }
-    const int32_t pos = *pos_ptr;
-    if (pos < 0 || (uint32_t)pos >= max_len) { if (tid == 0) atomicExch(status, 1); return; }
-    float rc = 0.f, rs = 0.f;
-    if (tid < hd) { rc = bf2f(cos_t[(uint64_t)pos * hd + tid]); rs = bf2f(sin_t[(uint64_t)pos * hd + tid]); }
     /* per-head RMSNorm of q and k (Qwen3), then rotary embedding with bf16 rounding per operation */
     if (q_norm) {
         const float qi = rsqrtf(block_sum(qv * qv, red) / (float)hd + eps), ki = rsqrtf(block_sum(kv * kv, red) / (float)hd + eps);
