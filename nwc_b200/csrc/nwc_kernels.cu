@@ -361,23 +361,23 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
                 xs[i] = i < K ? bf16_round_nan(bf16_to_float(in.norm_w[i]) * bf16_rt(bf16_to_float(xs[i]) * inv)) : (uint16_t)0;
         }
     } else if (in.mode == kInputSwiglu) {
-        if (vec) {
-            const uint4 *gate = reinterpret_cast<const uint4 *>(in.gate_up), *up = reinterpret_cast<const uint4 *>(in.gate_up + K);
-#pragma unroll 2
-            for (uint32_t c = tid; c < chunks; c += THREADS) {
-                uint4 o = make_uint4(0u, 0u, 0u, 0u);
-                if (c < live) {
-                    const uint4 gv = gate[c], uv = up[c];
-                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-                    uint32_t ow[4];
+        if (vec) {                                               /* four values per step: the exponentials spread evenly over the threads */
+            const uint2 *gate = reinterpret_cast<const uint2 *>(in.gate_up), *up = reinterpret_cast<const uint2 *>(in.gate_up + K);
+#pragma unroll 3
+            for (uint32_t c = tid; c < (cols >> 2); c += THREADS) {
+                uint2 o = make_uint2(0u, 0u);
+                if (c < (K >> 2)) {
+                    const uint2 gv = gate[c], uv = up[c];
+                    const uint32_t gw[2] = {gv.x, gv.y}, uw[2] = {uv.x, uv.y};
+                    uint32_t ow[2];
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
+                    for (int k = 0; k < 2; k++) {
                         const float g0 = bf16_lo(gw[k]), g1 = bf16_hi(gw[k]);
                         ow[k] = bf16_pack(bf16_rt(g0 / (1.f + __expf(-g0))) * bf16_lo(uw[k]), bf16_rt(g1 / (1.f + __expf(-g1))) * bf16_hi(uw[k]));
                     }
-                    o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    o = make_uint2(ow[0], ow[1]);
                 }
-                sts128(xs_addr + c * 16u, o);
+                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xs_addr + c * 8u), "r"(o.x), "r"(o.y) : "memory");
             }
         } else {
             for (uint32_t i = tid; i < cols; i += THREADS) {
@@ -667,7 +667,10 @@ static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p) {
    bit windows refill from shared memory with 32-bit addresses and no lane ever waits for a 4-byte global load.  Raw
    rows still come straight from global memory (coalesced 512 B per row and warp, two rows ahead).
    A block whose stream does not fit a stage (escape-heavy data) is decoded through the global-memory window instead. */
-constexpr uint32_t kPrefixThreads = 1024, kPrefixStageBytes = 2560, kPrefixWarpBytes = 2u * kPrefixStageBytes + 256u + 16u;
+#ifndef NWC_PREFIX_THREADS
+#define NWC_PREFIX_THREADS 1024
+#endif
+constexpr uint32_t kPrefixThreads = NWC_PREFIX_THREADS, kPrefixStageBytes = 2560, kPrefixWarpBytes = 2u * kPrefixStageBytes + 256u + 16u;
 constexpr uint32_t kPrefixSmemBytes = 16416u + (kPrefixThreads / 32u) * kPrefixWarpBytes;
 
 /* bit window over a stream staged in shared memory; table look-ups form their address with one shift and one IMAD */
@@ -743,9 +746,18 @@ struct GlobalWindow : BitWindow<MAX_RANK> {
 /* One layout-0 block: 8 rows x 16 columns per lane.  Even rows enter the mma as the "row r" half of the A fragment, odd
    rows as the "row r + 8" half (both rows meet the same columns of x); after two rows the diagonal of D holds the lane
    quads' dot products. */
+/* the low bytes of the first two rows of a lane's 8 x 16 cell of block (rb, cb): constants, so a caller may fetch them early */
+template <int ELEM>
+__device__ __forceinline__ void first_raw_rows(const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane, uint4 &raw0, uint4 &raw1) {
+    const uint32_t row0 = rb * 8u, col0 = cb * kBlockCols + lane * 16u, stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
+    const bool col_ok = col0 < g.K16;
+    const uint8_t *rawp = a.low + (uint64_t)row0 * stride + (ELEM == kFp8 ? (col0 >> 1) : col0);
+    raw0 = raw_row16<ELEM>(rawp, col_ok && row0 < g.M); raw1 = raw_row16<ELEM>(rawp + stride, col_ok && row0 + 1u < g.M);
+}
+
 template <class WIN, int ELEM, bool XF32>
 __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane,
-                                                      uint32_t table, uint32_t sym, uint32_t four, float *stash, uint32_t xs = 0u) {
+                                                      uint32_t table, uint32_t sym, uint32_t four, float *stash, uint32_t xs = 0u, const uint4 *early_rows = nullptr) {
     const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 8u, col0 = cb * kBlockCols + lane * 16u;
     const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
     const bool col_ok = col0 < g.K16, diag = q == (r >> 1);
@@ -754,7 +766,9 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
     else if (!XF32 && xs) { xa.load_shared(xs + col0 * 2u); xb.load_shared(xs + col0 * 2u + 16u); }     /* x staged by the CTA */
     else { xa.load(a.x, col0); xb.load(a.x, col0 + 8u); }
     const uint8_t *rawp = a.low + (uint64_t)row0 * stride + (ELEM == kFp8 ? (col0 >> 1) : col0);
-    uint4 raw0 = raw_row16<ELEM>(rawp, col_ok && row0 < g.M), raw1 = raw_row16<ELEM>(rawp + stride, col_ok && row0 + 1u < g.M);
+    uint4 raw0, raw1;
+    if (early_rows) { raw0 = early_rows[0]; raw1 = early_rows[1]; }
+    else { raw0 = raw_row16<ELEM>(rawp, col_ok && row0 < g.M); raw1 = raw_row16<ELEM>(rawp + stride, col_ok && row0 + 1u < g.M); }
 #pragma unroll 1
     for (uint32_t rp = 0; rp < 4u; rp++) {
         const uint4 rawA = raw0, rawB = raw1;
@@ -920,8 +934,11 @@ constexpr uint32_t kSmallThreads = 256, kSmallWarps = kSmallThreads / 32u;
 /* warps that share one row group: the smallest power of two that covers its column blocks (at most the CTA) */
 __host__ __device__ static inline uint32_t small_group_warps(uint32_t CB) { return CB > 4u ? 8u : (CB > 2u ? 4u : (CB > 1u ? 2u : 1u)); }
 
+#ifndef NWC_SMALL_RESIDENT
+#define NWC_SMALL_RESIDENT 2
+#endif
 template <int ELEM>
-__global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
+__global__ void __launch_bounds__(kSmallThreads, NWC_SMALL_RESIDENT) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
     extern __shared__ __align__(128) uint8_t small_smem[];
     uint32_t *tables = reinterpret_cast<uint32_t *>(small_smem);
@@ -976,6 +993,10 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
     /* the weights do not depend on the kernel before this one: start the copy of this warp's first stream and pull its
        raw rows towards L2 before anything else, so that both overlap the table staging, the wait and the prologue */
     prefetch_block(blockIdx.x, j, 0u);
+    /* the first two raw rows of that block as well: the decode loop then starts without a trip to L2 */
+    uint4 early_rows[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    const uint32_t early_block = next.valid ? next.b : 0xFFFFFFFFu;
+    if (next.valid) first_raw_rows<ELEM>(a, g, next.pass * per_pass + my_group, next.cb, lane, early_rows[0], early_rows[1]);
     stage_tables(tables, a.lut, tid, kSmallThreads);
     stage_norm_weight<kSmallThreads>(in, a.K, nw);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -999,7 +1020,8 @@ __global__ void __launch_bounds__(kSmallThreads, 2) small_kernel_layout0(const S
                     phases ^= 1u << which;
                     if (landed) {
                         SmemWindow<MR> W; W.open(stage0 + which * kPrefixStageBytes + (base - cur.start) + 4u * before);
-                        row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, false>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
+                        row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, false>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr,
+                                                                                     cur.b == early_block ? early_rows : nullptr);
                     }
                 } else {
                     GlobalWindow<MR> W; W.sym_ptr = reinterpret_cast<const uint8_t *>(tables + kTableWords);
