@@ -166,10 +166,11 @@ def kernel_only(a, cfg):
     nw = first
     x = torch.randn((K + 31) // 32 * 32, device="cuda").to(torch.bfloat16); x[K:] = 0
     y = torch.empty(M, dtype=torch.bfloat16, device="cuda")
-    def launch(w):
-        err = L.lib.nwc_linear_x16(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(x), None, L.ptr(w.scale),
-                                   L.ptr(w.scratch), L.ptr(y), w.n, w.block, K, w.code)
-        if err: raise RuntimeError(f"nwc_linear_x16 error {err}")
+    xtmp = torch.zeros_like(x)
+    def launch(w):                           # the decode loop's entry point with a ready x (mode 0): same kernels as inside a decode step
+        err = L.lib.nwc_linear_fused(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), 0, L.ptr(x), None, None, None, None,
+                                     1e-6, None, L.ptr(xtmp), None, L.ptr(w.scale), L.ptr(w.scratch), L.ptr(y), w.n, w.block, K, w.code)
+        if err: raise RuntimeError(f"nwc_linear_fused error {err}")
     reps = max(copies, 8)
     def timed(call, n_copies):
         side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
@@ -206,7 +207,7 @@ def kernel_only(a, cfg):
             if err: raise RuntimeError(f"nwc_ref_fp8 error {err}")
         native_fp8_ms = timed(native, n8)
         del q8
-    print(json.dumps({"kernel": f"token matvec {M}x{K} {a.elem} layout {a.layout}", "launches_per_call": L.lib.nwc_linear_launches(nw.n, K, nw.code, -1), "us_per_call": ms * 1e3,
+    print(json.dumps({"kernel": f"token matvec {M}x{K} {a.elem} layout {a.layout}", "launches_per_call": L.lib.nwc_linear_launches(nw.n, K, nw.code, 0), "us_per_call": ms * 1e3,
                       "bytes_per_call": nw.bytes, "bits_per_weight": 8 * nw.bytes / nw.n, "dense_bf16_gemv_us": None if dense_ms is None else dense_ms * 1e3,
                       "native_fp8_matvec_us": None if native_fp8_ms is None else native_fp8_ms * 1e3,
                       "roofline": {"bound": "hbm", "achieved": nw.bytes / ms / 1e6, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": nw.bytes / ms / 1e6 / peak},
