@@ -7,7 +7,7 @@
  *     [64, 64+4W)   one arrival word per rank r: the last call number rank r has announced to this rank
  *     [256, ...)    two partial vectors ("slots") of H bf16 values, written by this rank's matvec kernels
  *
- * Call n of every rank: announce n to all peers (store into their arrival words, after a system-scope fence so that the
+ * Call n of every rank (one cluster of 8 CTAs; CTA 0 does the signalling): announce n to all peers (store into their arrival words, after a system-scope fence so that the
  * partial written by the preceding matvec is visible), wait until every peer has announced n, read all W partials with
  * plain peer loads (no multicast, no multimem), add them in rank order in fp32 - so every rank gets the same bits - and
  * finish with h_out = bf16(h_in + bf16(sum)), x = RMSNorm(h_out) * w.  The o projection uses slot 0 and the down
@@ -18,6 +18,7 @@
  */
 #include <cstdint>
 #include <cuda_runtime.h>
+#include <cooperative_groups.h>
 #include "../../include/nwc_ops.h"
 #include "nwc_launch.h"
 
@@ -44,38 +45,48 @@ __device__ __forceinline__ uint4 load_peer(const uint8_t *p) {          /* never
     return v;
 }
 
-__global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(const CommPeers peers, int rank, int world, uint32_t slot_offset, const uint16_t *h_in,
-                                                                     uint16_t *h_out, const uint16_t *__restrict__ norm_w, float eps, uint32_t H, uint16_t *xn) {
-    __shared__ float red[32];
-    __shared__ uint32_t call_number;
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+/* One cluster of kCommCtas CTAs per rank: every CTA owns 1 / kCommCtas of the vector, so the peer loads run from
+   several SMs at once; the sum of squares of the RMSNorm crosses the cluster through distributed shared memory. */
+constexpr uint32_t kCommCtas = 8, kCommThreads = 256;
+
+__global__ void __launch_bounds__(kCommThreads, 1) allreduce_add_rmsnorm_kernel(const CommPeers peers, int rank, int world, uint32_t slot_offset, const uint16_t *h_in,
+                                                                              uint16_t *h_out, const uint16_t *__restrict__ norm_w, float eps, uint32_t H, uint16_t *xn) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float red[kCommThreads / 32u];
+    __shared__ float cta_squares[kCommCtas];       /* CTA 0's copy collects every CTA's sum of squares */
+    __shared__ uint32_t call_number;               /* CTA 0's copy is the one the cluster reads */
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, cta = cluster.block_rank(), ctas = cluster.num_blocks();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");                 /* this rank's partial is complete */
     uint8_t *mine = peers.buf[rank];
-    if (tid == 0) {
-        volatile uint32_t *counter = reinterpret_cast<volatile uint32_t *>(mine);
-        const uint32_t n = *counter + 1u;
-        *counter = n; call_number = n;
-    }
-    __syncthreads();
-    const uint32_t n = call_number;
-    bool arrived = true;
-    if (tid < (uint32_t)world && tid != (uint32_t)rank) {
-        __threadfence_system();
-        *reinterpret_cast<volatile uint32_t *>(peers.buf[tid] + 64u + 4u * (uint32_t)rank) = n;
-        const volatile uint32_t *word = reinterpret_cast<const volatile uint32_t *>(mine + 64u + 4u * tid);
-        uint32_t polls = 0;
-        while ((int32_t)(*word - n) < 0) {
-            if (++polls > kCommPolls) { arrived = false; break; }
-            __nanosleep(64);
+    if (cta == 0) {                                                     /* CTA 0 talks to the other ranks */
+        if (tid == 0) {
+            volatile uint32_t *counter = reinterpret_cast<volatile uint32_t *>(mine);
+            const uint32_t n = *counter + 1u;
+            *counter = n; call_number = n;
         }
-        __threadfence_system();
+        __syncthreads();
+        const uint32_t n = call_number;
+        bool arrived = true;
+        if (tid < (uint32_t)world && tid != (uint32_t)rank) {
+            __threadfence_system();
+            *reinterpret_cast<volatile uint32_t *>(peers.buf[tid] + 64u + 4u * (uint32_t)rank) = n;
+            const volatile uint32_t *word = reinterpret_cast<const volatile uint32_t *>(mine + 64u + 4u * tid);
+            uint32_t polls = 0;
+            while ((int32_t)(*word - n) < 0) {
+                if (++polls > kCommPolls) { arrived = false; break; }
+                __nanosleep(64);
+            }
+            __threadfence_system();
+        }
+        if (!__syncthreads_and(arrived) && tid == 0) atomicExch(&g_comm_status, kStatusPeerTimeout);
     }
-    if (!__syncthreads_and(arrived) && tid == 0) atomicExch(&g_comm_status, kStatusPeerTimeout);
-    /* sum of the partials in rank order, residual add, sum of squares */
-    const uint32_t chunks = H >> 3;
+    cluster.sync();                                                     /* every peer's partial is complete (or the wait ran out) */
+    /* this CTA's part of the vector: sum of the partials in rank order, residual add, sum of squares */
+    const uint32_t chunks = H >> 3, c0 = (uint32_t)((uint64_t)chunks * cta / ctas), c1 = (uint32_t)((uint64_t)chunks * (cta + 1u) / ctas);
     float ss = 0.f;
-    for (uint32_t c = tid; c < chunks; c += blockDim.x) {
+    for (uint32_t c = c0 + tid; c < c1; c += kCommThreads) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         uint4 part[kCommMaxRanks];
 #pragma unroll
@@ -104,10 +115,19 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(const CommP
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (lane == 0) red[warp] = ss;
     __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (uint32_t i = 0; i < kCommThreads / 32u; i++) t += red[i];
+        cluster.map_shared_rank(cta_squares, 0)[cta] = t;               /* into CTA 0's shared memory */
+    }
+    cluster.sync();
     float tot = 0.f;
-    for (uint32_t i = 0; i < (blockDim.x >> 5); i++) tot += red[i];
+    {
+        const float *all = cluster.map_shared_rank(cta_squares, 0);
+        for (uint32_t i = 0; i < ctas; i++) tot += all[i];              /* same order in every CTA */
+    }
     const float inv = rsqrtf(tot / (float)H + eps);
-    for (uint32_t c = tid; c < chunks; c += blockDim.x) {               /* each thread re-reads the chunks it wrote itself */
+    for (uint32_t c = c0 + tid; c < c1; c += kCommThreads) {            /* each thread re-reads the chunks it wrote itself */
         const uint4 hv = *(reinterpret_cast<const uint4 *>(h_out) + c), wv = __ldg(reinterpret_cast<const uint4 *>(norm_w) + c);
         const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
         uint32_t ow[4];
@@ -116,6 +136,7 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(const CommP
             ow[k] = f2bf(bf2f(ww[k] & 0xFFFFu) * bfround(bf2f(hw[k] & 0xFFFFu) * inv)) | (f2bf(bf2f(ww[k] >> 16) * bfround(bf2f(hw[k] >> 16) * inv)) << 16);
         *(reinterpret_cast<uint4 *>(xn) + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
+    cluster.sync();                                                     /* CTA 0's shared memory stays alive until everybody has read it */
 }
 
 uint64_t slot_bytes(uint32_t H) { return ((uint64_t)H * 2u + 255u) & ~255ull; }
@@ -174,10 +195,12 @@ NWC_EXPORT int nwc_allreduce_add_rmsnorm(void *stream, void *const *buffers, int
     CommPeers peers{};
     for (int r = 0; r < world; r++) { if (!buffers[r]) return -1; peers.buf[r] = static_cast<uint8_t *>(buffers[r]); }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1); cfg.blockDim = dim3(H >= 8192 ? 1024 : 512); cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = dependent_launch() ? 1 : 0;
+    cfg.gridDim = dim3(kCommCtas); cfg.blockDim = dim3(kCommThreads); cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCommCtas; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = dependent_launch() ? 2 : 1;
     return (int)cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel, peers, rank, world, (uint32_t)((slot & 1) * slot_bytes(H)), h_in, h_out, norm_w, eps, H, xn);
 }

@@ -1,5 +1,5 @@
-"""The tensor-parallel reduction kernel on one GPU: with a single rank it must equal the plain add + RMSNorm kernel bit
-for bit, with two "ranks" that are two local buffers it must add both partials, and a peer that never announces itself
+"""The tensor-parallel reduction kernel on one GPU: with a single rank it must equal the plain add + RMSNorm kernel (the
+residual bit for bit, the normalised vector to one bf16 step), with two "ranks" that are two local buffers it must add both partials, and a peer that never announces itself
 must end in status 3 after the bounded wait - no hang, the context stays usable."""
 import ctypes
 
@@ -50,7 +50,10 @@ def test_single_rank_equals_add_rmsnorm(H):
             want_h, want_x = torch.zeros_like(h), torch.zeros_like(h)
             assert L.lib.nwc_add_rmsnorm(L.stream(), L.ptr(h), L.ptr(part), L.ptr(want_h), L.ptr(w), 1e-6, H, L.ptr(want_x), None) == 0
             torch.cuda.synchronize()
-            assert torch.equal(h_out, want_h) and torch.equal(xn, want_x)
+            assert torch.equal(h_out, want_h)
+            # the sum of squares is added in a different order (eight CTAs): the normalised vector may differ by one bf16 step
+            assert ((xn.float() - want_x.float()).abs() <= 2.0 ** -7 * want_x.float().abs() + 1e-30).all()
+            assert (xn != want_x).float().mean().item() < 0.02
         assert L.lib.nwc_kernel_status(1) == 0
     finally:
         L.lib.nwc_comm_free(ctypes.c_void_p(buf))
