@@ -21,6 +21,7 @@
  * Interfaces replaced (reference: csrc/nwc_ops.cu): kern_block 446-550, kern_block1 632-703, kern_block2 884-981,
  * kern_f32_to_bf16_bias 553-565.
  */
+#include <cooperative_groups.h>
 #include "nwc_decode.cuh"
 #include "nwc_async.cuh"
 #include "nwc_launch.h"
@@ -413,12 +414,7 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
 #ifndef NWC_RING_THREADS
 #define NWC_RING_THREADS 512
 #endif
-#ifndef NWC_RING_RESIDENT
-#define NWC_RING_RESIDENT 1
-#endif
-#ifndef NWC_RING_GRID_MULT
-#define NWC_RING_GRID_MULT 1
-#endif
+
 constexpr uint32_t kRingThreads = NWC_RING_THREADS, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES;
 constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
 constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes;
@@ -426,7 +422,7 @@ constexpr uint32_t kRingBarrierBytes = (kRingThreads / 32u) * kRingStages * 8u;
 constexpr uint32_t kRingMaxSmem = 232448u;                       /* 227 KB opt-in limit of a CTA */
 /* shared memory of the layout-2 ring kernel: x (32 columns per slot, bf16), the barriers, then the per-warp rings */
 __host__ __device__ static inline uint32_t ring_x_bytes(const Geometry &g) { return (g.slots * 64u + 127u) & ~127u; }
-static inline uint32_t ring_smem_bytes(const Geometry &g, int input_mode = kInputPlain) { return (input_mode == kInputNorm ? 2u : 1u) * ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + 128u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
+static inline uint32_t ring_smem_bytes(const Geometry &g, int input_mode = kInputPlain) { return (input_mode == kInputNorm ? 2u : 1u) * ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + 256u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
 
 struct FlatPlan {
     uint32_t units_per_group;   /* slots (layout 2) or blocks (layouts 0, 1) per row group                              */
@@ -476,7 +472,7 @@ constexpr uint32_t kRingEntries = 2u * (kRingThreads / 32u);
 constexpr uint32_t kRingShareBytes = kRingEntries * 4u + kRingEntries * 16u * 4u;
 constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 
-__global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
+__global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
     extern __shared__ __align__(128) uint8_t ring_smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Geometry g(a.M, a.K, 2);
@@ -485,10 +481,18 @@ __global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_l
     uint32_t *share_group = reinterpret_cast<uint32_t *>(ring_smem + front);
     float *share_value = reinterpret_cast<float *>(ring_smem + front + kRingEntries * 4u);
     float *scal = reinterpret_cast<float *>(ring_smem + front + kRingShareBytes);
-    const uint32_t bars = xs + front + kRingShareBytes + 128u + warp * (kRingStages * 8u);
-    const uint32_t ring = xs + front + kRingShareBytes + 128u + kRingBarrierBytes + warp * kRingWarpBytes;
-    /* the CTA's run of slots, then this warp's equal share of it */
-    const uint64_t c0 = plan.start(blockIdx.x), c1 = plan.start(blockIdx.x + 1u);
+    /* what this CTA contributes to row groups it shares with other CTAs of its cluster: entry 0 its first group, entry 1 its last */
+    uint32_t *cta_group = reinterpret_cast<uint32_t *>(ring_smem + front + kRingShareBytes + 64u);
+    float *cta_value = reinterpret_cast<float *>(ring_smem + front + kRingShareBytes + 128u);
+    const uint32_t bars = xs + front + kRingShareBytes + 256u + warp * (kRingStages * 8u);
+    const uint32_t ring = xs + front + kRingShareBytes + 256u + kRingBarrierBytes + warp * kRingWarpBytes;
+    /* The plan's runs belong to clusters (a cluster of one CTA unless the launch says otherwise); the CTAs of a cluster
+       split the cluster's run evenly, then the warps split the CTA's run. */
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t cluster_ctas = cluster.num_blocks(), cta_rank = cluster.block_rank(), cluster_id = blockIdx.x / cluster_ctas;
+    const uint64_t k0 = plan.start(cluster_id), k1 = plan.start(cluster_id + 1u);
+    const uint64_t c0 = k0 + (k1 - k0) * cta_rank / cluster_ctas, c1 = k0 + (k1 - k0) * (cta_rank + 1u) / cluster_ctas;
     const uint32_t cn = (uint32_t)(c1 - c0), w0 = (uint32_t)((uint64_t)cn * warp / (kRingThreads / 32u)), w1 = (uint32_t)((uint64_t)cn * (warp + 1u) / (kRingThreads / 32u));
     const uint64_t u0 = c0 + w0;
     const uint32_t count = w1 - w0, n_stage = (count + kRingSlots - 1u) / kRingSlots;
@@ -516,6 +520,7 @@ __global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_l
        memory, zero beyond K (the last slot may cover columns past K16). */
     stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes));
     if (threadIdx.x < kRingEntries) share_group[threadIdx.x] = kNoGroup;
+    if (threadIdx.x < 2u) cta_group[threadIdx.x] = kNoGroup;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal);
     const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * 16u, xq = xs + (lane & 3u) * 16u;
@@ -529,7 +534,7 @@ __global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_l
         const uint32_t r = lane >> 2;
         if (seg_first == 0u && s == slots) {                     /* a whole row group: nobody else adds to it */
             if ((lane & 3u) == 0u) {
-                const uint32_t part = blockIdx.x - plan.owner((uint64_t)rb * slots);
+                const uint32_t part = cluster_id - plan.owner((uint64_t)rb * slots);
                 emit_flat(a, plan, rb * 16u + r, part, lo); emit_flat(a, plan, rb * 16u + r + 8u, part, hi);
             }
         } else {
@@ -560,11 +565,7 @@ __global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_l
         };
         /* the block whose first slot is f starts here: this warp adds the block's exceptions */
         auto exceptions = [&](uint32_t f) {
-#ifdef NWC_KO_EXC
-            const float2 e = make_float2(0.f, 0.f);
-#else
             const float2 e = ring_exceptions(next_count, next_base, a.data, xs, f >> 4, lane);
-#endif
             ex_lo += e.x; ex_hi += e.y;
             if (++next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
         };
@@ -599,17 +600,44 @@ __global__ void __launch_bounds__(kRingThreads, NWC_RING_RESIDENT) ring_kernel_l
     if (s != seg_first) flush();
     __syncthreads();
     /* Shared row groups: entries of one group are adjacent in entry order.  The first entry of each group adds the
-       others in that order (so the sum does not depend on timing) and writes the CTA's value for the group. */
+       others in that order (so the sum does not depend on timing).  The result is final when this CTA's run holds the
+       whole group (or the plan keeps per-cluster partials anyway); otherwise it is this CTA's share of a group that
+       other CTAs of the cluster also hold, and goes to the cluster-level entries. */
     {
         const uint32_t e = threadIdx.x >> 4, row = threadIdx.x & 15u, grp = share_group[e];
-        if (grp == kNoGroup) return;
-        for (uint32_t p = e; p-- > 0u;) { const uint32_t gp = share_group[p]; if (gp == grp) return; if (gp != kNoGroup) break; }
-        float v = share_value[e * 16u + row];
-        for (uint32_t n = e + 1u; n < kRingEntries; n++) {
-            const uint32_t gn = share_group[n];
-            if (gn == grp) v += share_value[n * 16u + row]; else if (gn != kNoGroup) break;
+        bool leader = grp != kNoGroup;
+        for (uint32_t p = e; leader && p-- > 0u;) { const uint32_t gp = share_group[p]; if (gp == grp) leader = false; else if (gp != kNoGroup) break; }
+        if (leader) {
+            float v = share_value[e * 16u + row];
+            for (uint32_t n = e + 1u; n < kRingEntries; n++) {
+                const uint32_t gn = share_group[n];
+                if (gn == grp) v += share_value[n * 16u + row]; else if (gn != kNoGroup) break;
+            }
+            const uint64_t g0 = (uint64_t)grp * slots;
+            if (cluster_ctas == 1u || (g0 >= c0 && g0 + slots <= c1)) emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner(g0), v);
+            else {
+                const uint32_t which = g0 < c0 ? 0u : 1u;            /* the group began before this CTA's run: its first group */
+                cta_value[which * 16u + row] = v;
+                if (row == 0u) cta_group[which] = grp;
+            }
         }
-        emit_flat(a, plan, grp * 16u + row, blockIdx.x - plan.owner((uint64_t)grp * slots), v);
+    }
+    if (cluster_ctas > 1u) {                                        /* same again one level up, through distributed shared memory */
+        cluster.sync();
+        if (threadIdx.x < 32u) {
+            const uint32_t which = threadIdx.x >> 4, row = threadIdx.x & 15u, grp = cta_group[which];
+            /* this CTA is the first of its cluster to hold the group unless the group began before its run */
+            if (grp != kNoGroup && !((uint64_t)grp * slots < c0 && cta_rank > 0u)) {
+                float v = cta_value[which * 16u + row];
+                for (uint32_t r = cta_rank + 1u; r < cluster_ctas; r++) {        /* later CTAs hold it as their first group, in rank order */
+                    const uint32_t theirs = cluster.map_shared_rank(cta_group, r)[0];
+                    if (theirs == grp) v += cluster.map_shared_rank(cta_value, r)[row];
+                    else if (theirs != kNoGroup) break;          /* (no entry: an empty run, or one that starts on a group boundary) */
+                }
+                emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner((uint64_t)grp * slots), v);
+            }
+        }
+        cluster.sync();                                             /* nobody leaves while its shared memory may still be read */
     }
 }
 
@@ -655,10 +683,30 @@ static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t
 #define NWC_FINALIZE_SLOTS 256
 #endif
 constexpr uint64_t kFinalizeSlots = NWC_FINALIZE_SLOTS;
-static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p) {
-    const uint64_t total = (uint64_t)g.groups * g.slots, ctas = (uint64_t)sms * NWC_RING_GRID_MULT;
-    const uint64_t whole = ((g.groups + ctas - 1u) / ctas) * g.slots, cut = (total + ctas - 1u) / ctas + kFinalizeSlots;
-    make_flat_plan(g, g.slots, ctas, p, whole <= cut);
+/* How many clusters of 2 / 4 / 8 CTAs of the layout-2 kernel one device runs at once (a cluster needs its SMs inside one
+   GPC, so fewer SMs are usable the larger the cluster); asked from the runtime once per device. */
+constexpr uint64_t kClusterSlots = 128;                          /* measured: a cluster launch pays off only beyond this many slots saved per CTA */
+struct ClusterRoom { int count[4]; };                            /* index = log2(cluster size); [0] = SM count */
+static ClusterRoom cluster_room(int sms);
+/* The runs of the plan belong to clusters of `cluster` CTAs.  Candidates: whole row groups per CTA (cluster 1), whole row
+   groups per cluster of 2, 4 or 8 CTAs that split them (one launch each, bf16 y written by the kernel; the larger the
+   cluster the finer the split but the fewer SMs), or equal runs of slots per CTA with per-CTA partials and the finalize
+   launch.  Cost = slots the busiest CTA streams, plus what the extra synchronisation or launch is worth in slots. */
+static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p, uint32_t &cluster) {
+    const uint64_t total = (uint64_t)g.groups * g.slots;
+    const ClusterRoom room = cluster_room(sms);
+    uint64_t best = (total + (uint64_t)sms - 1u) / (uint64_t)sms + kFinalizeSlots;
+    uint32_t best_cluster = 0;                                   /* 0 = equal runs + finalize */
+    for (uint32_t lg = 0; lg < 4u; lg++) {
+        const uint64_t clusters = lg == 0u ? (uint64_t)sms : (uint64_t)room.count[lg];
+        if (!clusters) continue;
+        const uint64_t use = clusters < g.groups ? clusters : g.groups;
+        const uint64_t cost = (((g.groups + use - 1u) / use) * g.slots + (1u << lg) - 1u) / (1u << lg) + (lg ? kClusterSlots : 0u);
+        if (cost < best) { best = cost; best_cluster = 1u << lg; }
+    }
+    cluster = best_cluster ? best_cluster : 1u;
+    if (best_cluster == 0u) { make_flat_plan(g, g.slots, (uint64_t)sms, p, false); if (!p.direct) return; cluster = 1u; }   /* (a single column block forces whole groups) */
+    make_flat_plan(g, g.slots, cluster == 1u ? (uint64_t)sms : (uint64_t)room.count[cluster == 2u ? 1 : (cluster == 4u ? 2 : 3)], p, true);
 }
 
 /* ---- layouts 0 and 1, token path: lane streams staged in shared memory by bulk copies -------------------------------- */
@@ -1101,14 +1149,19 @@ bool dependent_launch() { return g_dependent_launch; }
 /* kernel launch that may start before its stream predecessor has finished (the kernel orders itself with
    griddepcontrol.wait) when dependent launch is switched on */
 template <class... Params, class... Args>
-static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+static cudaError_t launch_cluster_kernel(void (*kernel)(Params...), uint32_t cluster, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = g_dependent_launch ? 1 : 0;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster > 1u) { attr[n].id = cudaLaunchAttributeClusterDimension; attr[n].val.clusterDim.x = cluster; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1; n++; }
+    if (g_dependent_launch) { attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[n].val.programmaticStreamSerializationAllowed = 1; n++; }
+    cfg.attrs = attr; cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+template <class... Params, class... Args>
+static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    return launch_cluster_kernel(kernel, 1u, grid, block, smem, st, args...);
 }
 
 constexpr uint32_t kSmallFixedSmem = 16416u + kSmallWarps * 64u * 4u + kSmallWarps * 8u * 4u + 32u + kSmallWarps * 2u * kPrefixStageBytes + kSmallWarps * 16u;
@@ -1147,7 +1200,7 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K) {
     FlatPlan plan;
     if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
     if (!g_disable_ring && layout == 1) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan); return plan.direct ? 1 : 2; }
-    if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { make_cta_plan_layout2(g, sms, plan); return plan.direct ? 1 : 2; }
+    if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { uint32_t cluster; make_cta_plan_layout2(g, sms, plan, cluster); return plan.direct ? 1 : 2; }
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
@@ -1196,8 +1249,9 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     FusedInput in{kInputPlain, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr};
     if (input) in = *input;
     if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_smem_bytes(g, in.mode) <= kRingMaxSmem) {
-        make_cta_plan_layout2(g, sms, plan);
-        err = launch_kernel(ring_kernel_layout2, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
+        uint32_t cluster;
+        make_cta_plan_layout2(g, sms, plan, cluster);
+        err = launch_cluster_kernel(ring_kernel_layout2, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
         if (err == cudaSuccess && !plan.direct)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
@@ -1221,6 +1275,29 @@ static void opt_in_smem() {
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeDequant, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeAtomic, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
+static ClusterRoom cluster_room(int sms) {
+    static ClusterRoom cache[64];
+    static bool known[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!known[dev]) {
+        ClusterRoom r{{sms, 0, 0, 0}};
+        cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+        for (int lg = 1; lg < 4; lg++) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)sms / (1u << lg) * (1u << lg)); cfg.blockDim = dim3(kRingThreads); cfg.dynamicSmemBytes = kRingMaxSmem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 1u << lg; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
+        }
+        cache[dev] = r; known[dev] = true;
+    }
+    return cache[dev];
+}
+
 void configure_segment_kernels() {
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);

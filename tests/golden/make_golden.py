@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory from the REFERENCE implementation.
 
-Run in a container that has the reference checkout (default /root/reference) and its kernel library compiled from
+Run where the reference checkout is mounted (its path: the NWC_REFERENCE_ROOT variable) and its kernel library is compiled from
 source by `make -C oracle ref`:
 
     python tests/golden/make_golden.py
