@@ -167,14 +167,23 @@ __device__ __forceinline__ float dot16_fp8(uint4 w, const uint32_t (&xh)[8]) {
     return (f0.x + f0.y) + (f1.x + f1.y);
 }
 
+/* Uncompressed fp8 weight-only matvec (the bandwidth baseline NWC-fp8 is compared with).  A warp takes kNativeRows rows at
+   a time so that the fp32 -> half conversion of its slice of x is paid once per kNativeRows rows and that many 16-byte
+   loads per lane are in flight. */
+constexpr uint32_t kNativeRows = 8;
 __global__ void __launch_bounds__(256) native_fp8_kernel(const uint8_t *__restrict__ w, const float *__restrict__ scale, const float *__restrict__ x,
                                                          uint16_t *__restrict__ y, uint32_t M, uint32_t K) {
     const uint32_t lane = threadIdx.x & 31u, warps = gridDim.x * (blockDim.x >> 5);
-    for (uint32_t row0 = 2u * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); row0 < M; row0 += 2u * warps) {
-        const bool two = row0 + 1u < M;
-        float acc0 = 0.f, acc1 = 0.f;
+    for (uint32_t row0 = kNativeRows * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); row0 < M; row0 += kNativeRows * warps) {
+        const uint32_t rows = min(kNativeRows, M - row0);
+        float acc[kNativeRows];
+#pragma unroll
+        for (uint32_t r = 0; r < kNativeRows; r++) acc[r] = 0.f;
         if ((K & 15u) == 0u) {
             for (uint32_t k = lane * 16u; k < K; k += 512u) {
+                uint4 wv[kNativeRows];
+#pragma unroll
+                for (uint32_t r = 0; r < kNativeRows; r++) wv[r] = r < rows ? ldg_stream128(w + (uint64_t)(row0 + r) * K + k) : make_uint4(0u, 0u, 0u, 0u);
                 uint32_t xh[8];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
@@ -182,28 +191,31 @@ __global__ void __launch_bounds__(256) native_fp8_kernel(const uint8_t *__restri
                     const __half2 p0 = __floats2half2_rn(v.x, v.y), p1 = __floats2half2_rn(v.z, v.w);
                     xh[2 * i] = *reinterpret_cast<const uint32_t *>(&p0); xh[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&p1);
                 }
-                acc0 += dot16_fp8(ldg_stream128(w + (uint64_t)row0 * K + k), xh);
-                if (two) acc1 += dot16_fp8(ldg_stream128(w + (uint64_t)(row0 + 1u) * K + k), xh);
+#pragma unroll
+                for (uint32_t r = 0; r < kNativeRows; r++) acc[r] += dot16_fp8(wv[r], xh);
             }
         } else {
             for (uint32_t k = lane; k < K; k += 32u) {
                 const float xv = __ldg(x + k);
-                acc0 = fmaf(fp8_to_float(w[(uint64_t)row0 * K + k]), xv, acc0);
-                if (two) acc1 = fmaf(fp8_to_float(w[(uint64_t)(row0 + 1u) * K + k]), xv, acc1);
+#pragma unroll
+                for (uint32_t r = 0; r < kNativeRows; r++) if (r < rows) acc[r] = fmaf(fp8_to_float(w[(uint64_t)(row0 + r) * K + k]), xv, acc[r]);
             }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) { acc0 += __shfl_xor_sync(0xffffffffu, acc0, o); acc1 += __shfl_xor_sync(0xffffffffu, acc1, o); }
+        for (uint32_t r = 0; r < kNativeRows; r++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+        }
         if (lane == 0) {
-            y[row0] = bf16_round(acc0 * scale[row0]);
-            if (two) y[row0 + 1u] = bf16_round(acc1 * scale[row0 + 1u]);
+#pragma unroll
+            for (uint32_t r = 0; r < kNativeRows; r++) if (r < rows) y[row0 + r] = bf16_round(acc[r] * scale[row0 + r]);
         }
     }
 }
 
 cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K) {
-    const uint32_t pairs = (M + 1u) / 2u;
-    unsigned grid = (pairs + 7u) / 8u;
+    const uint32_t units = (M + kNativeRows - 1u) / kNativeRows;
+    unsigned grid = (units + 7u) / 8u;
     if (grid > 148u * 8u) grid = 148u * 8u;
     native_fp8_kernel<<<grid, 256, 0, st>>>(w, scale, x, y, M, K);
     return cudaGetLastError();
