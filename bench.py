@@ -1,21 +1,29 @@
 """Benchmark of the NWC batch-1 decode path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--model qwen3-0.6b] [--layout 0] [--elem bf16]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--model llama3-70b] [--layout 2] [--elem bf16]
 
-Workload (N = 1): a Qwen3-0.6B-architecture decoder with random-init weights of the reference's distribution
-(W = r_i * 0.02 * z, r_i log-normal(0, 0.3), norms 1), compressed bf16 layout 0, batch 1, 32 random prompt ids, greedy
-decode replayed as one CUDA graph per token.  A step is one decoded token.
+Default workload: a Llama-3-70B-architecture decoder (80 layers, hidden 8192, MLP 28672, 64 q / 8 kv heads, vocabulary
+128256) with random-init weights of the reference's distribution (W = r_i * 0.02 * z, r_i log-normal(0, 0.3), norms 1),
+compressed bf16 layout 2 (about 105 GB), batch 1, 32 random prompt ids, greedy decode replayed as one CUDA graph per
+token.  A step is one decoded token.  `--model qwen3-0.6b --layout 0` and `--model qwen3-4b` select the smaller
+configurations.
+  N = 1   the whole model on one GPU.
+  N > 1   (torchrun, one rank per GPU) the SAME model sharded tensor-parallel over the N ranks: q/k/v, gate/up and lm_head
+          by rows, o and down by columns, the partial sums of o and down exchanged over NVLink inside the matvec kernels
+          (`--tp-reduce push`; `pull` = one reduction kernel per sum, `nccl` = NCCL all-reduce).  Strong scaling: value =
+          K / max-over-ranks time.  `--parallel replicas` runs N independent copies instead (weak scaling, small models).
   value     tokens/s of K graph replays, device-timed, nothing copied to or from the host inside the region
   e2e       the same through DecodeEngine.step(): token id from pinned host memory in, next token id back, every step
-  roofline  the dominant kernel (the fused decode-matvec on the lm_head matrix, larger than L2) launched back to back:
-            algorithmic bytes (the reference's own per-matrix byte count) / CUDA-event time, against the measured HBM peak
-  cpu_baseline  the CPU oracle's fused decode+matvec on all host cores over a bounded sample (one decoder layer plus
-            1/8 of the lm_head rows), extrapolated to a whole token
-With N > 1 (torchrun, one rank per GPU) every rank decodes its own sequence on its own replica of the model: no
-data-path collective, weak scaling; value = N * K / max-over-ranks time.
+  tokens_sha16   hash of the ids generated in the timed region (equal across N when no near-tie flips a token)
+  roofline  the token-matvec kernel with the largest share of the step (each of the five matrix kinds is timed alone, back
+            to back over the layers' own matrices so that no launch finds its matrix in L2): algorithmic bytes (the
+            reference's per-matrix byte count) / CUDA-event time, against the measured HBM peak
+  cpu_baseline  (N = 1) the CPU oracle's fused decode+matvec on all host cores over a bounded sample, extrapolated to a token
 --impl reference runs the CPU path alone (rank 0), each step one pass over the bounded sample.
 """
 import argparse
+import hashlib
+import importlib.util
 import json
 import os
 import statistics
@@ -31,19 +39,29 @@ if ROOT not in sys.path: sys.path.insert(0, ROOT)
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--model", default="qwen3-0.6b")
-    ap.add_argument("--layout", type=int, default=0)
+    ap.add_argument("--model", default="llama3-70b")
+    ap.add_argument("--layout", type=int, default=None, help="default: 2 (0 for qwen3-0.6b, the layout its configuration names)")
     ap.add_argument("--elem", default="bf16")
     ap.add_argument("--prompt", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="", help="time one token matvec alone: lm_head | qkv | o | gate_up | down | MxK (small case for ncu)")
-    ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"], help="N > 1: independent replicas (weak scaling) or tensor parallel with NCCL all-reduce (strong scaling)")
-    ap.add_argument("--tp-reduce", default="peer", choices=["peer", "nccl"], help="--parallel tp: sum partial outputs with this library's NVLink peer-memory kernel or with NCCL")
+    ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
+    ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
-    return ap.parse_args()
+    a = ap.parse_args()
+    if a.layout is None: a.layout = 0 if a.model == "qwen3-0.6b" else 2
+    return a
+
+
+def load_presets():
+    """The architecture table, by path: the reference arm must not load the CUDA library."""
+    spec = importlib.util.spec_from_file_location("nwc_presets", os.path.join(ROOT, "nwc_b200", "presets.py"))
+    m = importlib.util.module_from_spec(spec); sys.modules["nwc_presets"] = m; spec.loader.exec_module(m)
+    return m.PRESETS
 
 
 def measured_peak():
@@ -82,61 +100,71 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------------------------
 # CPU path (oracle port of the reference's format; the reference ships no compiled CPU decoder for formats v9+)
 
-def cpu_sample(cfg, layout, elem_code, threads, repeats=1):
-    """Seconds per token of the CPU fused decode+matvec, extrapolated from one layer + 1/8 of the lm_head rows."""
-    import numpy as np
-    import oracle as O
-    code = O.code_of(elem_code, layout)
-    shapes = [("qkv", cfg.qkv_rows, cfg.hidden), ("o", cfg.hidden, cfg.n_q * cfg.head_dim), ("gate_up", 2 * cfg.intermediate, cfg.hidden),
-              ("down", cfg.hidden, cfg.intermediate), ("lm_head/8", cfg.vocab // 8, cfg.hidden)]
-    packed = []
-    for i, (name, M, K) in enumerate(shapes):
-        w, x = O.synth_weights(M, K, 1000 + i)
-        src = w
-        if elem_code: src, _ = O.quantize_fp8(w)
-        packed.append((O.encode(src, code), O.bf16_to_f32(x)))
-    times = []
-    for _ in range(repeats):
+class CpuSample:
+    """A bounded sample of one token's matvec work for the CPU arm: the first 1 / `cut` of the rows of each of a decoder
+    layer's four matrices and 1 / (8 cut) of the lm_head rows, encoded once; a pass multiplies all five and the token time
+    is extrapolated as layers * cut * (layer part) + 8 cut * (lm_head part)."""
+
+    def __init__(self, cfg, layout, elem_code):
+        import oracle as O
+        self.O, self.cfg = O, cfg
+        weights = sum(r * c for k, (r, c) in cfg.matrix_shapes().items() if k != "lm_head")
+        self.cut = 1 if weights <= 120e6 else (4 if weights <= 500e6 else 8)     # keeps encoding + a pass within seconds
+        code = O.code_of(elem_code, layout)
+        self.packed = []
+        for i, (name, (M, K)) in enumerate(cfg.matrix_shapes().items()):
+            rows = max(16, M // (self.cut * (8 if name == "lm_head" else 1)) // 16 * 16)
+            w, x = O.synth_weights(rows, K, 1000 + i)
+            src = O.quantize_fp8(w)[0] if elem_code else w
+            self.packed.append((O.encode(src, code), O.bf16_to_f32(x), M / rows))
+        self.what = ("rows [0, M/%d) of one decoder layer's qkv, o, gate_up and down plus 1/%d of the lm_head rows per pass; token time = layers x layer part + lm_head part, each "
+                     "scaled by its row fraction" % (self.cut, 8 * self.cut))
+
+    def seconds_per_token(self, threads):
         per = []
-        for p, x in packed:
-            t = time.perf_counter(); O.matvec_f32(p, x, threads=threads); per.append(time.perf_counter() - t)
-        times.append(cfg.layers * sum(per[:4]) + 8.0 * per[4])
-    return times, "1 decoder layer (qkv, o, gate_up, down) + 1/8 of the lm_head rows per pass, extrapolated to layers x layer + 8 x slice"
+        for p, x, scale in self.packed:
+            t = time.perf_counter(); self.O.matvec_f32(p, x, threads=threads); per.append((time.perf_counter() - t) * scale)
+        return self.cfg.layers * sum(per[:4]) + per[4]
 
 
 def run_reference(a, cfg):
     threads = os.cpu_count() or 1
-    elem_code = 1 if a.elem == "fp8" else 0
-    for _ in range(max(0, min(a.warmup, 1))): cpu_sample(cfg, a.layout, elem_code, threads)
-    steps = max(1, min(a.steps, 8))
-    times, what = cpu_sample(cfg, a.layout, elem_code, threads, repeats=steps)
+    sample = CpuSample(cfg, a.layout, 1 if a.elem == "fp8" else 0)
+    for _ in range(a.warmup): sample.seconds_per_token(threads)
+    times = [sample.seconds_per_token(threads) for _ in range(max(1, a.steps))]
     sec = statistics.mean(times)
-    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": a.gpus, "steps": steps, "warmup": min(a.warmup, 1),
-            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
-            "config": workload(a, cfg, a.gpus, a.parallel == "tp"), "cpu_baseline": {"value": 1.0 / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what},
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": a.gpus, "steps": max(1, a.steps), "warmup": a.warmup,
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": scaling_of(a, a.gpus), "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
+            "config": workload(a, cfg, a.gpus), "cpu_baseline": {"value": 1.0 / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample.what},
             "e2e": {"value": 1.0 / sec, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def workload(a, cfg, world=1, tp=False):
+def is_tp(a, world): return world > 1 and a.parallel in ("auto", "tp")
+def scaling_of(a, world): return "strong" if is_tp(a, world) else "weak"
+
+
+def workload(a, cfg, world=1):
     """The `config` object; identical in both arms so that their lines can be compared key by key."""
     par = "1 GPU"
     if world > 1:
-        par = ("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, partial sums added after o and down (%s)" % (world, "NVLink peer-memory kernel" if a.tp_reduce == "peer" else "NCCL all-reduce") if tp
+        how = {"push": "pushed over NVLink inside the matvec kernels", "pull": "NVLink peer-memory reduction kernel", "nccl": "NCCL all-reduce"}[a.tp_reduce]
+        par = ("tp%d: q/k/v, gate/up, lm_head split by rows, o/down by columns, partial sums added after o and down (%s)" % (world, how) if is_tp(a, world)
                else "replicas x%d (no data-path collective)" % world)
     return {"workload": f"{cfg.name}-architecture decoder, random init, NWC {a.elem} layout {a.layout}, batch 1, {a.prompt} random prompt ids, greedy decode as a CUDA graph",
             "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab,
-            "l2_policy": "no flush: the compressed weights streamed per token and the lm_head matrix of the roofline leg are each larger than the 126 MB L2",
+            "l2_policy": "no flush: the compressed weights streamed per token are larger than the 126 MB L2, and the roofline leg walks the layers' own matrices (more than L2 in total) back to back",
             "parallelism": par}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the lm_head kernel, from the ncu captures summarised
-# under profiles/ (same command line as `--kernel lm_head`); other workloads report null
-NCU_TRAFFIC = {("qwen3-0.6b", 0, "bf16"): 217.5e6, ("qwen3-0.6b", 2, "bf16"): 239.1e6}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch over its algorithmic bytes, from the ncu captures summarised
+# under profiles/ (a smaller matrix of the same kernel and K where the full one is too large to capture; the kernel reads
+# every plane byte once, so traffic grows in proportion to the bytes); kinds without a capture report null
+NCU_TRAFFIC_RATIO = {("ring_kernel_layout2", 8192): 1.02, ("ring_kernel_layout2", 1024): 1.02, ("prefix_ring_kernel_layout0", 1024): 1.018}
 
 
-def token_kernel_name(layout, elem):
-    if layout == 0: return "prefix_ring_kernel_layout0"
+def token_kernel_name(layout, elem, small=False):
+    if layout == 0: return "small_kernel_layout0" if small else "prefix_ring_kernel_layout0"
     if layout == 1: return "prefix_ring_kernel_layout1"
     if layout == 2 and elem == "bf16": return "ring_kernel_layout2"
     return "segment_kernel<layout %d, %s>" % (layout, elem)
@@ -152,11 +180,11 @@ def trace(msg):
 def kernel_only(a, cfg):
     """The token matvec on synthetic matrices of one shape, back to back inside a CUDA graph over enough rotating copies
     that no launch finds its matrix in L2.  Prints one JSON line with the roofline of one call."""
+    import ctypes
     import torch
     from nwc_b200 import NWCWeight, _lib as L
     from nwc_b200.decode import synthetic_matrix
-    shapes = {"lm_head": (cfg.vocab, cfg.hidden), "qkv": (cfg.qkv_rows, cfg.hidden), "o": (cfg.hidden, cfg.n_q * cfg.head_dim),
-              "gate_up": (2 * cfg.intermediate, cfg.hidden), "down": (cfg.hidden, cfg.intermediate)}
+    shapes = cfg.matrix_shapes()
     M, K = shapes[a.kernel] if a.kernel in shapes else tuple(int(v) for v in a.kernel.lower().split("x"))
     torch.cuda.set_device(0)
     L.lib.nwc_set_dependent_launch(int(a.dependent_launch))
@@ -207,11 +235,56 @@ def kernel_only(a, cfg):
             if err: raise RuntimeError(f"nwc_ref_fp8 error {err}")
         native_fp8_ms = timed(native, n8)
         del q8
+    # the reference's own kernel for the same call (its library compiled unchanged for sm_100a; a comparison arm of this
+    # benchmark only): the reference ABI's nwc_linear_bf16 takes fp32 x for layout 0 and bf16 x otherwise
+    ref_ms = None
+    if a.vs_ref and a.steps > 1:
+        path = os.path.join(ROOT, "oracle", "_ref", "nwc_ops.so")
+        if os.path.exists(path):
+            ref = ctypes.CDLL(path)
+            ref.nwc_setup.restype = ctypes.c_int; ref.nwc_setup()
+            P, U64, U32, I = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int
+            ref.nwc_linear_bf16.restype, ref.nwc_linear_bf16.argtypes = I, [P] * 11 + [U64, U32, U32, I]
+            xr = (x.float() if a.layout == 0 else x).contiguous()
+            def ref_call(i):
+                w = mats[i]
+                err = ref.nwc_linear_bf16(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(xr), None, L.ptr(w.scale),
+                                          L.ptr(w.scratch), L.ptr(y), w.n, w.block, K, w.code)
+                if err: raise RuntimeError(f"reference nwc_linear_bf16 error {err}")
+            ref_ms = timed(ref_call, copies)
     print(json.dumps({"kernel": f"token matvec {M}x{K} {a.elem} layout {a.layout}", "launches_per_call": L.lib.nwc_linear_launches(nw.n, K, nw.code, 0), "us_per_call": ms * 1e3,
                       "bytes_per_call": nw.bytes, "bits_per_weight": 8 * nw.bytes / nw.n, "dense_bf16_gemv_us": None if dense_ms is None else dense_ms * 1e3,
                       "native_fp8_matvec_us": None if native_fp8_ms is None else native_fp8_ms * 1e3,
+                      "reference_kernel_us": None if ref_ms is None else ref_ms * 1e3,
                       "roofline": {"bound": "hbm", "achieved": nw.bytes / ms / 1e6, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": nw.bytes / ms / 1e6 / peak},
                       "note": "%d calls on %d rotating copies replayed as one CUDA graph, CUDA events around the replay (a call includes its finalize launch when it needs one)" % (reps, copies)}))
+
+
+def matvec_shares(eng, weights, cfg, reps_target=24):
+    """Each of the five kinds of token matvec timed alone: the layers' own matrices of that kind back to back (plain x,
+    mode 0) inside one CUDA graph, CUDA events around the replay.  Returns {kind: (us per launch, bytes per launch, launches
+    per token)}."""
+    import torch
+    out = {}
+    for kind in ("qkv", "o", "gate_up", "down", "lm_head"):
+        mats = [weights.lm_head] if kind == "lm_head" else [l[kind] for l in weights.layers]
+        total = sum(m.bytes for m in mats)
+        reps = max(8, min(reps_target, len(mats))) if len(mats) > 1 else 12
+        x = eng.xtmp if mats[0].in_features <= eng.xtmp.numel() else torch.zeros(mats[0].in_features + 32, dtype=torch.bfloat16, device="cuda")
+        y = torch.empty(max(m.out_features for m in mats), dtype=torch.bfloat16, device="cuda")
+        side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side): eng._linear(mats[0], x, y)
+        torch.cuda.current_stream().wait_stream(side)
+        kg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kg):
+            for i in range(reps): eng._linear(mats[i % len(mats)], x, y)
+        for _ in range(3): kg.replay()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(); kg.replay(); k1.record(); torch.cuda.synchronize()
+        out[kind] = (k0.elapsed_time(k1) / reps * 1e3, total / len(mats), 1 if kind == "lm_head" else len(weights.layers), min(reps, len(mats)) * (total / len(mats)))
+        del kg
+    return out
 
 
 def finish(eng, dist):
@@ -228,17 +301,16 @@ def finish(eng, dist):
 
 def main():
     a = parse()
-    from nwc_b200.decode import PRESETS  # the package import fails loudly when the CUDA library is missing
-    cfg = PRESETS[a.model]
+    cfg = load_presets()[a.model]
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    if a.impl == "reference":
+    if a.impl == "reference":                # the CPU arm: rank 0 alone, no CUDA library, no CUDA context
         if rank == 0: run_reference(a, cfg)
         return
     if a.kernel:
         if rank == 0: kernel_only(a, cfg)
         return
     import torch
-    from nwc_b200.decode import DecodeEngine, DecoderWeights
+    from nwc_b200.decode import DecodeEngine, DecoderWeights  # the package import fails loudly when the CUDA library is missing
     from nwc_b200 import _lib as L
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -246,19 +318,22 @@ def main():
     if world > 1:
         import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
-    tp = a.parallel == "tp" and world > 1
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
+    tp = is_tp(a, world)
     if tp and a.tp_reduce == "nccl": a.dependent_launch = 0         # NCCL kernels sit in the chain: keep plain stream order around them
+    max_len = a.prompt + 2 * (a.warmup + a.steps) + 16
     if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=0, tp_rank=rank, tp_world=world)
-        eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD, tp_reduce=a.tp_reduce)
+        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD, tp_reduce=a.tp_reduce)
+        a.tp_reduce = eng.tp_reduce                                  # what actually runs (push needs layout 2 bf16)
     else:
-        weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank)
-        eng = DecodeEngine(weights, max_len=a.prompt + a.warmup + 2 * a.steps + 16, dependent_launch=bool(a.dependent_launch))
+        weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank if world > 1 else 0)
+        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch))
     trace("weights built")
+    if dist is not None: torch.cuda.synchronize(); dist.barrier()    # ranks start their first kernels together (bounded waits inside)
     eng.capture()
     trace("graph captured")
-    g = torch.Generator().manual_seed(1234 + (0 if tp else rank))
+    g = torch.Generator().manual_seed(1234 + (0 if tp or world == 1 else rank))
     prompt = torch.randint(0, cfg.vocab, (a.prompt,), generator=g)
 
     def barrier():
@@ -267,6 +342,7 @@ def main():
         torch.cuda.synchronize()
 
     # ---- value: K graph replays, device-timed ----
+    barrier()
     eng.prefill(prompt)
     trace("prefill done")
     for _ in range(a.warmup): eng._run()
@@ -280,8 +356,11 @@ def main():
     ms = t0.elapsed_time(t1)
     trace("timed region done")
     clocks = sampler.stop() if sampler else None
-    if int(eng.status.item()): raise RuntimeError("decode position left the KV cache")
+    eng._check_status()                                               # position inside the cache, no bounded wait gave up
+    ids = eng.log[a.warmup: a.warmup + a.steps].cpu().tolist()
+    sha = hashlib.sha256(",".join(str(int(t)) for t in ids).encode()).hexdigest()[:16]
     # ---- e2e: host token in, host token out, every step ----
+    barrier()
     eng.prefill(prompt)
     tok = int(eng.cur.item())
     for _ in range(a.warmup): tok = eng.step(tok)
@@ -299,38 +378,37 @@ def main():
         finish(eng, dist)
         return
     trace("reduced over ranks")
-    # ---- roofline of the dominant kernel: lm_head matvec back to back inside one graph ----
+    # ---- roofline of the dominant kernel: the matrix kind with the largest share of the step's matvec time ----
     peak, peak_kind = measured_peak()
-    w = weights.lm_head
-    reps = 20
-    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side): eng._linear(w, eng.xtmp, eng.logits)
-    torch.cuda.current_stream().wait_stream(side)
-    kg = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(kg):
-        for _ in range(reps): eng._linear(w, eng.xtmp, eng.logits)
-    for _ in range(3): kg.replay()
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record(); kg.replay(); k1.record(); torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / reps
-    achieved = w.bytes / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "%s (fused decode-matvec), lm_head %dx%d layout %d" % (token_kernel_name(w.layout, a.elem), w.out_features, w.in_features, w.layout),
+    shares = matvec_shares(eng, weights, cfg)
+    per_token = {k: us * n for k, (us, _, n, _) in shares.items()}
+    top = max(per_token, key=per_token.get)
+    us, nbytes, count, walked = shares[top]
+    w = weights.lm_head if top == "lm_head" else weights.layers[0][top]
+    small = a.layout == 0 and -(-w.out_features // 8) * -(-w.in_features // 512) <= 2 * L.SM_COUNT * 32      # the single-launch small-matrix kernel
+    name = token_kernel_name(w.layout, a.elem, small)
+    achieved = nbytes / (us * 1e-6) / 1e9
+    ratio = NCU_TRAFFIC_RATIO.get((name, w.in_features))
+    roofline = {"bound": "hbm", "kernel": "%s (fused decode-matvec), %s %dx%d layout %d%s" % (name, top, w.out_features, w.in_features, w.layout, " (this rank's shard)" if tp else ""),
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC.get((a.model, a.layout, a.elem)) if not tp else None,
-                "bytes_per_launch": w.bytes, "us_per_launch": kernel_ms * 1e3,
+                "traffic": None if ratio is None else ratio * nbytes,
+                "bytes_per_launch": nbytes, "us_per_launch": us, "share_of_matvec_time": per_token[top] / sum(per_token.values()),
+                "bytes_walked_per_replay": walked,
+                "matvec_us": {k: round(v[0], 2) for k, v in shares.items()}, "matvec_frac": {k: round(v[1] / (v[0] * 1e-6) / 1e9 / peak, 3) for k, v in shares.items()},
+                "matvec_ms_per_token": sum(per_token.values()) / 1e3,
                 "model_bytes_per_token": weights.bytes_per_token(), "model_frac_of_roofline": weights.bytes_per_token() / (ms / a.steps * 1e-3) / 1e9 / peak}
     cpu = None
-    if not a.no_cpu_baseline:
+    if not a.no_cpu_baseline and world == 1:
         threads = os.cpu_count() or 1
-        times, what = cpu_sample(cfg, a.layout, 1 if a.elem == "fp8" else 0, threads, repeats=2)
-        cpu = {"value": 1.0 / min(times), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what}
-    streams = 1 if tp else world          # sequences decoded at once
+        sample = CpuSample(cfg, a.layout, 1 if a.elem == "fp8" else 0)
+        cpu = {"value": 1.0 / min(sample.seconds_per_token(threads) for _ in range(2)), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample.what}
+    streams = 1 if (tp or world == 1) else world          # sequences decoded at once
     line = {"metric": "decode_tokens_per_s", "value": streams * a.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
-            "config": workload(a, cfg, world, tp),
+            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": scaling_of(a, world), "vs_baseline": None, "dtype": a.elem, "data": "synthetic",
+            "config": workload(a, cfg, world),
             "e2e": {"value": streams * a.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": a.steps * eng.launches_per_step, "launches_per_step": eng.launches_per_step,
+            "tokens_sha16": sha, "tokens_head": [int(t) for t in ids[:8]],
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line), flush=True)
     finish(eng, dist)

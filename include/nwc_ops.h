@@ -82,7 +82,8 @@ int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const uint32_t *ba
                            int elem, uint32_t splits);
 
 /* Status word of the kernels' bounded waits: 0, 2 when a warp gave up waiting for a bulk copy (its rows are then
-   missing from y), 3 when nwc_allreduce_add_rmsnorm gave up waiting for a peer rank.  Synchronises the device;
+   missing from y), 3 when a kernel gave up waiting for a peer rank (nwc_allreduce_add_rmsnorm, nwc_linear_fused_tp,
+   nwc_argmax_tp).  Synchronises the device;
    clear != 0 resets the word. */
 int nwc_kernel_status(int clear);
 
@@ -153,6 +154,34 @@ int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, c
                      const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
                      uint32_t K, int elem);
 
+/* nwc_linear_fused on a tensor-parallel group of one node ("push" protocol; buffers as for nwc_allreduce_add_rmsnorm:
+   a host array of `world` exchange buffers, this rank's own at [rank]).
+     out_slot >= 0  (row-parallel matrices: o, down) y is not written; the kernel stores its bf16 result into push slot
+                    out_slot (0 or 1, used in turn) of EVERY rank's buffer with plain stores over NVLink, and its last CTA
+                    raises this rank's flag in every buffer after a system-scope fence.  M <= H, no bias / scale.
+     in_slot >= 0   (the matrix after a row-parallel one; mode must be 1, delta NULL, K == H) the prologue waits -
+                    bounded by nwc_comm_set_timeout_ms - until every rank's flag for that slot has arrived in this rank's
+                    buffer, adds the `world` partials in rank order in fp32 (every rank gets the same bits), and continues
+                    as mode 1 with that sum as delta.  After a timeout nwc_kernel_status() reports 3 and y is NaN.
+   So the sum over the ranks costs no kernel of its own and one NVLink trip.  Only matrices that run on the layout-2 bf16
+   ring kernel are covered (-2 otherwise: use nwc_allreduce_add_rmsnorm).  All ranks must make the same sequence of calls;
+   calls on one device must be in stream order.  tp == NULL is nwc_linear_fused. */
+typedef struct {
+    void *const *buffers;
+    int rank, world;
+    int in_slot, out_slot;      /* -1: unused */
+    uint32_t H;                 /* hidden size the buffers were allocated for */
+} nwc_tp_io;
+int nwc_linear_fused_tp(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                        const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta,
+                        uint16_t *h_out, const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp,
+                        const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
+                        uint32_t K, int elem, const nwc_tp_io *tp);
+
+/* Longest time a kernel waits for the other ranks of a tensor-parallel group (fused prologue, sharded argmax) before it
+   gives up with status 3; default 2000 ms. */
+void nwc_comm_set_timeout_ms(uint32_t ms);
+
 /* Prefill (T tokens at once): Y[t][m] = bf16(scale[m] * sum_k X[t][k] W[m][k] + bias[m]); X bf16 [T][ldx] (ldx a multiple
    of 8, 16-byte aligned), Y bf16 [T][ldy].  W is decoded tile by tile into the shared-memory operands of a tcgen05 /
    tensor-memory GEMM; no decompressed copy is written.  The reference dequantises into a temporary and calls a dense
@@ -186,9 +215,17 @@ int nwc_attention_decode(void *stream, const uint16_t *qkv, const uint16_t *q_no
 /* a16 <- bf16(bf16(silu(gate)) * up) with gate = gate_up[0..I), up = gate_up[I..2I); a32 (may be NULL) as fp32 */
 int nwc_swiglu(void *stream, const uint16_t *gate_up, uint32_t I, uint16_t *a16, float *a32);
 
-/* Greedy choice over bf16 logits[V] (lowest index wins ties): cur[0] <- token, log[*step] <- token (log may be NULL),
-   then *pos += 1 and *step += 1. */
-int nwc_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step);
+/* Greedy choice over bf16 logits[V] (lowest index wins ties): cur[0] <- token; then, only while *step < log_len and
+   *pos < max_pos (so a loop that runs past its buffers writes nothing out of bounds): log[*step] <- token (log may be
+   NULL), *pos += 1 and *step += 1. */
+int nwc_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step,
+               uint32_t log_len, uint32_t max_pos);
+
+/* The same over vocabulary-sharded logits: every rank passes its V rows (global index = rank * V + local index), the
+   ranks exchange one 8-byte (value, index) word each through their exchange buffers and all end with the same token.
+   The wait for the other ranks is bounded (status 3, the local best is used). */
+int nwc_argmax_tp(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos,
+                  int32_t *step, uint32_t log_len, uint32_t max_pos, void *const *buffers, int rank, int world);
 
 #ifdef __cplusplus
 }

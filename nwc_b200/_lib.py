@@ -42,7 +42,10 @@ _SIGNATURES = {
     "nwc_linear_prefill": (I, [P, P, P, P, P, P, P, U32, U32, P, P, P, U32, U64, U32, U32, I]),
     "nwc_attention_decode": (I, [P, P, P, P, P, P, P, P, P, U32, U32, U32, U32, ctypes.c_float, P, P]),
     "nwc_swiglu": (I, [P, P, U32, P, P]),
-    "nwc_argmax": (I, [P, P, U32, P, P, P, P]),
+    "nwc_argmax": (I, [P, P, U32, P, P, P, P, U32, U32]),
+    "nwc_argmax_tp": (I, [P, P, U32, P, P, P, P, U32, U32, P, I, I]),
+    "nwc_linear_fused_tp": (I, [P, P, P, P, P, P, I, P, P, P, P, P, ctypes.c_float, P, P, P, P, P, P, U64, U32, U32, I, P]),
+    "nwc_comm_set_timeout_ms": (None, [U32]),
     "nwc_linear_bf16_static": (I, [P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_matvec": (I, [P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_dequant": (I, [P, P, P, P, P, P, P, U64, U32, U32, I]),
@@ -63,6 +66,15 @@ _SIGNATURES = {
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)            # AttributeError here = a library that does not implement the C-ABI
     _fn.restype, _fn.argtypes = _res, _args
+
+
+
+class TpIo(ctypes.Structure):
+    """nwc_tp_io of include/nwc_ops.h: the exchange buffers of a tensor-parallel group and the push slots one
+    nwc_linear_fused_tp call reads (in_slot) and writes (out_slot); -1 = unused."""
+    _fields_ = [("buffers", ctypes.c_void_p), ("rank", ctypes.c_int), ("world", ctypes.c_int), ("in_slot", ctypes.c_int),
+                ("out_slot", ctypes.c_int), ("H", ctypes.c_uint32)]
+
 
 VERSION = lib.nwc_info(0)
 TAB_WORDS = lib.nwc_info(2)

@@ -2,7 +2,8 @@
 
 Each rank allocates its buffer through the library (plain device memory), the 64-byte CUDA IPC handles travel through
 `torch.distributed.all_gather_object`, and every rank opens the handles of the others.  The buffers carry the ranks'
-partial o / down outputs and the arrival words of `nwc_allreduce_add_rmsnorm` (layout: nwc_b200/csrc/nwc_comm.cu)."""
+partial o / down outputs, the flags of both reduction protocols and the words of the sharded argmax (layout:
+nwc_b200/csrc/nwc_comm.h)."""
 import ctypes
 
 import torch
@@ -34,8 +35,16 @@ class PeerBuffers:
             if err: raise RuntimeError(f"nwc_comm_import error {err} (rank {r}: no peer access between the two GPUs?)")
             self.opened.append(peer.value); pointers.append(peer.value)
         self.table = (ctypes.c_void_p * self.world)(*pointers)      # host array the launches read
+        self._io = {}
         torch.cuda.synchronize()
         dist.barrier(group=group)                                   # every buffer is zeroed and open before the first kernel
+
+    def io(self, in_slot: int = -1, out_slot: int = -1):
+        """nwc_tp_io argument of nwc_linear_fused_tp (kept alive by this object: the library reads it at launch time)."""
+        key = (in_slot, out_slot)
+        if key not in self._io:
+            self._io[key] = L.TpIo(ctypes.cast(self.table, ctypes.c_void_p), self.rank, self.world, in_slot, out_slot, self.hidden)
+        return ctypes.byref(self._io[key])
 
     def slot(self, i: int) -> ctypes.c_void_p:
         """Where this rank's row-parallel matvec writes its partial output (slot 0: o, slot 1: down)."""

@@ -24,6 +24,8 @@ int device_sms() {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
     configure_segment_kernels();
+    configure_model_kernels();
+    configure_prefill_kernels();
     g_sm_count[dev] = sms;
     return sms;
 }
@@ -96,12 +98,17 @@ NWC_EXPORT int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t 
     return run_segments(0, stream, data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, n, block, K, elem, 0, 1);
 }
 
+/* longest wait of a fused prologue for the other ranks' partials (nwc_comm_set_timeout_ms) */
+unsigned long long g_peer_timeout_ns = 2000000000ull;
+
 /* Token matvec with the activation prologue fused where that pays (layout 0 matrices of at most two blocks per resident
-   warp: one launch in all); other matrices run the prologue kernel into xtmp and then the regular token path. */
-NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
-                                const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
-                                const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
-                                float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem) {
+   warp: one launch in all; layout 2 bf16 on the ring kernel); other matrices run the prologue kernel into xtmp and then the
+   regular token path.  `tp` (may be null) names the exchange buffers of a tensor-parallel group: in_slot >= 0 takes the
+   summed partials of that push slot as the residual delta, out_slot >= 0 pushes y to every rank instead of writing it. */
+static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                        const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
+                        const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
+                        float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, const nwc_tp_io *tp) {
     if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1 || mode < 0 || mode > 2) return -1;
     if (!aligned16(data) || !aligned16(low) || !aligned16(lut)) return -1;
     if (mode == kInputNorm && (!h_in || !norm_w || h_out == h_in)) return -1;
@@ -112,14 +119,31 @@ NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_
     if (!sms) return (int)cudaErrorNoDevice;
     const uint32_t M = (uint32_t)(n / K);
     const Geometry g(M, K, layout_of(elem));
-    if (layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) {
+    const bool peer_in = tp && tp->in_slot >= 0, peer_out = tp && tp->out_slot >= 0;
+    PeerOutput push{};
+    int in_mode = mode;
+    if (peer_in || peer_out) {
+        if (!tp->buffers || tp->world < 1 || tp->world > (int)kCommMaxRanks || tp->rank < 0 || tp->rank >= tp->world || !tp->H || (tp->H & 7u)) return -1;
+        for (int r = 0; r < tp->world; r++) if (!tp->buffers[r]) return -1;
+        if (peer_in && (mode != kInputNorm || K != tp->H || tp->in_slot > 1 || delta)) return -1;
+        if (peer_out && (M > tp->H || tp->out_slot > 1 || bias || scale)) return -1;
+        if (peer_in) in_mode = kInputPeerNorm;
+        /* both directions are part of the layout-2 ring kernel only */
+        if (!token_path_fuses_input(elem, M, K, in_mode)) return -2;
+        if (peer_out) {
+            for (int r = 0; r < tp->world; r++) push.buf[r] = static_cast<uint8_t *>(tp->buffers[r]);
+            push.world = (uint32_t)tp->world; push.rank = (uint32_t)tp->rank; push.slot = (uint32_t)tp->out_slot; push.H = tp->H;
+        }
+    }
+    FusedInput in{in_mode, h_in, delta, h_out, norm_w, eps, gate_up, nullptr, 0u, 0u, g_peer_timeout_ns};
+    if (peer_in) { in.comm = static_cast<const uint8_t *>(tp->buffers[tp->rank]); in.world = (uint32_t)tp->world; in.slot = (uint32_t)tp->in_slot; }
+    if (!peer_in && !peer_out && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) {
         SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
-        FusedInput in{mode, h_in, delta, h_out, norm_w, eps, gate_up};
         return (int)launch_small_layout0(elem, sms, (cudaStream_t)stream, a, in);
     }
-    if (mode != kInputPlain && token_path_fuses_input(elem, M, K, mode)) {
+    if (token_path_fuses_input(elem, M, K, in_mode)) {              /* the ring kernel builds x itself (a plain x too) */
         SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
-        const FusedInput in{mode, h_in, delta, h_out, norm_w, eps, gate_up};
+        a.fixup = 1u; a.push = push;
         return (int)launch_segments(0, elem, sms, (cudaStream_t)stream, a, &in);
     }
     const uint16_t *xin = x;
@@ -133,6 +157,23 @@ NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_
     return run_segments(0, stream, data, bases, hdr, lut, low, xin, scratch, nullptr, bias, scale, y, n, block, K, elem, 0, 1);
 }
 
+NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                                const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
+                                const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
+                                float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    return linear_fused(stream, data, bases, hdr, lut, low, mode, x, h_in, delta, h_out, norm_w, eps, gate_up, xtmp, bias, scale, scratch, y, n, block, K, elem, nullptr);
+}
+
+NWC_EXPORT int nwc_linear_fused_tp(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                                   const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
+                                   const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
+                                   float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, const nwc_tp_io *tp) {
+    return linear_fused(stream, data, bases, hdr, lut, low, mode, x, h_in, delta, h_out, norm_w, eps, gate_up, xtmp, bias, scale, scratch, y, n, block, K, elem, tp);
+}
+
+NWC_EXPORT void nwc_comm_set_timeout_ms(uint32_t ms) { g_peer_timeout_ns = (unsigned long long)(ms ? ms : 1u) * 1000000ull; }
+namespace nwc { unsigned long long peer_timeout_ns() { return g_peer_timeout_ns; } }
+
 /* number of kernels one token-path call launches on the current device: fused_mode -1 = nwc_linear_bf16 / nwc_linear_x16,
    0..2 = nwc_linear_fused with that mode */
 NWC_EXPORT int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_mode) {
@@ -142,7 +183,8 @@ NWC_EXPORT int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_m
     const uint32_t M = (uint32_t)(n / K);
     const Geometry g(M, K, layout_of(elem));
     if (fused_mode >= 0 && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) return 1;
-    return count_token_launches(elem, sms, M, K) + (fused_mode > 0 && !token_path_fuses_input(elem, M, K, fused_mode) ? 1 : 0);
+    const bool ring = fused_mode >= 0 && token_path_fuses_input(elem, M, K, fused_mode);
+    return count_token_launches(elem, sms, M, K, ring) + (fused_mode > 0 && !ring ? 1 : 0);
 }
 
 NWC_EXPORT void nwc_set_dependent_launch(int on) { set_dependent_launch(on != 0); }
@@ -173,14 +215,18 @@ NWC_EXPORT int nwc_gather(void *stream, const uint8_t *data, const uint32_t *bas
 NWC_EXPORT int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint64_t M, uint32_t K) {
     if (!M || !K || M > 0xFFFFFFFFull) return -1;
     if (((K & 15u) == 0u) && (!aligned16(w) || !aligned16(x))) return -1;
-    return (int)launch_native_fp8((cudaStream_t)stream, w, scale, x, y, (uint32_t)M, K);
+    const int sms = device_sms();
+    if (!sms) return (int)cudaErrorNoDevice;
+    return (int)launch_native_fp8(sms, (cudaStream_t)stream, w, scale, x, y, (uint32_t)M, K);
 }
 
 NWC_EXPORT int nwc_setup(void) { return device_sms(); }
 
 NWC_EXPORT int nwc_kernel_status(int clear) {
-    const int a = read_kernel_status(clear != 0), b = read_prefill_status(clear != 0), c = read_comm_status(clear != 0);
-    return a > b ? (a > c ? a : c) : (b > c ? b : c);
+    const int v[4] = {read_kernel_status(clear != 0), read_prefill_status(clear != 0), read_comm_status(clear != 0), read_model_status(clear != 0)};
+    int worst = v[0];
+    for (int i = 1; i < 4; i++) if (v[i] > worst) worst = v[i];
+    return worst;
 }
 
 /* Prefill: Y[T][ldy] = bf16(scale * (X[T][ldx] W^T) + bias) on the tcgen05 tensor cores, W decoded tile by tile.

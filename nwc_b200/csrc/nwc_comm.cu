@@ -1,11 +1,9 @@
 /* Tensor-parallel decode: the sum of the ranks' partial o / down outputs, fused with the residual add and the RMSNorm
  * that follow it, as one kernel over NVLink peer memory.
  *
- * Every rank owns one exchange buffer in its own HBM (cudaMalloc, exported to the other ranks of the node with CUDA IPC):
- *
- *     [0, 4)        call counter of this rank (written by this rank's kernel only)
- *     [64, 64+4W)   one arrival word per rank r: the last call number rank r has announced to this rank
- *     [256, ...)    two partial vectors ("slots") of H bf16 values, written by this rank's matvec kernels
+ * Every rank owns one exchange buffer in its own HBM (cudaMalloc, exported to the other ranks of the node with CUDA IPC);
+ * its layout is in nwc_comm.h.  This kernel is the "pull" protocol: the call counter and the arrival words of the
+ * header, and the two pull slots (partial vectors of H bf16 values written by this rank's own matvec kernels).
  *
  * Call n of every rank (one cluster of 8 CTAs; CTA 0 does the signalling): announce n to all peers (store into their arrival words, after a system-scope fence so that the
  * partial written by the preceding matvec is visible), wait until every peer has announced n, read all W partials with
@@ -25,8 +23,7 @@
 namespace nwc {
 namespace {
 
-constexpr uint32_t kCommHeader = 256, kCommMaxRanks = 8, kCommPolls = 1u << 21;
-constexpr int kStatusPeerTimeout = 3;
+constexpr uint32_t kCommPolls = 1u << 21;
 __device__ int g_comm_status;
 
 struct CommPeers { uint8_t *buf[kCommMaxRanks]; };
@@ -62,7 +59,7 @@ __global__ void __launch_bounds__(kCommThreads, 1) allreduce_add_rmsnorm_kernel(
     uint8_t *mine = peers.buf[rank];
     if (cta == 0) {                                                     /* CTA 0 talks to the other ranks */
         if (tid == 0) {
-            volatile uint32_t *counter = reinterpret_cast<volatile uint32_t *>(mine);
+            volatile uint32_t *counter = &reinterpret_cast<CommControl *>(mine)->pull_calls;
             const uint32_t n = *counter + 1u;
             *counter = n; call_number = n;
         }
@@ -71,8 +68,8 @@ __global__ void __launch_bounds__(kCommThreads, 1) allreduce_add_rmsnorm_kernel(
         bool arrived = true;
         if (tid < (uint32_t)world && tid != (uint32_t)rank) {
             __threadfence_system();
-            *reinterpret_cast<volatile uint32_t *>(peers.buf[tid] + 64u + 4u * (uint32_t)rank) = n;
-            const volatile uint32_t *word = reinterpret_cast<const volatile uint32_t *>(mine + 64u + 4u * tid);
+            *reinterpret_cast<volatile uint32_t *>(&reinterpret_cast<CommControl *>(peers.buf[tid])->pull_arrived[rank]) = n;
+            const volatile uint32_t *word = &reinterpret_cast<const CommControl *>(mine)->pull_arrived[tid];
             uint32_t polls = 0;
             while ((int32_t)(*word - n) < 0) {
                 if (++polls > kCommPolls) { arrived = false; break; }
@@ -91,7 +88,7 @@ __global__ void __launch_bounds__(kCommThreads, 1) allreduce_add_rmsnorm_kernel(
         uint4 part[kCommMaxRanks];
 #pragma unroll
         for (int r = 0; r < (int)kCommMaxRanks; r++)                    /* all peer loads in flight before the first add */
-            part[r] = r < world ? load_peer(peers.buf[r] + kCommHeader + slot_offset + (uint64_t)c * 16u) : make_uint4(0u, 0u, 0u, 0u);
+            part[r] = r < world ? load_peer(peers.buf[r] + slot_offset + (uint64_t)c * 16u) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int r = 0; r < (int)kCommMaxRanks; r++) {
             if (r < world) {
@@ -139,8 +136,6 @@ __global__ void __launch_bounds__(kCommThreads, 1) allreduce_add_rmsnorm_kernel(
     cluster.sync();                                                     /* CTA 0's shared memory stays alive until everybody has read it */
 }
 
-uint64_t slot_bytes(uint32_t H) { return ((uint64_t)H * 2u + 255u) & ~255ull; }
-
 }  // namespace
 
 int read_comm_status(bool clear) {
@@ -156,7 +151,7 @@ using namespace nwc;
 
 #define NWC_EXPORT extern "C" __attribute__((visibility("default")))
 
-NWC_EXPORT uint64_t nwc_comm_bytes(uint32_t H) { return kCommHeader + 2u * slot_bytes(H); }
+NWC_EXPORT uint64_t nwc_comm_bytes(uint32_t H) { return comm_total_bytes(H); }
 
 NWC_EXPORT int nwc_comm_alloc(void **buffer, uint32_t H) {
     if (!buffer || !H || (H & 7u)) return -1;
@@ -185,7 +180,7 @@ NWC_EXPORT int nwc_comm_import(const uint8_t *handle64, void **peer_buffer) {
 NWC_EXPORT int nwc_comm_release(void *peer_buffer) { return (int)cudaIpcCloseMemHandle(peer_buffer); }
 
 NWC_EXPORT uint16_t *nwc_comm_slot(void *buffer, uint32_t H, int slot) {
-    return reinterpret_cast<uint16_t *>(static_cast<uint8_t *>(buffer) + kCommHeader + (slot & 1) * slot_bytes(H));
+    return reinterpret_cast<uint16_t *>(static_cast<uint8_t *>(buffer) + comm_pull_offset(H, (uint32_t)slot));
 }
 
 NWC_EXPORT int nwc_allreduce_add_rmsnorm(void *stream, void *const *buffers, int rank, int world, int slot, const uint16_t *h_in, uint16_t *h_out,
@@ -202,5 +197,5 @@ NWC_EXPORT int nwc_allreduce_add_rmsnorm(void *stream, void *const *buffers, int
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = dependent_launch() ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel, peers, rank, world, (uint32_t)((slot & 1) * slot_bytes(H)), h_in, h_out, norm_w, eps, H, xn);
+    return (int)cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel, peers, rank, world, (uint32_t)comm_pull_offset(H, (uint32_t)slot), h_in, h_out, norm_w, eps, H, xn);
 }

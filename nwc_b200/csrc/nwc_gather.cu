@@ -213,10 +213,10 @@ __global__ void __launch_bounds__(256) native_fp8_kernel(const uint8_t *__restri
     }
 }
 
-cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K) {
+cudaError_t launch_native_fp8(int sms, cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K) {
     const uint32_t units = (M + kNativeRows - 1u) / kNativeRows;
     unsigned grid = (units + 7u) / 8u;
-    if (grid > 148u * 8u) grid = 148u * 8u;
+    if (grid > (unsigned)sms * 8u) grid = (unsigned)sms * 8u;
     native_fp8_kernel<<<grid, 256, 0, st>>>(w, scale, x, y, M, K);
     return cudaGetLastError();
 }

@@ -296,10 +296,43 @@ __device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float
 __device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) { return (uint32_t)bf16_round_nan(lo) | ((uint32_t)bf16_round_nan(hi) << 16); }
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) { asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
 
+__host__ __device__ __forceinline__ bool norm_like(int mode) { return mode == kInputNorm || mode == kInputPeerNorm; }
+
+__device__ __forceinline__ unsigned long long global_timer_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ uint4 ld_volatile128(const void *p) {                 /* never from L1: peers rewrite these addresses every other call */
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+/* kInputPeerNorm: wait until every rank of the group has pushed its partial of `in.slot` into this rank's exchange
+   buffer.  The flag this rank expects is its own push count for the slot (all ranks make the same sequence of calls; the
+   own push finished before this kernel passed its dependency wait).  The wait is bounded by the global timer; when it
+   runs out the status word is set to 3 and false is returned to every thread.  Ends with a CTA barrier. */
+__device__ __forceinline__ bool wait_for_pushes(const FusedInput &in) {
+    const CommControl *ctl = reinterpret_cast<const CommControl *>(in.comm);
+    bool ok = true;
+    if (threadIdx.x < in.world) {
+        const uint32_t epoch = *reinterpret_cast<const volatile uint32_t *>(&ctl->push_epoch[in.slot]);
+        const volatile uint32_t *flag = &ctl->push_flag[in.slot][threadIdx.x];
+        if ((int32_t)(*flag - epoch) < 0) {
+            const unsigned long long t0 = global_timer_ns();
+            while ((int32_t)(*flag - epoch) < 0) {
+                if (global_timer_ns() - t0 > in.timeout_ns) { ok = false; break; }
+                __nanosleep(20);
+            }
+        }
+        __threadfence_system();                                  /* the partials are read after the flags */
+    }
+    ok = __syncthreads_and(ok) != 0;
+    if (!ok && threadIdx.x == 0) atomicExch(&g_kernel_status, kStatusPeerTimeout);
+    return ok;
+}
+
 /* before the dependency wait: the RMSNorm weight (a constant) goes to shared memory */
 template <uint32_t THREADS>
 __device__ __forceinline__ void stage_norm_weight(const FusedInput &in, uint32_t K, uint16_t *nw) {
-    if (in.mode != kInputNorm || (K & 7u) != 0u) return;
+    if (!norm_like(in.mode) || (K & 7u) != 0u) return;
     const uint32_t nw_addr = smem_addr(nw);
     for (uint32_t c = threadIdx.x; c < (K >> 3); c += THREADS) sts128(nw_addr + c * 16u, __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c));
 }
@@ -310,7 +343,14 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t xs_addr = smem_addr(xs), nw_addr = smem_addr(nw), chunks = cols >> 3, live = K >> 3;   /* chunks of eight values */
     const bool vec = (K & 7u) == 0u;
-    if (in.mode == kInputNorm) {
+    if (norm_like(in.mode)) {
+        const bool peer = in.mode == kInputPeerNorm;             /* (the entry point admits this mode only with K % 8 == 0) */
+        if (peer && !wait_for_pushes(in)) {                      /* a rank is missing: poison x so that nothing downstream looks valid */
+            for (uint32_t c = tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u));
+            __syncthreads();
+            return;
+        }
+        const bool have_delta = peer || in.delta != nullptr;
         float ss = 0.f;
         if (vec) {
             for (uint32_t c = tid; c < chunks; c += THREADS) {
@@ -319,11 +359,27 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
                     const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
                     const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
                     uint32_t dw[4] = {0u, 0u, 0u, 0u}, ow[4];
-                    if (in.delta) { const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c); dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w; }
+                    if (peer) {                                  /* the ranks' partials, all loads in flight, added in rank order */
+                        uint4 part[kCommMaxRanks];
+#pragma unroll
+                        for (uint32_t r = 0; r < kCommMaxRanks; r++)
+                            part[r] = r < in.world ? ld_volatile128(in.comm + comm_push_offset(K, in.slot, r) + (uint64_t)c * 16u) : make_uint4(0u, 0u, 0u, 0u);
+                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (uint32_t r = 0; r < kCommMaxRanks; r++) {
+                            if (r < in.world) {
+                                const uint32_t pw[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+                                for (int k = 0; k < 4; k++) { acc[2 * k] += bf16_lo(pw[k]); acc[2 * k + 1] += bf16_hi(pw[k]); }
+                            }
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; k++) dw[k] = bf16_pack(acc[2 * k], acc[2 * k + 1]);
+                    } else if (in.delta) { const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c); dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w; }
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         float v0 = bf16_lo(hw[k]), v1 = bf16_hi(hw[k]);
-                        if (in.delta) { v0 = bf16_rt(v0 + bf16_lo(dw[k])); v1 = bf16_rt(v1 + bf16_hi(dw[k])); }
+                        if (have_delta) { v0 = bf16_rt(v0 + bf16_lo(dw[k])); v1 = bf16_rt(v1 + bf16_hi(dw[k])); }
                         ss += v0 * v0; ss += v1 * v1;
                         ow[k] = bf16_pack(v0, v1);
                     }
@@ -422,7 +478,7 @@ constexpr uint32_t kRingBarrierBytes = (kRingThreads / 32u) * kRingStages * 8u;
 constexpr uint32_t kRingMaxSmem = 232448u;                       /* 227 KB opt-in limit of a CTA */
 /* shared memory of the layout-2 ring kernel: x (32 columns per slot, bf16), the barriers, then the per-warp rings */
 __host__ __device__ static inline uint32_t ring_x_bytes(const Geometry &g) { return (g.slots * 64u + 127u) & ~127u; }
-static inline uint32_t ring_smem_bytes(const Geometry &g, int input_mode = kInputPlain) { return (input_mode == kInputNorm ? 2u : 1u) * ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + 256u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
+static inline uint32_t ring_smem_bytes(const Geometry &g, int input_mode = kInputPlain) { return (norm_like(input_mode) ? 2u : 1u) * ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + 256u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
 
 struct FlatPlan {
     uint32_t units_per_group;   /* slots (layout 2) or blocks (layouts 0, 1) per row group                              */
@@ -431,6 +487,8 @@ struct FlatPlan {
     uint32_t warps;             /* warps that take part; warp w owns chunks [w * chunks / warps, (w + 1) * chunks / warps) */
     uint32_t parts;             /* row stride of the partial sums = most warps that can share a row group               */
     uint32_t direct;            /* 1: no row group is cut, warps write y themselves                                      */
+    uint32_t fix;               /* 1 (layout 2 ring kernel, direct == 0): a cut row group is completed inside the kernel by
+                                   the CTA that arrives last at the group's counter, no finalize launch                   */
     __host__ __device__ __forceinline__ uint64_t start(uint32_t w) const { return ((uint64_t)w * chunks / warps) * grain; }
     /* the warp whose run holds unit u */
     __host__ __device__ __forceinline__ uint32_t owner(uint64_t u) const { return (uint32_t)(((u / grain + 1u) * warps - 1u) / chunks); }
@@ -442,6 +500,32 @@ __device__ __forceinline__ void emit_flat(const SegmentArgs &a, const FlatPlan &
     if (a.scale) v *= __ldg(a.scale + row);
     if (a.bias) v += bf16_to_float(__ldg(a.bias + row));
     a.y[row] = bf16_round(v);
+}
+
+/* Arrival counters of the row groups that a run boundary cuts (fix-up plans): one per CTA of the grid, indexed by the
+   first CTA that holds a part of the group; zero between kernels (the last arriver clears its counter).  One set per
+   device, so launches that use fix-up plans must be in stream order on their device. */
+constexpr uint32_t kFixCounters = 1024;
+static __device__ unsigned int g_fix_arrivals[kFixCounters];
+
+/* The 16 finished rows of row group `grp`, one per lane of a half-warp (`sub` = lane & 15 = row inside the group, `mask`
+   = the 16 lanes, all of which make this call): scale, bias and bf16 rounding as the reference's finalize step, then
+   either the local y or, for a row-parallel matrix of a tensor-parallel group, the push slot of EVERY rank's exchange
+   buffer (plain 4-byte stores over NVLink, two rows each; the flag that publishes them is raised at the kernel's end). */
+__device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, uint32_t sub, float v, uint32_t mask) {
+    const uint32_t row = grp * 16u + sub;
+    const bool live = row < a.M;
+    if (live && a.scale) v *= __ldg(a.scale + row);
+    if (live && a.bias) v += bf16_to_float(__ldg(a.bias + row));
+    const uint32_t h = live ? (uint32_t)bf16_round(v) : 0u;
+    if (a.push.world == 0u) { if (live) a.y[row] = (uint16_t)h; return; }
+    const uint32_t pair = h | (__shfl_down_sync(mask, h, 1) << 16);
+    if ((sub & 1u) == 0u && live) {
+        const uint64_t off = comm_push_offset(a.push.H, a.push.slot, a.push.rank) + (uint64_t)row * 2u;
+#pragma unroll
+        for (uint32_t p = 0; p < kCommMaxRanks; p++)
+            if (p < a.push.world) *reinterpret_cast<volatile uint32_t *>(a.push.buf[p] + off) = pair;
+    }
 }
 
 /* Exceptions of one block (column block cb) for this lane: sum of value * x over the lane's `count` entries, split by
@@ -477,7 +561,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Geometry g(a.M, a.K, 2);
     /* shared memory: x | RMSNorm weight (kInputNorm only) | shared row groups | reduction scratch | barriers | rings */
-    const uint32_t xs = smem_addr(ring_smem), x_bytes = ring_x_bytes(g), front = in.mode == kInputNorm ? 2u * x_bytes : x_bytes;
+    const uint32_t xs = smem_addr(ring_smem), x_bytes = ring_x_bytes(g), front = norm_like(in.mode) ? 2u * x_bytes : x_bytes;
     uint32_t *share_group = reinterpret_cast<uint32_t *>(ring_smem + front);
     float *share_value = reinterpret_cast<float *>(ring_smem + front + kRingEntries * 4u);
     float *scal = reinterpret_cast<float *>(ring_smem + front + kRingShareBytes);
@@ -533,7 +617,11 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
         const float lo = d[0] + ex_lo, hi = d[2] + ex_hi;
         const uint32_t r = lane >> 2;
         if (seg_first == 0u && s == slots) {                     /* a whole row group: nobody else adds to it */
-            if ((lane & 3u) == 0u) {
+            if (plan.direct || plan.fix) {                       /* final: row i of the group to lane i < 16, from the quad leader that holds it */
+                const uint32_t src = (lane & 7u) << 2;
+                const float vlo = __shfl_sync(0xffffffffu, lo, src), vhi = __shfl_sync(0xffffffffu, hi, src);
+                if (lane < 16u) emit_group(a, rb, lane, (lane & 8u) ? vhi : vlo, 0x0000FFFFu);
+            } else if ((lane & 3u) == 0u) {
                 const uint32_t part = cluster_id - plan.owner((uint64_t)rb * slots);
                 emit_flat(a, plan, rb * 16u + r, part, lo); emit_flat(a, plan, rb * 16u + r + 8u, part, hi);
             }
@@ -614,7 +702,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
                 if (gn == grp) v += share_value[n * 16u + row]; else if (gn != kNoGroup) break;
             }
             const uint64_t g0 = (uint64_t)grp * slots;
-            if (cluster_ctas == 1u || (g0 >= c0 && g0 + slots <= c1)) emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner(g0), v);
+            const bool inside = g0 >= c0 && g0 + slots <= c1;
+            const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16u);
+            if (plan.direct ? (cluster_ctas == 1u || inside) : (plan.fix && inside)) emit_group(a, grp, row, v, half_mask);
+            else if (cluster_ctas == 1u) emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner(g0), v);      /* one fp32 partial per CTA */
             else {
                 const uint32_t which = g0 < c0 ? 0u : 1u;            /* the group began before this CTA's run: its first group */
                 cta_value[which * 16u + row] = v;
@@ -634,10 +725,54 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
                     if (theirs == grp) v += cluster.map_shared_rank(cta_value, r)[row];
                     else if (theirs != kNoGroup) break;          /* (no entry: an empty run, or one that starts on a group boundary) */
                 }
-                emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner((uint64_t)grp * slots), v);
+                emit_group(a, grp, row, v, 0xFFFFu << (threadIdx.x & 16u));
             }
         }
         cluster.sync();                                             /* nobody leaves while its shared memory may still be read */
+    }
+    /* Fix-up plans: the row groups cut by this CTA's run boundaries (its first and its last one, at most) now hold this
+       CTA's partial.  One lane per group counts the arrival; the CTA that arrives last adds the partials in CTA order
+       (so the sum does not depend on timing), writes the rows and clears the counter. */
+    if (plan.fix) {
+        __syncthreads();                                            /* this CTA's partials are written */
+        if (warp == 0u && cn != 0u) {
+            const uint32_t half = lane >> 4, sub = lane & 15u, half_mask = 0xFFFFu << (16u * half);
+            const uint32_t first_group = (uint32_t)(c0 / slots), last_group = (uint32_t)((c1 - 1u) / slots);
+            const uint32_t grp = half ? last_group : first_group;
+            const uint64_t g0 = (uint64_t)grp * slots;
+            const bool cut = !(g0 >= c0 && g0 + slots <= c1);
+            if (cut && !(half && last_group == first_group)) {
+                const uint32_t first_owner = plan.owner(g0), holders = plan.owner(g0 + slots - 1u) - first_owner + 1u;
+                uint32_t last = 0u;
+                if (sub == 0u) { __threadfence(); last = atomicAdd(&g_fix_arrivals[first_owner], 1u) == holders - 1u ? 1u : 0u; }
+                last = __shfl_sync(half_mask, last, 16u * half);
+                if (last) {
+                    __threadfence();
+                    float v = 0.f;
+                    for (uint32_t p = 0; p < holders; p++) v += __ldcg(a.y32 + (uint64_t)(grp * 16u + sub) * plan.parts + p);
+                    emit_group(a, grp, sub, v, half_mask);
+                    if (sub == 0u) g_fix_arrivals[first_owner] = 0u;
+                }
+            }
+        }
+    }
+    /* Tensor-parallel output: the CTA that finishes last publishes this rank's partial.  Every CTA orders its peer stores
+       before its arrival with a system-scope fence; the last one raises this rank's flag in every buffer. */
+    if (a.push.world) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
+            __threadfence_system();
+            if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
+                own->push_done = 0u;
+                volatile uint32_t *count = &own->push_epoch[a.push.slot];
+                const uint32_t epoch = *count + 1u;
+                *count = epoch;
+                __threadfence_system();
+                for (uint32_t p = 0; p < a.push.world; p++)
+                    *reinterpret_cast<volatile uint32_t *>(&reinterpret_cast<CommControl *>(a.push.buf[p])->push_flag[a.push.slot][a.push.rank]) = epoch;
+            }
+        }
     }
 }
 
@@ -671,6 +806,7 @@ static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t
     }
     p.warps = (uint32_t)use;
     p.direct = p.grain % units_per_group == 0u ? 1u : 0u;
+    p.fix = 0u;
     p.parts = p.direct ? 1u : (uint32_t)((units_per_group - 1u) / (total / use)) + 2u;
     if (p.parts > g.CB) p.parts = g.CB;                                        /* bound above guarantees the true count fits */
 }
@@ -692,10 +828,14 @@ static ClusterRoom cluster_room(int sms);
    groups per cluster of 2, 4 or 8 CTAs that split them (one launch each, bf16 y written by the kernel; the larger the
    cluster the finer the split but the fewer SMs), or equal runs of slots per CTA with per-CTA partials and the finalize
    launch.  Cost = slots the busiest CTA streams, plus what the extra synchronisation or launch is worth in slots. */
-static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p, uint32_t &cluster) {
+/* With allow_fix the equal runs need no second launch: cut row groups are completed inside the kernel (FlatPlan::fix), which
+   is worth about kFixSlots slots (a CTA barrier, one atomic and a few dependent loads at the kernel's end). */
+constexpr uint64_t kFixSlots = 64;
+static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p, uint32_t &cluster, bool allow_fix = false) {
     const uint64_t total = (uint64_t)g.groups * g.slots;
     const ClusterRoom room = cluster_room(sms);
-    uint64_t best = (total + (uint64_t)sms - 1u) / (uint64_t)sms + kFinalizeSlots;
+    if (sms > (int)kFixCounters) allow_fix = false;
+    uint64_t best = (total + (uint64_t)sms - 1u) / (uint64_t)sms + (allow_fix ? kFixSlots : kFinalizeSlots);
     uint32_t best_cluster = 0;                                   /* 0 = equal runs + finalize */
     for (uint32_t lg = 0; lg < 4u; lg++) {
         const uint64_t clusters = lg == 0u ? (uint64_t)sms : (uint64_t)room.count[lg];
@@ -705,7 +845,11 @@ static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p, uint3
         if (cost < best) { best = cost; best_cluster = 1u << lg; }
     }
     cluster = best_cluster ? best_cluster : 1u;
-    if (best_cluster == 0u) { make_flat_plan(g, g.slots, (uint64_t)sms, p, false); if (!p.direct) return; cluster = 1u; }   /* (a single column block forces whole groups) */
+    if (best_cluster == 0u) {                                     /* (a single column block forces whole groups) */
+        make_flat_plan(g, g.slots, (uint64_t)sms, p, false);
+        if (!p.direct) { p.fix = allow_fix ? 1u : 0u; return; }
+        cluster = 1u;
+    }
     make_flat_plan(g, g.slots, cluster == 1u ? (uint64_t)sms : (uint64_t)room.count[cluster == 2u ? 1 : (cluster == 4u ? 2 : 3)], p, true);
 }
 
@@ -1194,13 +1338,13 @@ uint32_t choose_splits(const Geometry &g, int mode, int code, int sms) {
 }
 
 /* kernels the token path launches for an M x K matrix (automatic splits) */
-int count_token_launches(int code, int sms, uint32_t M, uint32_t K) {
+int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_fix) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(M, K, layout);
     FlatPlan plan;
     if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
     if (!g_disable_ring && layout == 1) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan); return plan.direct ? 1 : 2; }
-    if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { uint32_t cluster; make_cta_plan_layout2(g, sms, plan, cluster); return plan.direct ? 1 : 2; }
+    if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { uint32_t cluster; make_cta_plan_layout2(g, sms, plan, cluster, allow_fix); return plan.direct || plan.fix ? 1 : 2; }
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
@@ -1246,13 +1390,13 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
         }
         return err;
     }
-    FusedInput in{kInputPlain, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr};
+    FusedInput in{kInputPlain, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr, nullptr, 0u, 0u, 0ull};
     if (input) in = *input;
     if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_smem_bytes(g, in.mode) <= kRingMaxSmem) {
         uint32_t cluster;
-        make_cta_plan_layout2(g, sms, plan, cluster);
+        make_cta_plan_layout2(g, sms, plan, cluster, a.fixup != 0u);
         err = launch_cluster_kernel(ring_kernel_layout2, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
-        if (err == cudaSuccess && !plan.direct)
+        if (err == cudaSuccess && !plan.direct && !plan.fix)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
     }

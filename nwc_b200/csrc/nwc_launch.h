@@ -3,6 +3,7 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 #include "nwc_geometry.h"
+#include "nwc_comm.h"
 
 namespace nwc {
 
@@ -25,10 +26,14 @@ struct SegmentArgs {
     uint32_t splits;            /* K splits per row group; 0 = let the launcher choose                       */
     int x_bf16;                 /* token path of layout 0: x is bf16[K16] instead of fp32[K16]                */
     uint32_t splits_forced;     /* the caller's own splits request (0 = none): forced splits take the plain kernels */
+    uint32_t fixup;             /* 1: equal runs per CTA are allowed, row groups cut by a run boundary are completed inside
+                                   the kernel by the CTA that arrives last (per-device arrival counters: calls that set
+                                   this must be in stream order on their device)                                    */
+    PeerOutput push;            /* world > 0: y goes to every rank's exchange buffer instead of a.y                   */
 };
 
 /* How the fused small-matrix kernel builds its activation vector. */
-enum FusedInputMode : int { kInputPlain = 0, kInputNorm = 1, kInputSwiglu = 2 };
+enum FusedInputMode : int { kInputPlain = 0, kInputNorm = 1, kInputSwiglu = 2, kInputPeerNorm = 3 };
 struct FusedInput {
     int mode;
     const uint16_t *h_in;       /* kInputNorm: residual stream in (bf16[K])                         */
@@ -37,6 +42,11 @@ struct FusedInput {
     const uint16_t *norm_w;     /* kInputNorm: RMSNorm weight                                       */
     float eps;
     const uint16_t *gate_up;    /* kInputSwiglu: [gate | up], 2 K values                            */
+    /* kInputPeerNorm: as kInputNorm with delta = the sum, in rank order, of the `world` partial vectors that the ranks of
+       a tensor-parallel group pushed into push slot `slot` of this rank's exchange buffer `comm` */
+    const uint8_t *comm;
+    uint32_t world, slot;
+    unsigned long long timeout_ns;   /* longest wait for the peers' flags */
 };
 cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in);
 void set_dependent_launch(bool on);           /* programmatic dependent launch for the decode-step launches */
@@ -49,12 +59,16 @@ int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gav
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input = nullptr);
 bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode);
 void configure_segment_kernels();
-int count_token_launches(int code, int sms, uint32_t M, uint32_t K);
+int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_fix = false);
 
 cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy);
 int read_prefill_status(bool clear);
+void configure_prefill_kernels();
+int read_model_status(bool clear);           /* 0, or 3 when the sharded argmax gave up waiting for a rank */
+unsigned long long peer_timeout_ns();        /* longest wait for other ranks inside a kernel (nwc_comm_set_timeout_ms) */
+void configure_model_kernels();              /* per-device opt-ins of the decode-step kernels */
 int read_comm_status(bool clear);            /* 0, or 3 when a rank gave up waiting for its peers */
 cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids);
-cudaError_t launch_native_fp8(cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);
+cudaError_t launch_native_fp8(int sms, cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);
 
 }  // namespace nwc

@@ -193,19 +193,27 @@ __global__ void swiglu_kernel(const uint16_t *__restrict__ gu, uint32_t I, uint1
 
 /* Greedy choice: smallest index of the largest logit.  Every CTA folds its slice into one 64-bit key (order-preserving
    image of the value in the high word, inverted index in the low word) and takes the maximum into a device word; the
-   CTA that arrives last writes the token for the next step, logs it, advances pos and step, and clears the two words
-   for the next call.  Calls on one device must not overlap (they share the two words). */
+   CTA that arrives last writes the token for the next step, logs it, advances pos and step (only while the log and the
+   position range have room), and clears the two words for the next call.  Calls on one device must not overlap (they
+   share the two words).
+   Vocabulary-sharded logits (peers.world > 0): the last CTA first exchanges its rank's best with the other ranks - one
+   8-byte word per rank, stored into every rank's exchange buffer: call number (16 bits) | order-preserving bf16 value
+   (16 bits) | inverted GLOBAL index (32 bits) - then waits (bounded) until the word of every rank carries this call's
+   number and takes the largest.  Every rank ends with the same token without an all-gather of the logits. */
 static __device__ unsigned long long g_argmax_key;
 static __device__ unsigned int g_argmax_arrived;
+static __device__ int g_model_status;
 
 __device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t i) {
     uint32_t u = __float_as_uint(v);
     u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
     return ((unsigned long long)u << 32) | (0xFFFFFFFFu - i);
 }
+__device__ __forceinline__ unsigned long long timer_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 
 __global__ void __launch_bounds__(256) argmax_kernel(const uint16_t *__restrict__ logits, uint32_t V, int64_t *__restrict__ cur, int64_t *__restrict__ log,
-                                                      int32_t *__restrict__ pos, int32_t *__restrict__ step) {
+                                                      int32_t *__restrict__ pos, int32_t *__restrict__ step, uint32_t log_len, uint32_t max_pos,
+                                                      const nwc::PeerOutput peers, unsigned long long timeout_ns) {
     __shared__ unsigned long long best_of_warp[8];
     dependency_sync();
     unsigned long long best = 0ull;
@@ -232,10 +240,37 @@ __global__ void __launch_bounds__(256) argmax_kernel(const uint16_t *__restrict_
             __threadfence();
             const unsigned long long key = atomicExch(&g_argmax_key, 0ull);
             g_argmax_arrived = 0u;
-            const uint32_t idx = key ? 0xFFFFFFFFu - (uint32_t)key : 0u;
+            uint32_t idx = key ? 0xFFFFFFFFu - (uint32_t)key : 0u;
+            if (peers.world) {
+                nwc::CommControl *own = reinterpret_cast<nwc::CommControl *>(peers.buf[peers.rank]);
+                volatile uint32_t *calls = &own->argmax_epoch;
+                const uint32_t call = *calls + 1u;
+                *calls = call;
+                const unsigned long long tag = (unsigned long long)(call & 0xFFFFu) << 48;
+                const unsigned long long mine = tag | ((key >> 48) << 32) | (unsigned long long)(0xFFFFFFFFu - (idx + peers.rank * V));
+                for (uint32_t p = 0; p < peers.world; p++)
+                    *reinterpret_cast<volatile unsigned long long *>(&reinterpret_cast<nwc::CommControl *>(peers.buf[p])->argmax_key[peers.rank]) = mine;
+                unsigned long long top = 0ull;
+                const unsigned long long t0 = timer_ns();
+                for (uint32_t r = 0; r < peers.world; r++) {
+                    const volatile unsigned long long *slot = &own->argmax_key[r];
+                    unsigned long long w = *slot;
+                    while ((w >> 48) != (tag >> 48)) {
+                        if (timer_ns() - t0 > timeout_ns) { atomicExch(&g_model_status, nwc::kStatusPeerTimeout); w = mine; break; }
+                        __nanosleep(20);
+                        w = *slot;
+                    }
+                    w &= 0xFFFFFFFFFFFFull;
+                    top = w > top ? w : top;
+                }
+                idx = 0xFFFFFFFFu - (uint32_t)top;
+            }
             cur[0] = (int64_t)idx;
-            if (log) log[*step] = (int64_t)idx;
-            *pos += 1; *step += 1;
+            const int32_t s = *step, p = *pos;
+            if (s >= 0 && (uint32_t)s < log_len && p >= 0 && (uint32_t)p < max_pos) {
+                if (log) log[s] = (int64_t)idx;
+                *pos = p + 1; *step = s + 1;
+            }
         }
     }
 }
@@ -267,8 +302,7 @@ NWC_EXPORT int nwc_attention_decode(void *stream, const uint16_t *qkv, const uin
     if (!n_q || !n_kv || n_q % n_kv || head_dim % 8 || head_dim > 256 || head_dim < 32 || max_len == 0 || max_len > 8192) return -1;
     const size_t floats = 2 * (size_t)head_dim + max_len, need = (256u / (head_dim / 8u)) * (size_t)head_dim;   /* scores, or the group partials */
     const size_t smem = (floats > need ? floats : need) * sizeof(float);
-    static bool opted = false;
-    if (smem > 48 * 1024 && !opted) { cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024); opted = true; }
+    if (!nwc_setup()) return (int)cudaErrorNoDevice;             /* prepares this device's kernels on first use */
     return (int)launch(attention_decode_kernel, dim3(n_q), dim3(256), smem, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, head_dim,
                        max_len, eps, 1.0f / sqrtf((float)head_dim), out, status);
 }
@@ -278,9 +312,36 @@ NWC_EXPORT int nwc_swiglu(void *stream, const uint16_t *gate_up, uint32_t I, uin
     return (int)launch(swiglu_kernel, dim3((I + 255) / 256), dim3(256), 0, stream, gate_up, I, a16, a32);
 }
 
-NWC_EXPORT int nwc_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step) {
-    if (!V) return -1;
+static int run_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step, uint32_t log_len,
+                      uint32_t max_pos, const nwc::PeerOutput &peers) {
+    if (!V || !cur || !pos || !step) return -1;
     if (reinterpret_cast<uintptr_t>(logits) & 15u) return -1;
     const uint32_t chunks = V >> 3, grid = chunks >= 256u * 64u ? 64u : (chunks + 255u) / 256u + (chunks ? 0u : 1u);
-    return (int)launch(argmax_kernel, dim3(grid ? grid : 1u), dim3(256), 0, stream, logits, V, cur, log, pos, step);
+    return (int)launch(argmax_kernel, dim3(grid ? grid : 1u), dim3(256), 0, stream, logits, V, cur, log, pos, step, log_len, max_pos, peers, nwc::peer_timeout_ns());
 }
+
+NWC_EXPORT int nwc_argmax(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step, uint32_t log_len,
+                          uint32_t max_pos) {
+    return run_argmax(stream, logits, V, cur, log, pos, step, log_len, max_pos, nwc::PeerOutput{});
+}
+
+NWC_EXPORT int nwc_argmax_tp(void *stream, const uint16_t *logits, uint32_t V, int64_t *cur, int64_t *log, int32_t *pos, int32_t *step, uint32_t log_len,
+                             uint32_t max_pos, void *const *buffers, int rank, int world) {
+    if (!buffers || world < 1 || world > (int)nwc::kCommMaxRanks || rank < 0 || rank >= world || (uint64_t)V * (uint64_t)world > 0xFFFFFFFFull) return -1;
+    nwc::PeerOutput peers{};
+    for (int r = 0; r < world; r++) { if (!buffers[r]) return -1; peers.buf[r] = static_cast<uint8_t *>(buffers[r]); }
+    peers.world = (uint32_t)world; peers.rank = (uint32_t)rank;
+    return run_argmax(stream, logits, V, cur, log, pos, step, log_len, max_pos, peers);
+}
+
+namespace nwc {
+/* dynamic shared memory beyond 48 KB for long caches; attributes of a function are per device */
+void configure_model_kernels() { cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024); }
+
+int read_model_status(bool clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_model_status, sizeof(int)) != cudaSuccess) return -1;
+    if (clear && v) { const int z = 0; cudaMemcpyToSymbol(g_model_status, &z, sizeof(int)); }
+    return v;
+}
+}  // namespace nwc

@@ -163,13 +163,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
 }
 
 cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy) {
-    static bool opted = false;
-    if (!opted) { cudaFuncSetAttribute(prefill_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem); opted = true; }
     PrefillArgs p{w, X, Y, T, ldx, ldy};
     const dim3 grid((w.M + kPfRows - 1u) / kPfRows, (T + kPfMaxTokens - 1u) / kPfMaxTokens);
     prefill_kernel_layout2<<<grid, kPfThreads, kPfSmem, st>>>(p);
     return cudaGetLastError();
 }
+
+/* shared-memory opt-in of the prefill kernel on the current device (attributes of a function are per device) */
+void configure_prefill_kernels() { cudaFuncSetAttribute(prefill_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem); }
 
 int read_prefill_status(bool clear) {
     int v = 0;

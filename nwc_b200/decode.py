@@ -8,42 +8,14 @@ counter live in device memory, so the captured graph is replayed unchanged for e
 
 Architectures: Qwen3 (per-head q/k RMSNorm, tied or untied embeddings) and Llama-3 style (no q/k norm) decoders.
 """
-from dataclasses import dataclass
-
 import ctypes
 
 import torch
 
 from . import _lib as L
 from . import tp as TP
+from .presets import PRESETS, DecoderConfig
 from .weight import NWCWeight
-
-
-@dataclass
-class DecoderConfig:
-    name: str
-    layers: int
-    hidden: int
-    intermediate: int
-    n_q: int
-    n_kv: int
-    head_dim: int
-    vocab: int
-    tied: bool
-    qk_norm: bool
-    rope_theta: float = 1e6
-    eps: float = 1e-6
-
-    @property
-    def qkv_rows(self): return (self.n_q + 2 * self.n_kv) * self.head_dim
-
-
-PRESETS = {
-    "qwen3-0.6b": DecoderConfig("qwen3-0.6b", 28, 1024, 3072, 16, 8, 128, 151936, True, True),
-    "qwen3-4b": DecoderConfig("qwen3-4b", 36, 2560, 9728, 32, 8, 128, 151936, False, True),
-    "llama3-70b": DecoderConfig("llama3-70b", 80, 8192, 28672, 64, 8, 128, 128256, False, False, rope_theta=5e5, eps=1e-5),
-    "tiny": DecoderConfig("tiny", 2, 256, 1000, 4, 2, 64, 4096, True, True),
-}
 
 
 def synthetic_matrix(rows, cols, seed, device="cuda"):
@@ -114,17 +86,23 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="peer"):
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push"):
         """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None.
-        tp_reduce: "peer" sums the ranks' partial o / down outputs with this library's kernel over NVLink peer memory
-        (fused with the residual add and the RMSNorm that follow); "nccl" uses one NCCL all-reduce instead."""
+        tp_reduce, how the ranks' partial o / down outputs are summed:
+          "push"  the row-parallel matvec stores its partial into every rank's exchange buffer over NVLink and the next
+                  matvec's prologue adds them (no kernel of its own; layout 2 bf16 matrices, else "pull" is used);
+          "pull"  one kernel of this library per sum reads the peers' partials over NVLink (also called "peer");
+          "nccl"  one NCCL all-reduce per sum."""
         L.require_cuda()
         self.dependent_launch = bool(dependent_launch)
         self.tp_group, self.tp_world = tp_group, weights.tp_world
         if self.tp_world > 1 and tp_group is None: raise ValueError("sharded weights need the process group of their ranks")
-        if tp_reduce not in ("peer", "nccl"): raise ValueError("tp_reduce is 'peer' or 'nccl'")
+        if tp_reduce == "peer": tp_reduce = "pull"
+        if tp_reduce not in ("push", "pull", "nccl"): raise ValueError("tp_reduce is 'push', 'pull' or 'nccl'")
+        if tp_reduce == "push" and not all(w.layout == 2 and w.elem == 0 for w in weights.matrices()): tp_reduce = "pull"
+        self.tp_reduce = tp_reduce if self.tp_world > 1 else None
         self.peers = None
-        if self.tp_world > 1 and tp_reduce == "peer":
+        if self.tp_world > 1 and tp_reduce in ("push", "pull"):
             from .comm import PeerBuffers
             self.peers = PeerBuffers(tp_group, weights.cfg.hidden)
         self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
@@ -154,15 +132,30 @@ class DecodeEngine:
         if weights.embed.scale is not None: raise NotImplementedError("fp8 embedding tables are not supported by the decode loop")
 
     # ---- one token, eager: every call below is one or two kernels of this library on the current stream ----
-    def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None):
+    def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None, tp_in=-1, tp_out=-1):
         """y = W x with the activation prologue the mode names (0: x given; 1: x = RMSNorm(h_in + delta), h_out updated;
-        2: x = SwiGLU(gate_up)), through nwc_linear_fused."""
+        2: x = SwiGLU(gate_up)), through nwc_linear_fused.  tp_in / tp_out: push slots of the tensor-parallel exchange
+        (delta = the ranks' summed partials of slot tp_in; y pushed to every rank's slot tp_out instead of written)."""
         out = y if isinstance(y, ctypes.c_void_p) else L.ptr(y)      # a raw device pointer: this rank's slot of the exchange buffer
-        err = L.lib.nwc_linear_fused(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
-                                     L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), self.cfg.eps, L.ptr(gate_up), L.ptr(self.xtmp), None, L.ptr(w.scale),
-                                     L.ptr(w.scratch), out, w.n, w.block, w.in_features, w.code)
+        tp = self.peers.io(tp_in, tp_out) if (tp_in >= 0 or tp_out >= 0) else None
+        err = L.lib.nwc_linear_fused_tp(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
+                                        L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), self.cfg.eps, L.ptr(gate_up), L.ptr(self.xtmp), None, L.ptr(w.scale),
+                                        L.ptr(w.scratch), out, w.n, w.block, w.in_features, w.code, tp)
         if err: raise RuntimeError(f"nwc_linear_fused error {err}")
         self._count += L.lib.nwc_linear_launches(w.n, w.in_features, w.code, mode)
+
+    def _argmax(self, c, st):
+        """Greedy token from this rank's logits; with exchange buffers the ranks swap one (value, index) word each."""
+        if self.peers is not None:
+            self._check(L.lib.nwc_argmax_tp(st(), L.ptr(self.logits), c.vocab, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no),
+                                            self.log.numel(), self.max_len, self.peers.table, self.peers.rank, self.peers.world), "nwc_argmax_tp")
+            return
+        if self.tp_world > 1:                                        # NCCL path: gather the vocabulary-sharded logits, every rank picks the same token
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.tp_group)
+            self._count += 1
+        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits_all), c.vocab * self.tp_world, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no),
+                                     self.log.numel(), self.max_len), "nwc_argmax")
 
     def _all_reduce(self, t):
         """Sum the row-parallel partial outputs over the tensor-parallel ranks (one NCCL all-reduce over NVLink)."""
@@ -209,16 +202,33 @@ class DecodeEngine:
             self.peers.allreduce_add_rmsnorm(1, h, h_next, nxt, c.eps, self.xn); self._count += 1
             h, h_next = h_next, h
         self._linear(w.lm_head, self.xn, self.logits)
-        import torch.distributed as dist
-        dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.tp_group)
-        self._count += 1
-        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits_all), c.vocab * self.tp_world, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
+        self._argmax(c, st)
+
+    def _forward_push(self, c, w, st, e, h, h_next):
+        """Tensor-parallel step with the sums over the ranks fused into the matvecs: o and down push their partial to every
+        rank, the matvec after them (gate/up, the next layer's q/k/v, the lm_head) adds the partials, the residual and
+        applies its RMSNorm while it builds x.  Five launches per layer, as on one GPU."""
+        self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(h),
+                                     e.n, e.block, e.in_features, e.code), "nwc_gather")
+        for i, l in enumerate(w.layers):
+            self._linear(l["qkv"], None, self.qkv, mode=1, h_in=h, h_out=h_next, norm_w=l["in_norm"], tp_in=1 if i else -1)
+            h, h_next = h_next, h
+            self._check(L.lib.nwc_attention_decode(st(), L.ptr(self.qkv), L.ptr(l["q_norm"]), L.ptr(l["k_norm"]), L.ptr(self.cos), L.ptr(self.sin),
+                                                   L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
+                                                   c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
+            self._linear(l["o"], self.attn, None, tp_out=0)
+            self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, h_out=h_next, norm_w=l["post_norm"], tp_in=0)
+            h, h_next = h_next, h
+            self._linear(l["down"], None, None, mode=2, gate_up=self.gu, tp_out=1)
+        self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, h_out=h_next, norm_w=w.final_norm, tp_in=1)
+        self._argmax(c, st)
 
     def close(self):
         """Release the exchange buffers (all ranks: after synchronising and a barrier)."""
         if self.peers is not None: self.peers.close(); self.peers = None
 
     def _forward(self, c, w, st, e, h, h_next):
+        if self.tp_reduce == "push": return self._forward_push(c, w, st, e, h, h_next)
         if self.peers is not None: return self._forward_peer(c, w, st, e, h, h_next)
         self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(h),
                                      e.n, e.block, e.in_features, e.code), "nwc_gather")
@@ -237,11 +247,7 @@ class DecodeEngine:
             self._all_reduce(self.proj2)
             delta = self.proj2
         self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=w.final_norm)
-        if self.tp_world > 1:                                        # vocabulary-sharded logits: gather, then every rank picks the same token
-            import torch.distributed as dist
-            dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.tp_group)
-            self._count += 1
-        self._check(L.lib.nwc_argmax(st(), L.ptr(self.logits_all), c.vocab * self.tp_world, L.ptr(self.cur), L.ptr(self.log), L.ptr(self.pos), L.ptr(self.step_no)), "nwc_argmax")
+        self._argmax(c, st)
 
     # ---- graph ----
     def capture(self, warmup=3):
@@ -268,24 +274,36 @@ class DecodeEngine:
         if self.graph is not None: self.graph.replay()
         else: self.forward_token()
 
+    def _check_status(self):
+        """After a synchronise: the position must have stayed inside the KV cache and no bounded wait inside a kernel
+        (bulk copy, peer rank) may have run out - a step that did is not a valid token."""
+        if int(self.status.item()): raise RuntimeError("decode position left the KV cache")
+        st = L.lib.nwc_kernel_status(1)
+        if st: raise RuntimeError(f"a bounded wait inside a kernel gave up (status {st}: 2 = bulk copy, 3 = a tensor-parallel rank did not answer)")
+
     def prefill(self, prompt_ids):
         """Feed the prompt token by token through the decode step (teacher forcing); returns the first generated token
         id as a device tensor.  Positions restart at 0."""
         self.reset()
         prompt = torch.as_tensor(prompt_ids, dtype=torch.int64, device=self.device).reshape(-1)
+        if prompt.numel() > self.max_len: raise ValueError(f"prompt of {prompt.numel()} tokens does not fit the KV cache ({self.max_len})")
         for i in range(prompt.numel()):
             self.cur.copy_(prompt[i:i + 1])
             self._run()
         self.step_no.zero_()
+        torch.cuda.synchronize()
+        self._check_status()
         return self.cur
 
     def generate(self, n_tokens):
         """n_tokens greedy steps from the current state; returns the generated ids (the token in self.cur is consumed
         first, its successors are returned)."""
-        start = int(self.step_no.item())
+        start, pos = int(self.step_no.item()), int(self.pos.item())
+        if pos + n_tokens > self.max_len or start + n_tokens > self.log.numel():
+            raise ValueError(f"{n_tokens} more tokens from position {pos} do not fit the KV cache ({self.max_len})")
         for _ in range(n_tokens): self._run()
         torch.cuda.synchronize()
-        if int(self.status.item()): raise RuntimeError("decode position left the KV cache")
+        self._check_status()
         return self.log[start:start + n_tokens].clone()
 
     def step(self, token_id: int) -> int:
@@ -295,4 +313,5 @@ class DecodeEngine:
         self._run()
         self.pinned_out.copy_(self.cur, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if self.tp_world > 1: self._check_status()                  # rank skew must never turn into a silently wrong token
         return int(self.pinned_out[0])

@@ -87,3 +87,124 @@ def test_two_local_ranks_add_in_rank_order_and_missing_peer_times_out():
         assert float(y.sum()) == 8.0
     finally:
         L.lib.nwc_comm_free(ctypes.c_void_p(a)); L.lib.nwc_comm_free(ctypes.c_void_p(b))
+
+
+# ---- the push protocol: partial sums stored into every rank's buffer by the row-parallel matvec, added by the next
+# matvec's prologue.  Two "ranks" = two exchange buffers on this GPU; their kernels run one after the other in stream
+# order (pushers first), so nothing ever waits for a kernel that has not been launched yet. ----
+
+def _tp_linear(L, nw, mode, tp, x=None, h_in=None, h_out=None, norm_w=None, gate_up=None, y=None, K=None):
+    pad = (nw.in_features + 31) // 32 * 32
+    xtmp = torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
+    return L.lib.nwc_linear_fused_tp(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), mode, L.ptr(x), L.ptr(h_in), None,
+                                     L.ptr(h_out), L.ptr(norm_w), 1e-6, L.ptr(gate_up), L.ptr(xtmp), None, None, L.ptr(nw.scratch), L.ptr(y), nw.n, nw.block,
+                                     nw.in_features, nw.code, tp)
+
+
+def _io(L, table, rank, world, in_slot, out_slot, H):
+    io = L.TpIo(ctypes.cast(table, ctypes.c_void_p), rank, world, in_slot, out_slot, H)
+    return io, ctypes.byref(io)
+
+
+@pytest.mark.parametrize("H,Kshard", [(1024, 512), (2048, 1536), (8192, 1024)])
+def test_push_protocol_two_local_ranks(H, Kshard):
+    """o-projection shards of two ranks push into both buffers; the consumer (a column-parallel matrix with the fused
+    peer prologue) must see h + (partial0 + partial1) and the RMSNorm of it, for both ranks alike, twice in a row."""
+    from nwc_b200 import NWCWeight, _lib as L
+    from nwc_b200.decode import synthetic_matrix
+    g = torch.Generator().manual_seed(H + Kshard)
+    o_shards = [NWCWeight(synthetic_matrix(H, Kshard, 10 + r), layout=2) for r in range(2)]       # row-parallel: [H, K / 2] each
+    consumer = NWCWeight(synthetic_matrix(768, H, 20), layout=2)                                  # the matrix after the sum
+    xs = [torch.randn(Kshard, generator=g).to(torch.bfloat16).cuda() for _ in range(2)]
+    h = torch.randn(H, generator=g).to(torch.bfloat16).cuda()
+    norm_w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
+    a, b = _buffers(L, H, 2)
+    table = (ctypes.c_void_p * 2)(a, b)
+    try:
+        for round_no in range(2):
+            slot = round_no & 1
+            parts = []
+            for r in range(2):                                            # both pushers first
+                keep, io = _io(L, table, r, 2, -1, slot, H)
+                assert _tp_linear(L, o_shards[r], 0, io, x=xs[r]) == 0
+                parts.append(o_shards[r].linear_bf16(xs[r], None))           # the same product through the plain entry point
+            total = (parts[0].float() + parts[1].float()).to(torch.bfloat16)
+            want_h = (h.float() + total.float()).to(torch.bfloat16)
+            want_x = torch.zeros(H, dtype=torch.bfloat16, device="cuda")
+            assert L.lib.nwc_add_rmsnorm(L.stream(), L.ptr(h), L.ptr(total), L.ptr(torch.zeros_like(h)), L.ptr(norm_w), 1e-6, H, L.ptr(want_x), None) == 0
+            want_y = consumer.linear_bf16(want_x, None)
+            for r in range(2):                                            # then both consumers: every flag is already there
+                keep, io = _io(L, table, r, 2, slot, -1, H)
+                h_out, y = torch.zeros_like(h), torch.zeros(768, dtype=torch.bfloat16, device="cuda")
+                assert _tp_linear(L, consumer, 1, io, h_in=h, h_out=h_out, norm_w=norm_w, y=y) == 0
+                torch.cuda.synchronize()
+                assert torch.equal(h_out, want_h), (round_no, r)
+                assert (y.float() - want_y.float()).abs().max().item() <= 2.0 ** -6 * want_y.float().abs().max().item() + 1e-6
+            assert L.lib.nwc_kernel_status(1) == 0
+    finally:
+        L.lib.nwc_comm_free(ctypes.c_void_p(a)); L.lib.nwc_comm_free(ctypes.c_void_p(b))
+
+
+def test_push_consumer_gives_up_when_a_rank_never_pushes():
+    """Rank 1 never pushes: rank 0's consumer waits the (shortened) limit, reports status 3 and poisons its output with
+    NaN instead of publishing a sum that misses a partial; the context stays usable."""
+    from nwc_b200 import NWCWeight, _lib as L
+    from nwc_b200.decode import synthetic_matrix
+    H = 1024
+    o0 = NWCWeight(synthetic_matrix(H, 512, 1), layout=2)
+    consumer = NWCWeight(synthetic_matrix(256, H, 2), layout=2)
+    x = torch.ones(512, dtype=torch.bfloat16, device="cuda")
+    h = torch.ones(H, dtype=torch.bfloat16, device="cuda")
+    a, b = _buffers(L, H, 2)
+    table = (ctypes.c_void_p * 2)(a, b)
+    L.lib.nwc_comm_set_timeout_ms(40)
+    try:
+        keep, io = _io(L, table, 0, 2, -1, 0, H)
+        assert _tp_linear(L, o0, 0, io, x=x) == 0
+        keep2, io2 = _io(L, table, 0, 2, 0, -1, H)
+        h_out, y = torch.zeros_like(h), torch.zeros(256, dtype=torch.bfloat16, device="cuda")
+        assert _tp_linear(L, consumer, 1, io2, h_in=h, h_out=h_out, norm_w=h, y=y) == 0
+        torch.cuda.synchronize()
+        assert L.lib.nwc_kernel_status(1) == 3
+        assert torch.isnan(y.float()).all()
+        assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+    finally:
+        L.lib.nwc_comm_set_timeout_ms(2000)
+        L.lib.nwc_comm_free(ctypes.c_void_p(a)); L.lib.nwc_comm_free(ctypes.c_void_p(b))
+
+
+def test_sharded_argmax_exchanges_one_word_per_rank():
+    """Two local ranks with half the vocabulary each.  Rank 0 runs first and cannot hear from rank 1 (its kernel is not
+    launched yet): bounded wait, status 3, local best.  Rank 1 then finds rank 0's word and must return the global
+    winner with its global index; log / pos / step obey their limits."""
+    from nwc_b200 import _lib as L
+    V = 4096
+    g = torch.Generator().manual_seed(3)
+    logits = [torch.randn(V, generator=g).to(torch.bfloat16).cuda() for _ in range(2)]
+    logits[0][1234] = 9.0; logits[1][77] = 8.0                          # the winner lives on rank 0
+    a, b = _buffers(L, 256, 2)
+    table = (ctypes.c_void_p * 2)(a, b)
+    L.lib.nwc_comm_set_timeout_ms(40)
+    try:
+        outs = []
+        for r in range(2):
+            cur = torch.zeros(1, dtype=torch.int64, device="cuda"); log = torch.full((4,), -1, dtype=torch.int64, device="cuda")
+            pos = torch.zeros(1, dtype=torch.int32, device="cuda"); step = torch.zeros(1, dtype=torch.int32, device="cuda")
+            assert L.lib.nwc_argmax_tp(L.stream(), L.ptr(logits[r]), V, L.ptr(cur), L.ptr(log), L.ptr(pos), L.ptr(step), 4, 16, table, r, 2) == 0
+            torch.cuda.synchronize()
+            outs.append((int(cur), int(log[0]), int(pos), int(step), L.lib.nwc_kernel_status(1)))
+        assert outs[0] == (1234, 1234, 1, 1, 3)                          # alone: its own best, and it says so
+        assert outs[1] == (1234, 1234, 1, 1, 0)                          # global winner (rank 0, index 1234)
+        # limits: a full log or a position at the end of the cache stops the increments, nothing is written past them
+        cur = torch.zeros(1, dtype=torch.int64, device="cuda"); log = torch.full((4,), -1, dtype=torch.int64, device="cuda")
+        pos = torch.full((1,), 16, dtype=torch.int32, device="cuda"); step = torch.full((1,), 2, dtype=torch.int32, device="cuda")
+        assert L.lib.nwc_argmax(L.stream(), L.ptr(logits[1]), V, L.ptr(cur), L.ptr(log), L.ptr(pos), L.ptr(step), 4, 16) == 0
+        torch.cuda.synchronize()
+        assert int(cur) == 77 and int(pos) == 16 and int(step) == 2 and log.tolist() == [-1, -1, -1, -1]
+        step.fill_(4); pos.fill_(3)
+        assert L.lib.nwc_argmax(L.stream(), L.ptr(logits[1]), V, L.ptr(cur), L.ptr(log), L.ptr(pos), L.ptr(step), 4, 16) == 0
+        torch.cuda.synchronize()
+        assert int(pos) == 3 and int(step) == 4 and log.tolist() == [-1, -1, -1, -1]
+    finally:
+        L.lib.nwc_comm_set_timeout_ms(2000)
+        L.lib.nwc_comm_free(ctypes.c_void_p(a)); L.lib.nwc_comm_free(ctypes.c_void_p(b))

@@ -11,7 +11,10 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("M,K,layout,elem", [(4096, 1024, 0, 0), (1024, 2048, 0, 0), (1024, 3072, 0, 0), (6144, 1024, 0, 0), (100, 1000, 0, 0), (13, 40, 0, 0),
                                              (1024, 5120, 0, 0), (256, 1024, 0, 1), (512, 1024, 2, 0), (512, 1024, 1, 0),
-                                             (6144, 2560, 2, 0), (2560, 9728, 2, 0), (100, 1000, 2, 0), (13, 40, 2, 0), (48, 1004, 2, 0)])
+                                             (6144, 2560, 2, 0), (2560, 9728, 2, 0), (100, 1000, 2, 0), (13, 40, 2, 0), (48, 1004, 2, 0),
+                                             # layout 2 shapes whose row groups do not divide over the SMs: equal runs per CTA, cut row groups completed
+                                             # inside the kernel by the last CTA to arrive (no finalize launch)
+                                             (1280, 8192, 2, 0), (2000, 4096, 2, 0), (4100, 3000, 2, 0), (16, 28672, 2, 0), (7168, 1536, 2, 0)])
 def test_fused_modes_match_separate_kernels(M, K, layout, elem):
     from gpu_helpers import bits, bf16_tensor, make_case, to_weight
     from nwc_b200 import _lib as L
@@ -42,9 +45,10 @@ def test_fused_modes_match_separate_kernels(M, K, layout, elem):
         a, b = O.bf16_to_f32(bits(a)), O.bf16_to_f32(bits(b))
         assert np.isfinite(a).all() and rel_l2(a, b) <= 2e-3, rel_l2(a, b)
 
-    # mode 0
+    # mode 0 (twice: the fix-up counters of the first call must be back at zero for the second)
     x0 = vec(pad); x0[K:] = 0
     close(fused(0, x=x0), separate(x0))
+    assert torch.equal(fused(0, x=x0), fused(0, x=x0))
     # mode 1: residual add + RMSNorm
     h_ref, xn = h_in.clone(), torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
     assert L.lib.nwc_add_rmsnorm(L.stream(), L.ptr(h_in), L.ptr(delta), L.ptr(h_ref), L.ptr(norm_w), 1e-6, K, L.ptr(xn), None) == 0

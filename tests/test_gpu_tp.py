@@ -21,18 +21,24 @@ rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 cfg = DecoderConfig("tiny-tp", 2, 256, 1024, 4, 2, 64, 2048, True, True)
-ref = DecodeEngine(DecoderWeights.synthetic(cfg, layout=0, seed=3), max_len=96)
-shards = DecoderWeights.synthetic(cfg, layout=0, seed=3, tp_rank=rank, tp_world=world)
+layout = int(os.environ["NWC_TP_LAYOUT"])
+ref = DecodeEngine(DecoderWeights.synthetic(cfg, layout=layout, seed=3), max_len=96)
+shards = DecoderWeights.synthetic(cfg, layout=layout, seed=3, tp_rank=rank, tp_world=world)
 prompt = list(range(5, 17))
 ref.prefill(prompt); want = ref.generate(32).tolist()
 seq = prompt + want
 sequences = {}
-for how, pdl in (("peer", True), ("peer", False), ("nccl", False)):        # this library's NVLink reduce (with and without dependent launch), NCCL
+# layout 2: sums pushed inside the matvec kernels; layout 0: the separate NVLink reduction kernel; NCCL as the baseline
+modes = (("push", True), ("push", False), ("pull", True), ("nccl", False)) if layout == 2 else (("pull", True), ("pull", False), ("nccl", False))
+for how, pdl in modes:
     tp = DecodeEngine(shards, max_len=96, tp_group=dist.group.WORLD, tp_reduce=how, dependent_launch=pdl)
+    assert tp.tp_reduce == how
     ref.reset(); tp.reset(); agree = close = 0
+    gathered = torch.empty(cfg.vocab, dtype=torch.bfloat16, device="cuda")
     for t in range(len(seq) - 1):
         ref.cur.fill_(seq[t]); tp.cur.fill_(seq[t]); ref.forward_token(); tp.forward_token()
-        a, b = ref.logits.float(), tp.logits_all.float()
+        dist.all_gather_into_tensor(gathered, tp.logits)
+        a, b = ref.logits.float(), gathered.float()
         assert (a - b).abs().max().item() <= 0.05 * a.abs().max().item() + 0.05, (how, t)
         if int(ref.cur) == int(tp.cur): agree += 1
         else:
@@ -49,16 +55,18 @@ for how, pdl in (("peer", True), ("peer", False), ("nccl", False)):        # thi
     from nwc_b200 import _lib as L
     assert L.lib.nwc_kernel_status(1) == 0, how           # no rank gave up waiting for a peer
     torch.cuda.synchronize(); dist.barrier(); tp.close()
-assert sequences[("peer", True)] == sequences[("peer", False)]
+first = modes[0][0]
+assert sequences[(first, True)] == sequences[(first, False)]
 dist.destroy_process_group()
 print("TP OK", rank, agree, close)
 """
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tp2_follows_single_gpu_engine(tmp_path):
+@pytest.mark.parametrize("layout", [2, 0])
+def test_tp2_follows_single_gpu_engine(tmp_path, layout):
     script = tmp_path / "tp_worker.py"; script.write_text(WORKER)
-    env = dict(os.environ, NWC_ROOT=ROOT, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29573")
+    env = dict(os.environ, NWC_ROOT=ROOT, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29573", NWC_TP_LAYOUT=str(layout))
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
                           "--master-port", "29573", str(script)], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
