@@ -51,6 +51,7 @@ def parse():
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
+    ap.add_argument("--fixup", type=int, default=1, help="0: work splits of whole row groups instead of equal runs with in-kernel fix-up (A/B)")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     a = ap.parse_args()
     if a.layout is None: a.layout = 0 if a.model == "qwen3-0.6b" else 2
@@ -187,6 +188,7 @@ def kernel_only(a, cfg):
     shapes = cfg.matrix_shapes()
     M, K = shapes[a.kernel] if a.kernel in shapes else tuple(int(v) for v in a.kernel.lower().split("x"))
     torch.cuda.set_device(0)
+    L.lib.nwc_set_fixup_plans(int(a.fixup))
     L.lib.nwc_set_dependent_launch(int(a.dependent_launch))
     first = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
     copies = max(1, min(64, -(-(320 << 20) // first.bytes)))          # rotate over > 320 MB so that no launch finds its matrix in L2

@@ -110,6 +110,10 @@ int nwc_allreduce_add_rmsnorm(void *stream, void *const *buffers, int rank, int 
    tests); on = 1 (default) restores the rings. */
 void nwc_set_ring_kernels(int on);
 
+/* on = 0 keeps nwc_linear_fused on work splits of whole row groups (or a finalize launch) instead of equal runs per CTA
+   whose cut row groups are completed inside the kernel (A/B tests); on = 1 (default) restores them. */
+void nwc_set_fixup_plans(int on);
+
 /* nwc_linear_bf16 with a bf16 activation vector for every layout (layout 0: bf16[K16]; layouts 1, 2: bf16[K rounded up
    to 32]): the decode loop keeps activations in bf16, which spares layout 0 the fp32 copy and the second mma pass. */
 int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,

@@ -1,209 +1,175 @@
-"""Compressed checkpoints: the reference's on-disk format, read and written (reference: nwc/checkpoint.py).
+"""save_pretrained / load_pretrained / export_bf16 for converted Hugging Face models.
 
-A checkpoint is a directory:
-  config.json, generation_config.json, tokenizer files    Hugging Face files, untouched
-  nwc_config.json    {nwc_checkpoint: 1, library_version: 9|10|11, base_model, weights: [{id, out, in, block, bytes,
-                     elem?, layout?}], modules: [{path, kind: linear|embedding|fused, weight, bias | padding_idx |
-                     names, sizes}], bytes_nwc, bytes_bf16}; missing elem / layout mean bf16 / 0
-  model.safetensors  the remaining parameters plus, per matrix, "nwc/<id>/{data,bases,hdr,lut,low[,scale]}"
-Versions 9, 10 and 11 (layouts 0, 1, 2) all load.  The model skeleton is built on the meta device with plain torch,
-so no weights other than the compressed ones ever exist in host or device memory.
+The on-disk schema is the reference's (nwc/checkpoint.py; restated in nwc_b200/store.py), so checkpoints written by
+either implementation load in the other.  The code around it is this library's:
+
+  * saving walks the model once and turns every NWC module into a schema record (`_describe_model`);
+  * loading builds the model skeleton on the meta device with plain torch, then installs one module per record, each
+    matrix streamed from the tensor file directly onto the GPU (`store.CheckpointReader`): neither bf16 originals nor a
+    host copy of the whole checkpoint ever exist;
+  * exporting decodes matrix by matrix back to the plain bf16 tensor names of the original model.
+The decode loop reads the same checkpoints without Transformers: `nwc_b200.decode.DecodeEngine.from_pretrained`.
 """
-import json
 import os
 import shutil
 
 import torch
 import torch.nn as nn
-from safetensors.torch import load_file, save_file
 
 from ._lib import VERSION
-from .modules import NWCEmbedding, NWCLinear, _FusedHead
-from .weight import NWCWeight
-
-FORMAT = 1
-COMPATIBLE = {9, 10, 11}
-TENSOR_NAMES = ("data", "bases", "hdr", "lut", "low")
+from .modules import FusedProjection, NWCEmbedding, NWCLinear, fused_groups, install_fused
+from .store import CheckpointReader, resolve, write_checkpoint  # noqa: F401  (resolve is part of this module's interface)
+from .weight import ELEM_NAMES, NWCWeight
 
 
-def _parent(path): return path.rsplit(".", 1)[0] if "." in path else ""
+def _describe_model(model):
+    """(matrix records, module records, extra tensors) of a converted model.  A matrix shared by several modules (tied
+    embedding + lm_head) is stored once; fused groups contribute one record for all their heads."""
+    matrices, modules, extra, ids = [], [], {}, {}
 
+    def matrix_id(w: NWCWeight):
+        if id(w) not in ids:
+            ids[id(w)] = len(matrices)
+            matrices.append({"id": len(matrices), "out": w.out_features, "in": w.in_features, "block": w.block, "bytes": w.bytes,
+                             "elem": ELEM_NAMES[w.elem], "layout": w.layout, "tensors": w.tensors()})
+        return ids[id(w)]
 
-def _collect(model):
-    """Unique NWCWeight objects and the modules that use them."""
-    index, weights, modules, groups = {}, [], [], set()
-
-    def key(w):
-        if id(w) not in index:
-            index[id(w)] = len(weights)
-            weights.append({"id": len(weights), "out": w.out_features, "in": w.in_features, "block": w.block, "bytes": w.bytes,
-                            "elem": "fp8" if w.elem else "bf16", "layout": w.layout, "w": w})
-        return index[id(w)]
-
-    for path, m in model.named_modules():
-        if isinstance(m, NWCLinear):
-            modules.append({"path": path, "kind": "linear", "weight": key(m.w), "bias": f"{path}.bias" if m.bias is not None else None})
-        elif isinstance(m, NWCEmbedding):
-            modules.append({"path": path, "kind": "embedding", "weight": key(m.w), "padding_idx": m.padding_idx})
-        elif isinstance(m, _FusedHead) and id(m.g) not in groups:
-            groups.add(id(m.g))
-            lin, parent = m.g["lin"], _parent(path)
-            modules.append({"path": parent, "kind": "fused", "weight": key(lin.w), "names": m.g["names"], "sizes": m.g["sizes"],
-                            "bias": f"nwc/fused/{parent}.bias" if lin.bias is not None else None})
-    return weights, modules
+    fused_lins = {id(g.lin) for _, g in fused_groups(model)}
+    for path, mod in model.named_modules():
+        if isinstance(mod, NWCLinear) and id(mod) not in fused_lins:
+            modules.append({"path": path, "kind": "linear", "weight": matrix_id(mod.w), "bias": f"{path}.bias" if mod.bias is not None else None})
+        elif isinstance(mod, NWCEmbedding):
+            modules.append({"path": path, "kind": "embedding", "weight": matrix_id(mod.w), "padding_idx": mod.padding_idx})
+    for parent, g in fused_groups(model):                           # their bias is not a registered parameter of the model
+        key = f"nwc/fused/{parent}.bias" if g.lin.bias is not None else None
+        if key: extra[key] = g.lin.bias.data
+        modules.append({"path": parent, "kind": "fused", "weight": matrix_id(g.lin.w), "names": g.names, "sizes": g.sizes, "bias": key})
+    return matrices, modules, extra
 
 
 def save_pretrained(model: nn.Module, path: str, tokenizer=None, base_model: str = None):
     """Write a converted model as an NWC checkpoint.  Returns the nwc_config dict."""
-    os.makedirs(path, exist_ok=True)
-    weights, modules = _collect(model)
-    tensors = {k: v.detach().cpu().contiguous() for k, v in model.state_dict().items()}
-    for e in weights:
-        for name, t in e["w"].tensors().items(): tensors[f"nwc/{e['id']}/{name}"] = t.detach().cpu().contiguous()
-    for m in modules:                   # biases of fused groups are not registered parameters of the model
-        if m["kind"] != "fused" or not m["bias"]: continue
-        for p, mod in model.named_modules():
-            if isinstance(mod, _FusedHead) and _parent(p) == m["path"]:
-                tensors[m["bias"]] = mod.g["lin"].bias.detach().cpu().contiguous(); break
-    save_file(tensors, os.path.join(path, "model.safetensors"), metadata={"format": "pt", "nwc": str(FORMAT)})
-    config = {"nwc_checkpoint": FORMAT, "library_version": VERSION,
-              "base_model": base_model, "weights": [{k: v for k, v in e.items() if k != "w"} for e in weights], "modules": modules,
-              "bytes_nwc": sum(e["bytes"] for e in weights), "bytes_bf16": sum(2 * e["out"] * e["in"] for e in weights)}
-    with open(os.path.join(path, "nwc_config.json"), "w", encoding="utf-8") as f: json.dump(config, f, indent=1)
+    matrices, modules, extra = _describe_model(model)
+    plain = dict(model.state_dict()); plain.update(extra)
+    config = write_checkpoint(path, plain, matrices, modules, VERSION, base_model)
     model.config.save_pretrained(path)
-    gc = getattr(model, "generation_config", None)
-    if gc is not None: gc.save_pretrained(path)
-    if tokenizer is not None: tokenizer.save_pretrained(path)
+    for part in (getattr(model, "generation_config", None), tokenizer):
+        if part is not None: part.save_pretrained(path)
     return config
 
 
-def _set(model, path, module):
+def _attach(model, path, module):
     parent, _, name = path.rpartition(".")
     setattr(model.get_submodule(parent) if parent else model, name, module)
 
 
-def resolve(path: str) -> str:
-    """A local directory as is; anything else is treated as a Hugging Face repo id and fetched into the HF cache."""
-    if os.path.isdir(path): return path
-    if os.path.exists(path): raise FileNotFoundError(f"{path} is a file, an NWC checkpoint is a directory")
-    try:
-        from huggingface_hub import snapshot_download
-    except ImportError:
-        raise FileNotFoundError(f"{path} is not a directory, and huggingface_hub is not installed")
-    return snapshot_download(path)
+def _skeleton(hf_config):
+    """The model without any storage (meta device), built with plain torch."""
+    from transformers import AutoModelForCausalLM
+    with torch.device("meta"):
+        try: return AutoModelForCausalLM.from_config(hf_config, dtype=torch.bfloat16)
+        except TypeError: return AutoModelForCausalLM.from_config(hf_config, torch_dtype=torch.bfloat16)
 
 
-def _read_config(path):
-    cfg_path = os.path.join(path, "nwc_config.json")
-    if not os.path.exists(cfg_path):
-        raise FileNotFoundError(f"{path} is not an NWC checkpoint (no nwc_config.json)")
-    with open(cfg_path, encoding="utf-8") as f: config = json.load(f)
-    if config.get("library_version") not in COMPATIBLE:
-        raise RuntimeError(f"checkpoint is format version {config.get('library_version')}, this library reads {sorted(COMPATIBLE)}")
-    return config
-
-
-def _weight_from(tensors, e, device):
-    t = {n: tensors.pop(f"nwc/{e['id']}/{n}") for n in TENSOR_NAMES}
-    return NWCWeight.from_tensors(e["out"], e["in"], e["block"], t["data"], t["bases"], t["hdr"], t["lut"], t["low"], device,
-                                  elem=e.get("elem", "bf16"), scale=tensors.pop(f"nwc/{e['id']}/scale", None), layout=e.get("layout", 0))
-
-
-def _materialize(model, name, value, device):
-    """Replace the meta parameter / buffer `name` by `value` on `device`."""
-    parent, _, leaf = name.rpartition(".")
-    mod = model.get_submodule(parent) if parent else model
-    value = value.to(device)
-    if leaf in mod._parameters: mod._parameters[leaf] = nn.Parameter(value, requires_grad=False)
-    elif leaf in mod._buffers: mod._buffers[leaf] = value
+def _fill(model, name, value):
+    """Give the meta parameter / buffer `name` its stored value."""
+    owner_path, _, leaf = name.rpartition(".")
+    owner = model.get_submodule(owner_path) if owner_path else model
+    if leaf in owner._parameters: owner._parameters[leaf] = nn.Parameter(value, requires_grad=False)
+    elif leaf in owner._buffers: owner._buffers[leaf] = value
     else: raise KeyError(f"{name} is not a parameter or buffer of the model")
 
 
-def _rebuild_meta_buffers(model, hf_config, device):
+def _recompute_buffers(model, hf_config, device):
     """Buffers that checkpoints do not store (rotary inv_freq and the like) are still on the meta device after loading:
     re-create the modules that own them from the config and take their freshly computed buffers."""
     for path, mod in list(model.named_modules()):
-        names = [n for n, b in mod.named_buffers(recurse=False) if b.device.type == "meta"]
-        if not names: continue
+        missing = [n for n, b in mod.named_buffers(recurse=False) if b.device.type == "meta"]
+        if not missing: continue
         fresh = None
-        for build in (lambda: type(mod)(config=hf_config, device="cpu"), lambda: type(mod)(config=hf_config), lambda: type(mod)(hf_config)):
-            try:
-                fresh = build(); break
-            except TypeError:
-                continue
-        if fresh is None: raise RuntimeError(f"buffer {path}.{names[0]} is not in the checkpoint and its module cannot be rebuilt from the config")
-        for n in names: mod._buffers[n] = dict(fresh.named_buffers(recurse=False))[n].detach().clone().to(device)
-        for k, v in vars(fresh).items():             # plain attributes computed next to the buffers (e.g. original_inv_freq)
-            if isinstance(v, torch.Tensor) and isinstance(getattr(mod, k, None), torch.Tensor) and getattr(mod, k).device.type == "meta": setattr(mod, k, v.to(device))
+        for make in (lambda: type(mod)(config=hf_config, device="cpu"), lambda: type(mod)(config=hf_config), lambda: type(mod)(hf_config)):
+            try: fresh = make(); break
+            except TypeError: continue
+        if fresh is None: raise RuntimeError(f"buffer {path}.{missing[0]} is not in the checkpoint and its module cannot be rebuilt from the config")
+        computed = dict(fresh.named_buffers(recurse=False))
+        for n in missing: mod._buffers[n] = computed[n].detach().clone().to(device)
+        for attr, value in vars(fresh).items():                    # plain tensor attributes computed next to the buffers (e.g. original_inv_freq)
+            mine = getattr(mod, attr, None)
+            if isinstance(value, torch.Tensor) and isinstance(mine, torch.Tensor) and mine.device.type == "meta": setattr(mod, attr, value.to(device))
 
 
 def load_pretrained(path: str, device="cuda", verbose=True):
     """Load an NWC checkpoint: the model on `device` with NWC modules in place; no bf16 originals are ever created."""
-    from transformers import AutoConfig, AutoModelForCausalLM
-    path = resolve(path)
-    config = _read_config(path)
-    hf_config = AutoConfig.from_pretrained(path)
-    with torch.device("meta"):
-        try: model = AutoModelForCausalLM.from_config(hf_config, dtype=torch.bfloat16)
-        except TypeError: model = AutoModelForCausalLM.from_config(hf_config, torch_dtype=torch.bfloat16)
-    tensors = load_file(os.path.join(path, "model.safetensors"))
-    weights = {e["id"]: _weight_from(tensors, e, device) for e in config["weights"]}
-    for m in config["modules"]:
-        w = weights[m["weight"]]
-        if m["kind"] == "linear":
-            _set(model, m["path"], NWCLinear(w=w, bias=tensors.pop(m["bias"], None) if m["bias"] else None, device=device))
-        elif m["kind"] == "embedding":
-            _set(model, m["path"], NWCEmbedding(w=w, padding_idx=m["padding_idx"]))
-        else:
-            lin = NWCLinear(w=w, bias=tensors.pop(m["bias"], None) if m["bias"] else None, device=device)
-            shared = {"lin": lin, "y": None, "x_id": None, "names": m["names"], "sizes": m["sizes"]}
-            start = 0
-            for i, (name, size) in enumerate(zip(m["names"], m["sizes"])):
-                _set(model, f"{m['path']}.{name}" if m["path"] else name, _FusedHead(shared, i, start, start + size)); start += size
-    for k, v in tensors.items(): _materialize(model, k, v, device)
-    _rebuild_meta_buffers(model, hf_config, device)
+    from transformers import AutoConfig
+    reader = CheckpointReader(path)
+    hf_config = AutoConfig.from_pretrained(reader.path)
+    model = _skeleton(hf_config)
+    cache = {}
+
+    def matrix(wid):                                                # a matrix shared by two modules is loaded once
+        if wid not in cache: cache[wid] = NWCWeight.from_compressed(reader.matrix(wid, device), device, reader.records[wid]["block"])
+        return cache[wid]
+
+    taken = set()
+    def bias_of(record):
+        if not record.get("bias"): return None
+        taken.add(record["bias"])
+        return reader.tensor(record["bias"], device)
+
+    for rec in reader.modules:
+        if rec["kind"] == "embedding": _attach(model, rec["path"], NWCEmbedding(w=matrix(rec["weight"]), padding_idx=rec["padding_idx"]))
+        elif rec["kind"] == "linear": _attach(model, rec["path"], NWCLinear(w=matrix(rec["weight"]), bias=bias_of(rec), device=device))
+        elif rec["kind"] == "fused":
+            lin = NWCLinear(w=matrix(rec["weight"]), bias=bias_of(rec), device=device)
+            install_fused(model.get_submodule(rec["path"]) if rec["path"] else model, FusedProjection(lin, rec["names"], rec["sizes"]))
+        else: raise RuntimeError(f"unknown module kind '{rec['kind']}' in the checkpoint")
+    for name in reader.plain_names():
+        if name not in taken: _fill(model, name, reader.tensor(name, device))
+    _recompute_buffers(model, hf_config, device)
     for n, p in model.named_parameters():
         if p.device.type == "meta": raise RuntimeError(f"parameter {n} missing in the checkpoint")
     model.to(device).eval()
     if verbose:
-        print(f"NWC: checkpoint loaded, {config['bytes_bf16'] / 1e9:.2f} GB BF16 -> {config['bytes_nwc'] / 1e9:.2f} GB "
-              f"(ratio {config['bytes_nwc'] / max(config['bytes_bf16'], 1):.4f})")
+        c = reader.config
+        print(f"NWC: checkpoint loaded, {c['bytes_bf16'] / 1e9:.2f} GB BF16 -> {c['bytes_nwc'] / 1e9:.2f} GB (ratio {c['bytes_nwc'] / max(c['bytes_bf16'], 1):.4f})")
     return model
 
 
 def export_bf16(path: str, out: str, device="cuda", verbose=True):
     """NWC checkpoint -> plain bf16 Transformers checkpoint at `out` (bit-identical weights).  Returns the bf16 bytes."""
-    path = resolve(path)
-    config = _read_config(path)
-    with open(os.path.join(path, "config.json"), encoding="utf-8") as f: tied = json.load(f).get("tie_word_embeddings", False)
-    tensors = load_file(os.path.join(path, "model.safetensors"))
-    embedding_ids = {m["weight"] for m in config["modules"] if m["kind"] == "embedding"}
-    result, total = {}, 0
-    for e in config["weights"]:
-        w = _weight_from(tensors, e, device)
-        full = w.dequant()
-        if w.scale is not None: full = (full.float() * w.scale[:, None]).to(torch.bfloat16)
-        full = full.contiguous().cpu(); del w
-        total += full.numel() * 2
-        for m in config["modules"]:
-            if m["weight"] != e["id"]: continue
-            if m["kind"] == "embedding": result[f"{m['path']}.weight"] = full
-            elif m["kind"] == "linear":
-                if not (tied and e["id"] in embedding_ids): result[f"{m['path']}.weight"] = full
-                if m["bias"]: result[f"{m['path']}.bias"] = tensors.pop(m["bias"])
+    from safetensors.torch import save_file
+    reader = CheckpointReader(path)
+    tied = bool(reader.hf_config().get("tie_word_embeddings", False))
+    users = {}
+    for rec in reader.modules: users.setdefault(rec["weight"], []).append(rec)
+    result, total, consumed = {}, 0, set()
+
+    def take(name):
+        consumed.add(name)
+        return reader.tensor(name, "cpu")
+
+    for wid, records in users.items():
+        full = NWCWeight.from_compressed(reader.matrix(wid, device), device).dense().contiguous().cpu()
+        total += 2 * full.numel()
+        is_table = any(r["kind"] == "embedding" for r in records)
+        for rec in records:
+            if rec["kind"] == "embedding": result[f"{rec['path']}.weight"] = full
+            elif rec["kind"] == "linear":
+                if not (tied and is_table): result[f"{rec['path']}.weight"] = full          # a tied lm_head has no tensor of its own
+                if rec.get("bias"): result[f"{rec['path']}.bias"] = take(rec["bias"])
             else:
-                bias = tensors.pop(m["bias"]) if m["bias"] else None
-                start = 0
-                for name, size in zip(m["names"], m["sizes"]):
-                    key = f"{m['path']}.{name}" if m["path"] else name
-                    result[f"{key}.weight"] = full[start:start + size].clone()
-                    if bias is not None: result[f"{key}.bias"] = bias[start:start + size].clone()
-                    start += size
-    result.update(tensors)
+                bias, at = (take(rec["bias"]) if rec.get("bias") else None), 0
+                for name, size in zip(rec["names"], rec["sizes"]):
+                    prefix = f"{rec['path']}.{name}" if rec["path"] else name
+                    result[f"{prefix}.weight"] = full[at:at + size].clone()
+                    if bias is not None: result[f"{prefix}.bias"] = bias[at:at + size].clone()
+                    at += size
+    for name in reader.plain_names():
+        if name not in consumed: result[name] = reader.tensor(name, "cpu")
     os.makedirs(out, exist_ok=True)
     save_file(result, os.path.join(out, "model.safetensors"), metadata={"format": "pt"})
-    for name in os.listdir(path):
-        if name not in ("model.safetensors", "nwc_config.json") and os.path.isfile(os.path.join(path, name)):
-            shutil.copyfile(os.path.join(path, name), os.path.join(out, name))
+    for name in os.listdir(reader.path):
+        src = os.path.join(reader.path, name)
+        if name not in ("model.safetensors", "nwc_config.json") and os.path.isfile(src): shutil.copyfile(src, os.path.join(out, name))
     if verbose: print(f"NWC: exported {total / 1e9:.2f} GB of BF16 weights to {out}")
     return total

@@ -517,7 +517,7 @@ __device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, u
     const bool live = row < a.M;
     if (live && a.scale) v *= __ldg(a.scale + row);
     if (live && a.bias) v += bf16_to_float(__ldg(a.bias + row));
-    const uint32_t h = live ? (uint32_t)bf16_round(v) : 0u;
+    const uint32_t h = live ? (uint32_t)bf16_round_nan(v) : 0u;        /* (the reference's rounding for every finite value; NaN stays NaN) */
     if (a.push.world == 0u) { if (live) a.y[row] = (uint16_t)h; return; }
     const uint32_t pair = h | (__shfl_down_sync(mask, h, 1) << 16);
     if ((sub & 1u) == 0u && live) {
@@ -831,10 +831,11 @@ static ClusterRoom cluster_room(int sms);
 /* With allow_fix the equal runs need no second launch: cut row groups are completed inside the kernel (FlatPlan::fix), which
    is worth about kFixSlots slots (a CTA barrier, one atomic and a few dependent loads at the kernel's end). */
 constexpr uint64_t kFixSlots = 64;
+static bool g_disable_ring = false, g_disable_fixup = false;     /* A/B switches of the tests (set_ring_kernels, set_fixup_plans) */
 static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p, uint32_t &cluster, bool allow_fix = false) {
     const uint64_t total = (uint64_t)g.groups * g.slots;
     const ClusterRoom room = cluster_room(sms);
-    if (sms > (int)kFixCounters) allow_fix = false;
+    if (sms > (int)kFixCounters || g_disable_fixup) allow_fix = false;
     uint64_t best = (total + (uint64_t)sms - 1u) / (uint64_t)sms + (allow_fix ? kFixSlots : kFinalizeSlots);
     uint32_t best_cluster = 0;                                   /* 0 = equal runs + finalize */
     for (uint32_t lg = 0; lg < 4u; lg++) {
@@ -1319,8 +1320,8 @@ cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const Segme
     return launch_kernel(small_kernel_layout0<kBf16>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
 }
 
-static bool g_disable_ring = false;
 void set_ring_kernels(bool on) { g_disable_ring = !on; }
+void set_fixup_plans(bool on) { g_disable_fixup = !on; }
 int read_kernel_status(bool clear) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_kernel_status, sizeof(int)) != cudaSuccess) return -1;

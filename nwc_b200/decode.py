@@ -65,6 +65,96 @@ class DecoderWeights:
             return synthetic_matrix(r, c, seed * 100003 + names[name], device)
         return cls(cfg, source, lambda name, n: torch.ones(n, dtype=torch.bfloat16, device=device), layout, elem, device, tp_rank, tp_world)
 
+    @classmethod
+    def from_checkpoint(cls, path, device="cuda", tp_rank=0, tp_world=1):
+        """The compressed matrices of an NWC checkpoint (formats v9 / v10 / v11, as written by save_pretrained of this
+        library or of the reference) mapped onto the decode loop, without ever creating bf16 weights: the `fused` records
+        of q/k/v and gate/up, the `linear` records of o, down and lm_head and the `embedding` record are taken as stored.
+        With tp_world > 1 every matrix is cut into this rank's shard by re-packing its blocks (nwc_b200/repack.py).  Only
+        checkpoints whose projections were not fused, or whose head sizes do not fall on block boundaries, are
+        dequantised and re-encoded instead.  Architectures: Qwen3 and Llama style decoders without biases."""
+        from . import repack as R
+        from .store import CheckpointReader
+        rd = CheckpointReader(path)
+        hf = rd.hf_config()
+        kind = hf.get("model_type", "")
+        if kind not in ("qwen3", "llama"): raise ValueError(f"the decode loop knows qwen3 and llama decoders, not '{kind}'")
+        heads = hf["num_attention_heads"]
+        cfg = DecoderConfig(hf.get("_name_or_path") or kind, hf["num_hidden_layers"], hf["hidden_size"], hf["intermediate_size"], heads,
+                            hf.get("num_key_value_heads", heads), hf.get("head_dim") or hf["hidden_size"] // heads, hf["vocab_size"],
+                            bool(hf.get("tie_word_embeddings", False)), kind == "qwen3",
+                            rope_theta=float((hf.get("rope_parameters") or {}).get("rope_theta", hf.get("rope_theta", 1e4))), eps=float(hf.get("rms_norm_eps", 1e-6)))
+        self = cls.__new__(cls)
+        self.full_cfg, self.tp_rank, self.tp_world = cfg, tp_rank, tp_world
+        self.cfg = TP.local_config(cfg, tp_world) if tp_world > 1 else cfg
+        by_path = {m["path"]: m for m in rd.modules}
+        for m in rd.modules:
+            if m.get("bias"): raise ValueError(f"{m['path']} has a bias; the decode loop runs bias-free decoders")
+        cache = {}
+
+        def stored(wid):
+            if wid not in cache: cache.clear(); cache[wid] = rd.matrix(wid, device)      # one matrix in flight at a time
+            return cache[wid]
+
+        def weight_of(c):
+            return NWCWeight.from_tensors(c.M, c.K, L.FIXED_BLOCK, c.data, c.bases, c.hdr, c.lut, c.low, device, elem=c.elem, scale=c.scale, layout=c.layout)
+
+        def reencoded(full_bf16, shard_kind, like):
+            part = TP.shard(shard_kind, full_bf16, cfg, tp_rank, tp_world) if tp_world > 1 and shard_kind else full_bf16
+            return NWCWeight(part.contiguous(), device, elem="bf16" if like.elem == "bf16" else "fp8", layout=like.layout)
+
+        def dense(c):
+            w = weight_of(c); full = w.dequant()
+            return full if w.scale is None else (full.float() * w.scale[:, None]).to(torch.bfloat16)
+
+        def projection(parent, names, shard_kind):
+            """A fused group stored under `parent`, or separate linears parent.<name> (then concatenated and re-encoded)."""
+            rec = by_path.get(parent)
+            if rec is not None and rec["kind"] == "fused" and list(rec["names"]) == list(names):
+                c = stored(rec["weight"])
+                if tp_world == 1: return weight_of(c)
+                sizes, starts, ranges = rec["sizes"], [0], []
+                for n in sizes: starts.append(starts[-1] + n)
+                per = [n // tp_world for n in sizes]
+                if all(n % tp_world == 0 for n in sizes) and R.rows_divisible(c.layout, *per):
+                    for s0, n in zip(starts, per): ranges.append((s0 + tp_rank * n, s0 + (tp_rank + 1) * n))
+                    return weight_of(R.take_rows(c, ranges))
+                return reencoded(dense(c), shard_kind, c)
+            parts = [stored(by_path[f"{parent}.{n}"]["weight"]) for n in names]
+            like = parts[0]
+            return reencoded(torch.cat([dense(p) for p in parts], 0), shard_kind, like)
+
+        def row_parallel(path_, shard_kind):
+            c = stored(by_path[path_]["weight"])
+            if tp_world == 1: return weight_of(c)
+            n = c.K // tp_world
+            if c.K % tp_world == 0 and n % R.BLOCK_COLS == 0: return weight_of(R.take_cols(c, tp_rank * n, (tp_rank + 1) * n))
+            return reencoded(dense(c), shard_kind, c)
+
+        emb_rec = next(m for m in rd.modules if m["kind"] == "embedding")
+        self.embed = weight_of(stored(emb_rec["weight"]))
+        head_rec = by_path.get("lm_head")
+        if head_rec is None: raise ValueError("checkpoint has no compressed lm_head")
+        if tp_world == 1:
+            self.lm_head = self.embed if head_rec["weight"] == emb_rec["weight"] else weight_of(stored(head_rec["weight"]))
+        else:
+            c = stored(head_rec["weight"]); V = cfg.vocab // tp_world
+            self.lm_head = weight_of(R.take_rows(c, [(tp_rank * V, (tp_rank + 1) * V)])) if R.rows_divisible(c.layout, V) else reencoded(dense(c), "lm_head", c)
+        vec = lambda name: rd.tensor(name, device).to(torch.bfloat16).contiguous()
+        self.layers = []
+        for i in range(cfg.layers):
+            pre = f"model.layers.{i}"
+            self.layers.append({
+                "in_norm": vec(f"{pre}.input_layernorm.weight"), "post_norm": vec(f"{pre}.post_attention_layernorm.weight"),
+                "q_norm": vec(f"{pre}.self_attn.q_norm.weight") if cfg.qk_norm else None,
+                "k_norm": vec(f"{pre}.self_attn.k_norm.weight") if cfg.qk_norm else None,
+                "qkv": projection(f"{pre}.self_attn", ("q_proj", "k_proj", "v_proj"), "qkv"), "o": row_parallel(f"{pre}.self_attn.o_proj", "o"),
+                "gate_up": projection(f"{pre}.mlp", ("gate_proj", "up_proj"), "gate_up"), "down": row_parallel(f"{pre}.mlp.down_proj", "down")})
+        self.final_norm = vec("model.norm.weight")
+        cache.clear()
+        assert self.cfg.qkv_rows == self.layers[0]["qkv"].out_features
+        return self
+
     def matrices(self):
         seen, out = set(), []
         for w in [self.embed, self.lm_head] + [l[k] for l in self.layers for k in ("qkv", "o", "gate_up", "down")]:
@@ -130,6 +220,16 @@ class DecodeEngine:
         self.launches_per_step = 0
         self._count = 0
         if weights.embed.scale is not None: raise NotImplementedError("fp8 embedding tables are not supported by the decode loop")
+
+    @classmethod
+    def from_pretrained(cls, path, max_len=1024, device="cuda", tp_group=None, **kw):
+        """Decode engine on an NWC checkpoint directory (see DecoderWeights.from_checkpoint); with a process group the
+        matrices are cut into this rank's tensor-parallel shards while loading."""
+        rank, world = 0, 1
+        if tp_group is not None:
+            import torch.distributed as dist
+            rank, world = dist.get_rank(tp_group), dist.get_world_size(tp_group)
+        return cls(DecoderWeights.from_checkpoint(path, device, rank, world), max_len=max_len, device=device, tp_group=tp_group, **kw)
 
     # ---- one token, eager: every call below is one or two kernels of this library on the current stream ----
     def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None, tp_in=-1, tp_out=-1):

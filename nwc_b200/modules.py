@@ -1,10 +1,19 @@
-"""nn.Module drop-ins on compressed matrices and the model-wide conversion helpers.
+"""nn.Module drop-ins on compressed matrices, and the model-wide conversion.
 
-Same public names and behaviour as the reference's integration layer (reference: nwc/nwc_torch.py:272-445):
-NWCLinear / NWCEmbedding replace nn.Linear / nn.Embedding, `fuse` concatenates sibling projections into one matrix,
-`convert` walks a model and swaps every supported layer.  One token (x.numel() == in_features, bf16) takes the fused
-decode-matvec; anything else dequantises and calls a dense matmul.
+Public names and call signatures follow the reference's integration layer (reference: nwc/nwc_torch.py:272-445):
+NWCLinear / NWCEmbedding stand in for nn.Linear / nn.Embedding, `fuse` merges sibling projections that read the same
+input into one compressed matrix, `convert` swaps every supported layer of a model.  How they work here:
+
+  * one token (x.numel() == in_features, bf16) runs the fused decode-matvec; more tokens run `NWCLinear.prefill_backend`:
+    "dense" (default: dequantise into a temporary, then the vendor matmul - what the reference does, and the faster of
+    the two on B200 today) or "tcgen05" (this library's tile-wise decode into a tensor-memory GEMM, layout 2 bf16);
+  * a fused projection is ONE module-level object (`FusedProjection`) that owns the matrix and remembers its latest
+    result together with the identity of the input storage it was computed from; its heads are views into that result;
+  * `convert` first makes a plan (which layer becomes what, which table is shared with the lm_head) from one scan of the
+    model and then carries it out, so nothing depends on module iteration order.
 """
+import os
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -12,31 +21,53 @@ import torch.nn.functional as F
 from .weight import NWCWeight, fits, quantize_fp8, ref_fp8_matvec
 
 
+def _bias_param(bias, device):
+    return None if bias is None else nn.Parameter(bias.detach().to(device=device, dtype=torch.bfloat16), requires_grad=False)
+
+
+def _drop_storage(param):
+    """Free a replaced layer's original weights (the module object may still be referenced elsewhere)."""
+    param.data = torch.empty(0)
+
+
 class NWCLinear(nn.Module):
     """nn.Linear on a compressed matrix (elem "bf16" lossless, or "fp8" weight-only)."""
 
+    prefill_backend = os.environ.get("NWC_PREFILL", "dense")      # "dense" | "tcgen05"
+
     def __init__(self, linear: nn.Linear = None, device="cuda", block=None, w: NWCWeight = None, bias=None, elem="bf16", layout=None):
         super().__init__()
-        self.w = w if w is not None else NWCWeight(linear.weight.data, device, block, elem=elem, layout=layout)
-        self.in_features, self.out_features = self.w.in_features, self.w.out_features
+        if w is None:
+            if linear is None: raise ValueError("NWCLinear needs an nn.Linear or a compressed matrix")
+            w = NWCWeight(linear.weight.data, device, block, elem=elem, layout=layout)
         if linear is not None and linear.bias is not None: bias = linear.bias.data
-        self.bias = None if bias is None else nn.Parameter(bias.to(device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.w, self.bias = w, _bias_param(bias, device)
+        self.in_features, self.out_features = w.in_features, w.out_features
 
-    def forward(self, x):
-        if x.numel() == self.in_features and x.dtype == torch.bfloat16:            # one token: fused kernel
-            y = self.w.linear_bf16(x.contiguous().view(-1), None if self.bias is None else self.bias.data)
-            return y.view(*x.shape[:-1], self.out_features)
-        if x.dtype == torch.bfloat16:                                                # prefill: decode tile-wise into the tensor-core GEMM where covered
-            y = self.w.linear_prefill(x.reshape(-1, self.in_features), None if self.bias is None else self.bias.data)
+    def _bias_data(self):
+        return None if self.bias is None else self.bias.data
+
+    def _many_tokens(self, x):
+        """x [..., in] with more than one token."""
+        if self.prefill_backend == "tcgen05" and x.dtype == torch.bfloat16:
+            y = self.w.linear_prefill(x.reshape(-1, self.in_features), self._bias_data())
             if y is not None: return y.view(*x.shape[:-1], self.out_features)
-        if self.w.scale is None: return F.linear(x, self.w.dequant(), self.bias)    # otherwise: temporary dequantisation
-        y = F.linear(x, self.w.dequant()).float() * self.w.scale                     # fp8: unscaled matmul, then the row scale
+        dense = self.w.dequant()                                   # temporary bf16 copy, freed after the matmul
+        if self.w.scale is None: return F.linear(x, dense, self.bias)
+        y = F.linear(x, dense).float() * self.w.scale              # fp8: matmul over the unscaled codes, then the row scale
         if self.bias is not None: y = y + self.bias.float()
         return y.to(x.dtype)
 
+    def forward(self, x):
+        if x.dtype == torch.bfloat16 and x.numel() == self.in_features:
+            y = self.w.linear_bf16(x.reshape(-1), self._bias_data())
+            return y.view(*x.shape[:-1], self.out_features)
+        return self._many_tokens(x)
+
     def extra_repr(self):
-        return (f"in={self.in_features}, out={self.out_features}, elem={'fp8' if self.w.elem else 'bf16'}, layout={self.w.layout}, "
-                f"{self.w.bytes / 1e6:.1f} MB (BF16: {self.w.bytes_bf16 / 1e6:.1f} MB)")
+        w = self.w
+        return (f"in={self.in_features}, out={self.out_features}, elem={'fp8' if w.elem else 'bf16'}, layout={w.layout}, "
+                f"{w.bytes / 1e6:.1f} MB (BF16: {w.bytes_bf16 / 1e6:.1f} MB)")
 
 
 class NWCEmbedding(nn.Module):
@@ -44,128 +75,162 @@ class NWCEmbedding(nn.Module):
 
     def __init__(self, emb: nn.Embedding = None, w: NWCWeight = None, padding_idx=None):
         super().__init__()
+        if w is None: raise ValueError("NWCEmbedding needs the compressed table")
         self.w = w
         self.num_embeddings, self.embedding_dim = w.out_features, w.in_features
-        self.padding_idx = emb.padding_idx if emb is not None else padding_idx
+        self.padding_idx = padding_idx if emb is None else emb.padding_idx
 
     def forward(self, ids):
         rows = self.w.gather(ids)
         if self.w.scale is None: return rows
-        return (rows.float() * self.w.scale[ids.to(self.w.scale.device)][..., None]).to(torch.bfloat16)
+        row_scale = self.w.scale[ids.to(self.w.scale.device)]     # fp8 table: codes come back unscaled
+        return (rows.float() * row_scale.unsqueeze(-1)).to(torch.bfloat16)
 
     def extra_repr(self):
         return f"{self.num_embeddings}, {self.embedding_dim}, {self.w.bytes / 1e6:.1f} MB (BF16: {self.w.bytes_bf16 / 1e6:.1f} MB)"
 
 
-class _FusedHead(nn.Module):
-    """One output slice of a fused projection: head 0 runs the fused matvec, the others pick their slice of its result."""
+class FusedProjection:
+    """Several projections of the same input stored as one compressed matrix (q/k/v, gate/up).  Not a module itself: its
+    heads are the modules the model calls.  The first head called with a new input runs the matrix once; the others slice
+    the stored result.  "Same input" = same storage address, shape and version counter, so a recycled Python object id or
+    an in-place update of x can never return a stale result."""
 
-    def __init__(self, shared, index, start, end):
+    def __init__(self, lin: NWCLinear, names, sizes):
+        self.lin, self.names, self.sizes = lin, list(names), [int(s) for s in sizes]
+        self.offsets = [sum(self.sizes[:i]) for i in range(len(self.sizes))]
+        self._key, self._out = None, None
+
+    def result(self, x):
+        key = (x.data_ptr(), tuple(x.shape), x._version, x.dtype)
+        if key != self._key or self._out is None:
+            self._out, self._key = self.lin(x), key
+        return self._out
+
+    def heads(self):
+        return [_FusedHead(self, i) for i in range(len(self.names))]
+
+
+class _FusedHead(nn.Module):
+    """One output slice of a FusedProjection."""
+
+    def __init__(self, group: FusedProjection, index: int):
         super().__init__()
-        self.g, self.index, self.start, self.end = shared, index, start, end
-        self.in_features, self.out_features = shared["lin"].in_features, end - start
+        self.g, self.index = group, index
+        self.start = group.offsets[index]
+        self.end = self.start + group.sizes[index]
+        self.in_features, self.out_features = group.lin.in_features, group.sizes[index]
 
     def forward(self, x):
-        g = self.g
-        if self.index == 0 or g["x_id"] != id(x) or g["y"] is None:
-            g["y"] = g["lin"](x); g["x_id"] = id(x)
-        return g["y"][..., self.start:self.end]
+        return self.g.result(x)[..., self.start:self.end]
+
+
+def install_fused(parent: nn.Module, group: FusedProjection):
+    """Put the heads of `group` in place of the attributes it names on `parent`."""
+    for name, head in zip(group.names, group.heads()): setattr(parent, name, head)
+
+
+def fused_groups(model: nn.Module):
+    """(parent path, FusedProjection) for every fused projection of the model, each once."""
+    seen, found = set(), []
+    for path, mod in model.named_modules():
+        if isinstance(mod, _FusedHead) and id(mod.g) not in seen:
+            seen.add(id(mod.g)); found.append((path.rpartition(".")[0], mod.g))
+    return found
 
 
 def fuse(model: nn.Module, groups=(("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj")), device="cuda", elem="bf16", layout=None, verbose=True):
     """Concatenate sibling nn.Linear layers that read the same input into one compressed matrix (fewer, larger
     launches).  Call before `convert`.  Returns the number of fused groups."""
-    count = 0
-    for mod in list(model.modules()):
+    made = 0
+    for parent in list(model.modules()):
         for names in groups:
-            lins = [getattr(mod, nm, None) for nm in names]
-            if not all(isinstance(l, nn.Linear) for l in lins): continue
-            if len({l.in_features for l in lins}) != 1 or any(l.weight.dtype != torch.bfloat16 for l in lins): continue
-            W = torch.cat([l.weight.data for l in lins], 0)
-            if not fits(*W.shape): continue
+            members = [getattr(parent, n, None) for n in names]
+            if not all(isinstance(m, nn.Linear) for m in members): continue
+            if any(m.in_features != members[0].in_features or m.weight.dtype != torch.bfloat16 for m in members): continue
+            stacked = torch.cat([m.weight.data for m in members], dim=0)
+            if not fits(*stacked.shape): continue
             bias = None
-            if any(l.bias is not None for l in lins):
-                bias = torch.cat([l.bias.data if l.bias is not None else torch.zeros(l.out_features, dtype=W.dtype, device=W.device) for l in lins], 0)
-            lin = NWCLinear(w=NWCWeight(W, device, elem=elem, layout=layout), bias=bias, device=device)
-            shared = {"lin": lin, "y": None, "x_id": None, "names": list(names), "sizes": [l.out_features for l in lins]}
-            start = 0
-            for i, (nm, l) in enumerate(zip(names, lins)):
-                setattr(mod, nm, _FusedHead(shared, i, start, start + l.out_features)); start += l.out_features
-                l.weight.data = torch.empty(0)
-            count += 1
-    if verbose: print(f"NWC: {count} projection groups fused")
-    return count
+            if any(m.bias is not None for m in members):            # members without a bias contribute zeros
+                bias = torch.cat([m.bias.data if m.bias is not None else stacked.new_zeros(m.out_features) for m in members])
+            lin = NWCLinear(w=NWCWeight(stacked, device, elem=elem, layout=layout), bias=bias, device=device)
+            install_fused(parent, FusedProjection(lin, names, [m.out_features for m in members]))
+            for m in members: _drop_storage(m.weight)
+            made += 1
+    if verbose: print(f"NWC: {made} projection groups fused")
+    return made
 
 
-def _children(model):
-    for name, mod in list(model.named_modules()):
-        for child, cm in list(mod.named_children()):
-            yield name, mod, child, cm
+class _ConversionPlan:
+    """What `convert` will do, decided from one scan: `tables` = embeddings to compress (with the lm_head modules that
+    share their storage), `linears` = plain layers, `skipped` = layers left alone and why."""
+
+    def __init__(self, model, tied, embeddings):
+        self.tables, self.linears, self.skipped = [], [], []
+        sites = [(path, parent, attr, child) for path, parent in model.named_modules() for attr, child in parent.named_children()]
+        table_sites = [(s, s[3].weight.data_ptr()) for s in sites if isinstance(s[3], nn.Embedding)]
+        table_ptrs = {ptr for _, ptr in table_sites}
+        usable = lambda t: t.dtype == torch.bfloat16 and t.numel() > 0
+        claimed = set()
+        for site, ptr in table_sites:
+            emb = site[3]
+            if not (usable(emb.weight) and fits(emb.num_embeddings, emb.embedding_dim)): continue
+            sharers = [s for s in sites if isinstance(s[3], nn.Linear) and s[3].weight.numel() and s[3].weight.data_ptr() == ptr] if tied else []
+            if sharers or embeddings:
+                self.tables.append((site, sharers))
+                claimed.update(id(s[3]) for s in sharers)
+        for s in sites:
+            lin = s[3]
+            if not isinstance(lin, nn.Linear) or id(lin) in claimed: continue
+            name = f"{s[0]}.{s[2]}" if s[0] else s[2]
+            if lin.weight.data_ptr() in table_ptrs and lin.weight.numel(): self.skipped.append(f"{name} {tuple(lin.weight.shape)} [tied]")
+            elif usable(lin.weight) and fits(lin.out_features, lin.in_features): self.linears.append(s)
+            else: self.skipped.append(f"{name} {tuple(lin.weight.shape)} [shape]")
 
 
 def convert(model: nn.Module, device="cuda", verbose=True, tied=True, elem="bf16", embeddings=True, layout=None):
     """Replace every supported nn.Linear (and embeddings) by NWC modules and move the rest to `device`.
-    Returns (bytes_nwc, bytes_bf16) of the compressed matrices."""
-    total_nwc = total_bf16 = replaced = 0
-    skipped = []
-
-    def account(w):
-        nonlocal total_nwc, total_bf16, replaced
-        total_nwc += w.bytes; total_bf16 += w.bytes_bf16; replaced += 1
-
-    shared_ptrs = {m.weight.data_ptr() for m in model.modules() if isinstance(m, nn.Embedding)}
-    if tied:       # tied embedding + lm_head: one compressed matrix serves the lookup (gather) and the logits (matvec)
-        embs = {m.weight.data_ptr(): m for m in model.modules()
-                if isinstance(m, nn.Embedding) and m.weight.dtype == torch.bfloat16 and m.weight.numel() and fits(m.num_embeddings, m.embedding_dim)}
-        for name, mod, child, cm in list(_children(model)):
-            if not (isinstance(cm, nn.Linear) and cm.weight.numel() and cm.weight.data_ptr() in embs): continue
-            emb = embs[cm.weight.data_ptr()]
-            w = NWCWeight(emb.weight.data, device, elem=elem, layout=layout)
-            setattr(mod, child, NWCLinear(cm, device, w=w))
-            for _, emod, echild, ecm in list(_children(model)):
-                if ecm is emb: setattr(emod, echild, NWCEmbedding(emb, w))
-            account(w)
-            shared_ptrs.discard(cm.weight.data_ptr())
-            emb.weight.data = torch.empty(0); cm.weight.data = torch.empty(0)
-    if embeddings:  # untied tables: always lossless bf16, looked up with the gather kernel
-        for name, mod, child, cm in list(_children(model)):
-            if isinstance(cm, nn.Embedding) and cm.weight.dtype == torch.bfloat16 and cm.weight.numel() and fits(cm.num_embeddings, cm.embedding_dim):
-                w = NWCWeight(cm.weight.data, device, elem="bf16", layout=layout)
-                setattr(mod, child, NWCEmbedding(cm, w))
-                account(w); cm.weight.data = torch.empty(0)
-    for m in model.modules():
-        if isinstance(m, _FusedHead) and m.index == 0: account(m.g["lin"].w)
-    for name, mod, child, cm in list(_children(model)):
-        if not isinstance(cm, nn.Linear): continue
-        if cm.weight.dtype == torch.bfloat16 and cm.weight.numel() and fits(cm.out_features, cm.in_features) and cm.weight.data_ptr() not in shared_ptrs:
-            new = NWCLinear(cm, device, elem=elem, layout=layout)
-            setattr(mod, child, new); account(new.w)
-            cm.weight.data = torch.empty(0)
-        else:
-            skipped.append(f"{name}.{child} {tuple(cm.weight.shape)} [{'tied' if cm.weight.data_ptr() in shared_ptrs else 'shape'}]")
+    Returns (bytes_nwc, bytes_bf16) of the compressed matrices.  A tied embedding + lm_head pair becomes ONE compressed
+    matrix serving the lookup (gather kernel) and the logits (matvec); untied tables are always stored lossless."""
+    plan = _ConversionPlan(model, tied, embeddings)
+    done = [g.lin.w for _, g in fused_groups(model)]                # matrices `fuse` already made count towards the totals
+    for (path, parent, attr, emb), sharers in plan.tables:
+        w = NWCWeight(emb.weight.data, device, elem=elem if sharers else "bf16", layout=layout)
+        setattr(parent, attr, NWCEmbedding(emb, w))
+        for _, head_parent, head_attr, head in sharers:
+            setattr(head_parent, head_attr, NWCLinear(head, device, w=w))
+            _drop_storage(head.weight)
+        _drop_storage(emb.weight)
+        done.append(w)
+    for path, parent, attr, lin in plan.linears:
+        new = NWCLinear(lin, device, elem=elem, layout=layout)
+        setattr(parent, attr, new)
+        _drop_storage(lin.weight)
+        done.append(new.w)
     model.to(device)
+    total_nwc, total_bf16 = sum(w.bytes for w in done), sum(w.bytes_bf16 for w in done)
     if verbose:
-        print(f"NWC ({elem}): {replaced} linear layers replaced, {total_bf16 / 1e9:.2f} GB BF16 -> {total_nwc / 1e9:.2f} GB "
+        print(f"NWC ({elem}): {len(done)} linear layers replaced, {total_bf16 / 1e9:.2f} GB BF16 -> {total_nwc / 1e9:.2f} GB "
               f"(ratio {total_nwc / max(total_bf16, 1):.4f})")
-        if skipped: print("  skipped:", ", ".join(skipped[:6]), "..." if len(skipped) > 6 else "")
+        if plan.skipped: print("  skipped:", ", ".join(plan.skipped[:6]), "..." if len(plan.skipped) > 6 else "")
     return total_nwc, total_bf16
 
 
 class RefFP8Linear(nn.Module):
-    """Comparison only: uncompressed weight-only fp8 served by the library's plain fp8 matvec at batch 1."""
+    """Comparison only: uncompressed weight-only fp8 served by the library's plain fp8 matvec at batch 1 (the baseline the
+    fp8 configuration is measured against; reference: nwc/nwc_torch.py:272-292)."""
 
     def __init__(self, linear: nn.Linear, device="cuda"):
         super().__init__()
-        q, scale = quantize_fp8(linear.weight.data)
-        self.w8 = q.contiguous().to(device); self.scale = scale.to(device)
+        codes, scale = quantize_fp8(linear.weight.data)
+        self.w8, self.scale = codes.contiguous().to(device), scale.to(device)
         self.in_features, self.out_features = linear.in_features, linear.out_features
-        self.bias = None if linear.bias is None else nn.Parameter(linear.bias.data.to(device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.bias = _bias_param(None if linear.bias is None else linear.bias.data, device)
 
     def forward(self, x):
-        if x.numel() == self.in_features and x.dtype == torch.bfloat16:
+        if x.dtype == torch.bfloat16 and x.numel() == self.in_features:
             y = ref_fp8_matvec(self.w8, self.scale, x.reshape(-1).float())
-            if self.bias is not None: y = y + self.bias
-            return y.view(*x.shape[:-1], self.out_features)
+            return (y if self.bias is None else y + self.bias).view(*x.shape[:-1], self.out_features)
         y = F.linear(x, self.w8.to(torch.bfloat16)).float() * self.scale
         if self.bias is not None: y = y + self.bias.float()
         return y.to(x.dtype)
@@ -173,11 +238,12 @@ class RefFP8Linear(nn.Module):
 
 def convert_ref_fp8(model: nn.Module, device="cuda", verbose=True):
     """Replace every untied nn.Linear by RefFP8Linear (the uncompressed fp8 baseline)."""
-    shared = {m.weight.data_ptr() for m in model.modules() if isinstance(m, nn.Embedding)}
-    n = 0
-    for name, mod, child, cm in list(_children(model)):
-        if isinstance(cm, nn.Linear) and cm.weight.dtype == torch.bfloat16 and cm.weight.data_ptr() not in shared:
-            setattr(mod, child, RefFP8Linear(cm, device)); cm.weight.data = torch.empty(0); n += 1
+    tables = {m.weight.data_ptr() for m in model.modules() if isinstance(m, nn.Embedding)}
+    swapped = 0
+    for parent in list(model.modules()):
+        for attr, lin in list(parent.named_children()):
+            if isinstance(lin, nn.Linear) and lin.weight.dtype == torch.bfloat16 and lin.weight.data_ptr() not in tables:
+                setattr(parent, attr, RefFP8Linear(lin, device)); _drop_storage(lin.weight); swapped += 1
     model.to(device)
-    if verbose: print(f"reference fp8: {n} linear layers replaced")
-    return n
+    if verbose: print(f"reference fp8: {swapped} linear layers replaced")
+    return swapped

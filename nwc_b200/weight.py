@@ -1,6 +1,12 @@
-"""NWCWeight: one [out, in] matrix kept entropy-coded in HBM, plus the calls that use it without decompressing it
-to memory.  Python-side mirror of the reference's compressed-tensor object (reference: nwc/nwc_torch.py:126-269): same
-constructor, attributes and methods, so checkpoint code and modules written against the reference work on it.
+"""NWCWeight: one [out, in] matrix kept entropy-coded in HBM and the kernels that consume it without ever writing a
+decompressed copy.
+
+The attribute and method names are the reference's compressed-tensor contract (reference: nwc/nwc_torch.py:126-269:
+data, bases, hdr, lut, low, scale, scratch, K16, bytes, bytes_bf16, bytes_native, elem, layout, code, block;
+linear_bf16 / matvec / gather / dequant / tensors / from_tensors), because checkpoints and model code are written
+against them.  Behind them this class is a thin owner of device tensors around three things of this library: the GPU
+encoder (construction), `repack.Compressed` (the stored form, also what tensor-parallel shards are cut from) and the
+C-ABI calls.
 """
 import os
 
@@ -8,9 +14,11 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib as L
+from .repack import Compressed
 
 ELEM_BF16, ELEM_FP8 = 0, 1
 ELEMS = {"bf16": ELEM_BF16, "fp8": ELEM_FP8}
+ELEM_NAMES = {v: k for k, v in ELEMS.items()}
 LAYOUTS = (0, 1, 2)
 FP8_MAX = 448.0
 # default layout per element type; NWC_LAYOUT=0|1|2 overrides (same switch as the reference)
@@ -20,12 +28,12 @@ if "NWC_LAYOUT" in os.environ:
 
 
 def quantize_fp8(w: torch.Tensor):
-    """bf16 / float [out, in] -> (float8_e4m3fn tensor, fp32 scale[out]): symmetric absmax scaling per output channel
-    (reference: nwc/nwc_torch.py:88-94)."""
-    wf = w.detach().float()
-    scale = wf.abs().amax(dim=1).clamp_min(1e-12) / FP8_MAX
-    q = (wf / scale[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
-    return q, scale
+    """[out, in] weights -> (float8_e4m3fn codes, fp32 scale[out]) with scale = row absmax / 448, the weight-only fp8
+    scheme of the reference (nwc/nwc_torch.py:88-94)."""
+    full = w.detach().to(torch.float32)
+    scale = torch.clamp_min(full.abs().amax(dim=1), 1e-12) / FP8_MAX
+    codes = torch.clamp(full / scale.unsqueeze(1), -FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return codes, scale
 
 
 def fits(out_features, in_features):
@@ -37,10 +45,36 @@ def choose_block(n):
     return L.FIXED_BLOCK
 
 
-def _layout_query(out_f, in_f, code):
-    lay = torch.empty(4, dtype=torch.int64)
-    if L.lib.nwc_layout(out_f, in_f, code, L.ptr(lay)): raise RuntimeError("nwc_layout: bad shape")
-    return lay.tolist()          # blocks, raw-plane bytes, scratch floats, K16
+class _Sizes:
+    """What nwc_layout reports for a shape: block count, raw-plane bytes, scratch floats, padded row length."""
+
+    def __init__(self, out_f, in_f, code):
+        answer = torch.empty(4, dtype=torch.int64)
+        if L.lib.nwc_layout(out_f, in_f, code, L.ptr(answer)): raise RuntimeError("nwc_layout: bad shape")
+        self.blocks, self.raw_bytes, self.scratch_floats, self.K16 = answer.tolist()
+
+
+def _encode_on_device(src, out_f, in_f, code, sizes, device):
+    """Run the GPU encoder over `src` (int16 bf16 bits or uint8 fp8 codes, on `device`).  The stream buffer is sized for
+    ~12 bits per weight first and for the worst case if that does not suffice.  Returns (data, bases, hdr, low, lut)."""
+    n = out_f * in_f
+    psym = torch.zeros(L.NPAIR, dtype=torch.int16)
+    bases = torch.empty(sizes.blocks, dtype=torch.int32, device=device)
+    hdr = torch.empty(sizes.blocks * L.HDR_BLOCK, dtype=torch.uint8, device=device)
+    low = torch.zeros(sizes.raw_bytes + L.RAW_SLACK, dtype=torch.uint8, device=device)
+    overhead = sizes.blocks * 64 + 4096
+    for capacity in (n + n // 2 + overhead, 3 * n + overhead):
+        stream = torch.empty(capacity, dtype=torch.uint8, device=device)
+        length = L.lib.nwc_encode_device(L.stream(), L.ptr(src), n, in_f, code, L.ptr(psym), L.ptr(bases), L.ptr(hdr), L.ptr(stream), capacity, L.ptr(low))
+        if length != -1: break
+    if length == -2: raise ValueError("fp8 weights contain NaN")
+    if length == -3: raise ValueError("layout 2 cannot code this matrix (a lane stream has more than 255 exceptions); use layout 0 or 1")
+    if length < 0: raise RuntimeError(f"nwc_encode failed ({length})")
+    data = torch.zeros(length + 64, dtype=torch.uint8, device=device)         # exact size + the slack the kernels may read
+    data[:length].copy_(stream[:length])
+    lut = torch.empty(L.TAB_WORDS, dtype=torch.int32)
+    L.lib.nwc_build_tab(None, L.ptr(psym), code, L.ptr(lut))
+    return data, bases, hdr, low, lut.to(device)
 
 
 class NWCWeight:
@@ -50,85 +84,80 @@ class NWCWeight:
 
     def __init__(self, w: torch.Tensor, device="cuda", block=None, elem="bf16", scale=None, layout=None):
         L.require_cuda()
-        if w.dim() != 2: raise ValueError("a 2-d weight matrix is expected")
         device = torch.device(device)
         if device.type != "cuda": raise RuntimeError("nwc_b200 encodes and decodes on CUDA devices only")
-        out_f, in_f = w.shape
-        if not fits(out_f, in_f): raise ValueError(f"shape {tuple(w.shape)} not supported")
-        self.elem = ELEMS[elem]
-        self.layout = LAYOUT_DEFAULT[self.elem] if layout is None else int(layout)
-        if self.layout not in LAYOUTS: raise ValueError(f"unknown layout {self.layout}")
+        if w.dim() != 2: raise ValueError("a 2-d weight matrix is expected")
+        if not fits(*w.shape): raise ValueError(f"shape {tuple(w.shape)} not supported")
+        self._describe(w.shape[0], w.shape[1], ELEMS[elem], LAYOUT_DEFAULT[ELEMS[elem]] if layout is None else int(layout), block or L.FIXED_BLOCK)
         with torch.cuda.device(device):
             if self.elem == ELEM_FP8:
-                if w.dtype == torch.float8_e4m3fn:
-                    if scale is None: raise ValueError("fp8 weights need their per-row scale")
-                    q = w
-                else:
-                    q, scale = quantize_fp8(w.to(device))
-                src = q.detach().to(device).contiguous().view(torch.uint8)
-                self.scale = scale.detach().float().contiguous().to(device)
+                if w.dtype != torch.float8_e4m3fn: w, scale = quantize_fp8(w.to(device))
+                elif scale is None: raise ValueError("fp8 weights need their per-row scale")
+                src = w.detach().to(device).contiguous().view(torch.uint8)
+                scale = scale.detach().to(device=device, dtype=torch.float32).contiguous()
             else:
                 if w.dtype != torch.bfloat16: raise ValueError("bf16 weights expected (elem='fp8' for fp8 weights)")
-                src = w.detach().to(device).contiguous().view(torch.int16)
-                self.scale = None
-            n = out_f * in_f
-            nb, n_low, n_scratch, self.K16 = _layout_query(out_f, in_f, self.code)
-            psym = torch.zeros(L.NPAIR, dtype=torch.int16)
-            bases = torch.empty(nb, dtype=torch.int32, device=device)
-            hdr = torch.empty(nb * L.HDR_BLOCK, dtype=torch.uint8, device=device)
-            low = torch.zeros(n_low + L.RAW_SLACK, dtype=torch.uint8, device=device)
-            dl = -1
-            for cap in (n + n // 2 + nb * 64 + 4096, 3 * n + nb * 64 + 4096):     # ~12 bits per weight nearly always suffice
-                data = torch.empty(cap, dtype=torch.uint8, device=device)
-                dl = L.lib.nwc_encode_device(L.stream(), L.ptr(src), n, in_f, self.code, L.ptr(psym), L.ptr(bases), L.ptr(hdr), L.ptr(data), cap, L.ptr(low))
-                if dl >= 0 or dl in (-2, -3): break
-            if dl == -2: raise ValueError("fp8 weights contain NaN")
-            if dl == -3: raise ValueError("layout 2 cannot code this matrix (a lane stream has more than 255 exceptions); use layout 0 or 1")
-            if dl < 0: raise RuntimeError(f"nwc_encode failed ({dl})")
-            lut = torch.empty(L.TAB_WORDS, dtype=torch.int32)
-            L.lib.nwc_build_tab(None, L.ptr(psym), self.code, L.ptr(lut))
-            self.out_features, self.in_features, self.n, self.block = out_f, in_f, n, block or L.FIXED_BLOCK
-            self.data = torch.zeros(dl + 64, dtype=torch.uint8, device=device)
-            self.data[: min(dl, cap)].copy_(data[: min(dl, cap)])
-            del data
-            self.bases, self.hdr, self.low, self.lut = bases, hdr, low, lut.to(device)
-            self._finish(dl, n_low, n_scratch, device)
+                src, scale = w.detach().to(device).contiguous().view(torch.int16), None
+            sizes = _Sizes(self.out_features, self.in_features, self.code)
+            data, bases, hdr, low, lut = _encode_on_device(src, self.out_features, self.in_features, self.code, sizes, device)
+            self._adopt(data, bases, hdr, lut, low, scale, sizes, data.numel() - 64, device)
+
+    # ---- construction helpers ----
+    def _describe(self, out_f, in_f, elem, layout, block):
+        if layout not in LAYOUTS: raise ValueError(f"unknown layout {layout}")
+        self.out_features, self.in_features, self.n = int(out_f), int(in_f), int(out_f) * int(in_f)
+        self.elem, self.layout, self.block = elem, layout, block
+
+    def _adopt(self, data, bases, hdr, lut, low, scale, sizes, stream_bytes, device):
+        """Take ownership of the device tensors and do the byte accounting (the roofline numerator of every matvec: stream +
+        offsets + headers + table + raw planes + scales, as the reference counts them, nwc/nwc_torch.py:185-190)."""
+        self.data, self.bases, self.hdr, self.lut, self.low, self.scale, self.K16 = data, bases, hdr, lut, low, scale, sizes.K16
+        self.bytes = stream_bytes + 4 * bases.numel() + hdr.numel() + 4 * lut.numel() + sizes.raw_bytes + (4 * scale.numel() if scale is not None else 0)
+        self.bytes_bf16 = 2 * self.n
+        self.bytes_native = self.n + 4 * self.out_features if self.elem == ELEM_FP8 else 2 * self.n
+        self.scratch = torch.empty(sizes.scratch_floats, dtype=torch.float32, device=device)
 
     @property
     def code(self):
         """The library's elem parameter: element type in bits 0..3, layout in bits 4..7."""
         return self.elem | (self.layout << 4)
 
-    def _finish(self, dl, n_low, n_scratch, device):
-        n = self.n
-        self.bytes = dl + self.bases.numel() * 4 + self.hdr.numel() + self.lut.numel() * 4 + n_low + (self.scale.numel() * 4 if self.scale is not None else 0)
-        self.bytes_bf16 = 2 * n
-        self.bytes_native = n + self.out_features * 4 if self.elem == ELEM_FP8 else 2 * n
-        self.scratch = torch.empty(n_scratch, dtype=torch.float32, device=device)
+    @classmethod
+    def from_compressed(cls, c: Compressed, device="cuda", block=None):
+        """A matrix in its stored form (a checkpoint record or a tensor-parallel shard cut from one) onto `device`."""
+        L.require_cuda()
+        self = cls.__new__(cls)
+        self._describe(c.M, c.K, ELEMS[c.elem], int(c.layout), block or L.FIXED_BLOCK)
+        sizes = _Sizes(c.M, c.K, self.code)
+        low = c.low
+        if (c.bases.numel(), c.hdr.numel(), c.lut.numel()) != (sizes.blocks, sizes.blocks * L.HDR_BLOCK, L.TAB_WORDS) or low.numel() not in (sizes.raw_bytes, sizes.raw_bytes + L.RAW_SLACK):
+            raise ValueError("checkpoint does not match this library version")
+        if low.numel() == sizes.raw_bytes: low = F.pad(low, (0, L.RAW_SLACK))          # the planes are read one slot ahead
+        put = lambda t: t.contiguous().to(device)
+        scale = None if c.scale is None else put(c.scale.float())
+        self._adopt(put(c.data), put(c.bases), put(c.hdr), put(c.lut), put(low), scale, sizes, c.data.numel(), device)
+        return self
 
     @classmethod
     def from_tensors(cls, out_f, in_f, block, data, bases, hdr, lut, low, device="cuda", elem="bf16", scale=None, layout=0):
         """Compressed matrix from stored tensors (checkpoints), without the original weights."""
-        L.require_cuda()
-        self = cls.__new__(cls)
-        self.elem = ELEMS[elem]; self.layout = int(layout)
-        if self.layout not in LAYOUTS: raise ValueError(f"unknown layout {self.layout}")
-        n = out_f * in_f
-        nb, n_low, n_scratch, self.K16 = _layout_query(out_f, in_f, self.code)
-        if bases.numel() != nb or hdr.numel() != nb * L.HDR_BLOCK or low.numel() not in (n_low, n_low + L.RAW_SLACK) or lut.numel() != L.TAB_WORDS:
-            raise ValueError("checkpoint does not match this library version")
-        self.out_features, self.in_features, self.n, self.block = out_f, in_f, n, block
-        if low.numel() == n_low: low = F.pad(low, (0, L.RAW_SLACK))      # the planes are read one slot ahead
-        self.data, self.bases, self.hdr, self.lut, self.low = (t.contiguous().to(device) for t in (data, bases, hdr, lut, low))
-        self.scale = None if scale is None else scale.float().contiguous().to(device)
-        self._finish(self.data.numel(), n_low, n_scratch, device)
-        return self
+        return cls.from_compressed(Compressed(out_f, in_f, int(layout), elem, data, bases, hdr, lut, low, scale), device, block)
+
+    def compressed(self) -> Compressed:
+        return Compressed(self.out_features, self.in_features, self.layout, ELEM_NAMES[self.elem], self.data, self.bases, self.hdr, self.lut, self.low, self.scale)
 
     def tensors(self):
         """The tensors that fully describe the compressed state."""
-        t = {"data": self.data, "bases": self.bases, "hdr": self.hdr, "lut": self.lut, "low": self.low}
-        if self.scale is not None: t["scale"] = self.scale
-        return t
+        named = {"data": self.data, "bases": self.bases, "hdr": self.hdr, "lut": self.lut, "low": self.low}
+        if self.scale is not None: named["scale"] = self.scale
+        return named
+
+    # ---- calls ----
+    def _operands(self):
+        return (L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low))
+
+    def _shape_args(self):
+        return (self.n, self.block, self.in_features, self.code)
 
     def _padded_x(self, x):
         """x zero-extended to the length the kernels read: K16 for layout 0, K rounded up to 32 otherwise."""
@@ -141,20 +170,17 @@ class NWCWeight:
         """fp32 test path: y = W x, fp32 in and out."""
         y = torch.empty(self.out_features, dtype=torch.float32, device=x_f32.device)
         xin = self._padded_x(x_f32.float().contiguous())
-        err = L.lib.nwc_matvec(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low),
-                               L.ptr(xin), L.ptr(y), self.n, self.block, self.in_features, self.code)
+        err = L.lib.nwc_matvec(L.stream(), *self._operands(), L.ptr(xin), L.ptr(y), *self._shape_args())
         if err: raise RuntimeError(f"nwc_matvec error {err}")
         return y if self.scale is None else y * self.scale
 
     def linear_bf16(self, x: torch.Tensor, bias, splits: int = 0) -> torch.Tensor:
-        """Token path: y = scale * (W x) + bias; x bf16 or fp32 [in], y bf16 [out]."""
+        """Token path: y = scale * (W x) + bias; x bf16 or fp32 [in], y bf16 [out].  The ABI takes fp32 x for layout 0 and
+        bf16 x for layouts 1 and 2."""
         y = torch.empty(self.out_features, dtype=torch.bfloat16, device=x.device)
-        if self.layout: xin = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-        else: xin = x if x.dtype == torch.float32 else x.float()
-        xin = self._padded_x(xin.contiguous())
-        err = L.lib.nwc_linear_bf16_splits(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low),
-                                           L.ptr(xin), L.ptr(bias), L.ptr(self.scale), L.ptr(self.scratch), L.ptr(y),
-                                           self.n, self.block, self.in_features, self.code, splits)
+        xin = self._padded_x(x.to(torch.bfloat16 if self.layout else torch.float32).contiguous())
+        err = L.lib.nwc_linear_bf16_splits(L.stream(), *self._operands(), L.ptr(xin), L.ptr(bias), L.ptr(self.scale), L.ptr(self.scratch), L.ptr(y),
+                                           *self._shape_args(), splits)
         if err: raise RuntimeError(f"nwc_linear_bf16 error {err}")
         return y
 
@@ -166,8 +192,8 @@ class NWCWeight:
         if K % 8: x = F.pad(x, (0, 8 - K % 8))
         x = x.contiguous()
         y = torch.empty(T, self.out_features, dtype=torch.bfloat16, device=x.device)
-        err = L.lib.nwc_linear_prefill(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low), L.ptr(x), T,
-                                       x.shape[1], L.ptr(bias), L.ptr(self.scale), L.ptr(y), self.out_features, self.n, self.block, self.in_features, self.code)
+        err = L.lib.nwc_linear_prefill(L.stream(), *self._operands(), L.ptr(x), T, x.shape[1], L.ptr(bias), L.ptr(self.scale), L.ptr(y), self.out_features,
+                                       *self._shape_args())
         if err == -2: return None
         if err: raise RuntimeError(f"nwc_linear_prefill error {err}")
         return y
@@ -176,8 +202,7 @@ class NWCWeight:
         """Rows ids -> bf16[..., in] (embedding lookup straight from the compressed matrix)."""
         flat = ids.reshape(-1).to(device=self.data.device, dtype=torch.int64).contiguous()
         out = torch.empty(flat.numel(), self.K16, dtype=torch.bfloat16, device=self.data.device)
-        err = L.lib.nwc_gather(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low),
-                               L.ptr(flat), flat.numel(), L.ptr(out), self.n, self.block, self.in_features, self.code)
+        err = L.lib.nwc_gather(L.stream(), *self._operands(), L.ptr(flat), flat.numel(), L.ptr(out), *self._shape_args())
         if err: raise RuntimeError(f"nwc_gather error {err}")
         if self.K16 != self.in_features: out = out[:, : self.in_features].contiguous()
         return out.view(*ids.shape, self.in_features)
@@ -186,8 +211,7 @@ class NWCWeight:
         """The whole matrix as bf16 (a view with row stride K16 when K is not a multiple of 16).  fp8: the unscaled
         fp8 values, exact in bf16; multiply rows by `scale` for the weights."""
         w = torch.empty((self.out_features, self.K16), dtype=torch.bfloat16, device=self.data.device)
-        err = L.lib.nwc_dequant(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(self.lut), L.ptr(self.low),
-                                L.ptr(w), self.n, self.block, self.in_features, self.code)
+        err = L.lib.nwc_dequant(L.stream(), *self._operands(), L.ptr(w), *self._shape_args())
         if err: raise RuntimeError(f"nwc_dequant error {err}")
         return w if self.K16 == self.in_features else w[:, : self.in_features]
 
@@ -195,6 +219,11 @@ class NWCWeight:
         """fp8 matrices: (float8_e4m3fn [out, in], fp32 scale[out]), bit-exact with what was encoded."""
         if self.elem != ELEM_FP8: raise ValueError("not an fp8 matrix")
         return self.dequant().to(torch.float8_e4m3fn), self.scale
+
+    def dense(self) -> torch.Tensor:
+        """The weights as a plain bf16 matrix (fp8: codes times scale, rounded to bf16)."""
+        full = self.dequant()
+        return full if self.scale is None else (full.float() * self.scale[:, None]).to(torch.bfloat16)
 
 
 def ref_fp8_matvec(w8: torch.Tensor, scale: torch.Tensor, x_f32: torch.Tensor) -> torch.Tensor:

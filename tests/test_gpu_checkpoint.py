@@ -80,3 +80,82 @@ def test_corrupt_checkpoints_are_rejected(tmp_path):
     with pytest.raises(RuntimeError, match="format version"): load_pretrained(d, verbose=False)
     c["library_version"] = 11; c["weights"][0]["in"] += 16; json.dump(c, open(cfgp, "w"))
     with pytest.raises(ValueError, match="does not match"): load_pretrained(d, verbose=False)
+
+
+# ---- checkpoint -> decode engine (the CUDA-graph loop runs what load_pretrained reads), and its tensor-parallel shards ----
+
+def qwen3_model(layers=2, hidden=256, inter=1024, vocab=2048, tied=True):
+    from transformers import AutoModelForCausalLM, Qwen3Config
+    torch.manual_seed(1)
+    cfg = Qwen3Config(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=layers, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=64, max_position_embeddings=512, tie_word_embeddings=tied, rope_theta=1e6, rms_norm_eps=1e-6)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16).eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "norm" in n: p.copy_(1.0 + 0.1 * torch.randn_like(p.float()))
+    return cfg, model
+
+
+def engine_sources(sd):
+    def source(name, r, c):
+        if name == "embed": return sd["model.embed_tokens.weight"].cuda()
+        if name == "lm_head": return sd.get("lm_head.weight", sd["model.embed_tokens.weight"]).cuda()
+        i, kind = name[1:].split(".")
+        pre = f"model.layers.{i}."
+        if kind == "qkv": return torch.cat([sd[pre + f"self_attn.{k}_proj.weight"] for k in "qkv"], 0).cuda()
+        if kind == "o": return sd[pre + "self_attn.o_proj.weight"].cuda()
+        if kind == "gate_up": return torch.cat([sd[pre + "mlp.gate_proj.weight"], sd[pre + "mlp.up_proj.weight"]], 0).cuda()
+        return sd[pre + "mlp.down_proj.weight"].cuda()
+
+    def vector(name, n):
+        if name == "final_norm": return sd["model.norm.weight"].cuda()
+        i, kind = name[1:].split(".")
+        key = {"in_norm": "input_layernorm", "post_norm": "post_attention_layernorm", "q_norm": "self_attn.q_norm", "k_norm": "self_attn.k_norm"}[kind]
+        return sd[f"model.layers.{i}.{key}.weight"].cuda()
+    return source, vector
+
+
+@pytest.mark.parametrize("layout,tied,fused", [(2, True, True), (0, False, True), (1, True, True), (2, False, False)])
+def test_engine_from_checkpoint_decodes_the_same_tokens(tmp_path, layout, tied, fused):
+    """save_pretrained -> DecodeEngine.from_pretrained: 64 greedy tokens equal to the engine built from the bf16 matrices
+    (the same compressed bits either way when the projections were fused before saving; unfused checkpoints are
+    concatenated and re-encoded, which decodes to the same weights)."""
+    from nwc_b200 import convert, fuse, save_pretrained
+    from nwc_b200.decode import DecodeEngine, DecoderConfig, DecoderWeights
+    hf_cfg, model = qwen3_model(tied=tied)
+    sd = {k: v.clone() for k, v in model.state_dict().items()}
+    if fused: fuse(model, layout=layout, verbose=False)
+    convert(model, verbose=False, layout=layout)
+    d = str(tmp_path / "ckpt"); save_pretrained(model, d, base_model="test"); del model
+    cfg = DecoderConfig("t", 2, 256, 1024, 4, 2, 64, 2048, tied, True, rope_theta=1e6, eps=1e-6)
+    source, vector = engine_sources(sd)
+    ref = DecodeEngine(DecoderWeights(cfg, source, vector, layout=layout), max_len=128)
+    eng = DecodeEngine.from_pretrained(d, max_len=128)
+    assert eng.cfg.hidden == 256 and eng.cfg.qk_norm and eng.cfg.tied == tied and (eng.w.embed is eng.w.lm_head) == tied
+    prompt = list(range(11, 23))
+    ref.prefill(prompt); want = ref.generate(64).tolist()
+    eng.prefill(prompt); got = eng.generate(64).tolist()
+    assert got == want
+    eng.capture(); eng.prefill(prompt)
+    assert eng.generate(64).tolist() == want
+
+
+@pytest.mark.parametrize("layout", [0, 1, 2])
+def test_checkpoint_shards_are_repacked_blocks(tmp_path, layout):
+    """Both ranks' shards of a two-way tensor-parallel load, built on this one GPU: every shard must dequantise to exactly
+    the rows / columns of the full matrix that nwc_b200.tp assigns to the rank, and (being re-packed, not re-encoded) must
+    carry the full matrix's decoder table."""
+    from nwc_b200 import convert, fuse, save_pretrained, tp as TP
+    from nwc_b200.decode import DecoderWeights
+    hf_cfg, model = qwen3_model(hidden=1024, inter=2048, tied=False)
+    fuse(model, layout=layout, verbose=False); convert(model, verbose=False, layout=layout)
+    d = str(tmp_path / "ckpt"); save_pretrained(model, d, base_model="test"); del model
+    full = DecoderWeights.from_checkpoint(d)
+    for rank in (0, 1):
+        part = DecoderWeights.from_checkpoint(d, tp_rank=rank, tp_world=2)
+        pairs = [("lm_head", full.lm_head, part.lm_head)] + [(k, fl[k], pl[k]) for fl, pl in zip(full.layers, part.layers) for k in ("qkv", "o", "gate_up", "down")]
+        for kind, f, p in pairs:
+            want = TP.shard(kind, f.dequant(), full.cfg, rank, 2)
+            assert torch.equal(p.dequant().contiguous(), want.contiguous()), (kind, rank)
+            assert torch.equal(p.lut, f.lut), kind
+        assert torch.equal(part.embed.dequant(), full.embed.dequant())
