@@ -26,11 +26,19 @@ LANES, SYM_TABLE_LEN, LUT_WORDS, RAW_SLACK = 32, 1024, 4096, 512
 _P, _U64, _U32, _I = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int
 
 
+def reference_root() -> str:
+    """Where the reference checkout lies: the NWC_REFERENCE_ROOT variable, else a directory `reference` next to this
+    repository.  Empty when there is none (the GPU box: only the prebuilt files travel there)."""
+    cand = os.environ.get("NWC_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.exists(os.path.join(cand, "csrc", "nwc_ops.cu")) else ""
+
+
 def build(ref: bool = True) -> None:
     """Compile the oracle (and the reference library when its sources are reachable)."""
     subprocess.run(["make", "-s", "-C", HERE], check=True)
-    if ref and os.path.exists(os.environ.get("NWC_REFERENCE_ROOT", "/root/reference") + "/csrc/nwc_ops.cu"):
-        subprocess.run(["make", "-s", "-C", HERE, "ref", "REF=" + os.environ.get("NWC_REFERENCE_ROOT", "/root/reference")], check=True)
+    root = reference_root()
+    if ref and root:
+        subprocess.run(["make", "-s", "-C", HERE, "ref", "REF=" + root], check=True)
 
 
 def code_of(elem: int, layout: int) -> int:

@@ -19,10 +19,12 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("NWC_REFERENCE_ROOT", "/root/reference")
+sys.path.insert(0, ROOT)
+import oracle                                                # noqa: E402
+REF = oracle.reference_root()
+if not REF: raise SystemExit("reference checkout not found: set NWC_REFERENCE_ROOT")
 os.environ["NWC_DLL"] = os.path.join(ROOT, "oracle", "_ref", "nwc_ops.so")
 sys.path.insert(0, REF)
-sys.path.insert(0, ROOT)
 from nwc.nwc_torch import NWCWeight, quantize_fp8          # the reference's bridge   # noqa: E402
 
 spec = importlib.util.spec_from_file_location("ref_format_test", os.path.join(REF, "tests", "test_format_cpu.py"))

@@ -159,3 +159,22 @@ def test_checkpoint_shards_are_repacked_blocks(tmp_path, layout):
             assert torch.equal(p.dequant().contiguous(), want.contiguous()), (kind, rank)
             assert torch.equal(p.lut, f.lut), kind
         assert torch.equal(part.embed.dequant(), full.embed.dequant())
+
+
+def test_command_line_self_check_and_export(tmp_path, capsys):
+    """`python -m nwc_b200.doctor` reports a working machine (every layout and element type round-trips), and
+    `python -m nwc_b200.export` writes the bf16 checkpoint that export_bf16 would."""
+    from safetensors.torch import load_file
+    from nwc_b200 import convert, fuse, save_pretrained
+    from nwc_b200 import doctor, export
+    assert doctor.main(["--shape", "130x1536"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("round trip") == 6 and "FAIL" not in out and "Ready." in out
+    cfg, model = small_model()
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    fuse(model, layout=2, verbose=False); convert(model, verbose=False, layout=2)
+    d, e = str(tmp_path / "ckpt"), str(tmp_path / "plain")
+    save_pretrained(model, d)
+    assert export.main([d, e]) == 0
+    exported = load_file(os.path.join(e, "model.safetensors"))
+    assert all(torch.equal(exported[k], v) for k, v in state.items() if k != "lm_head.weight")

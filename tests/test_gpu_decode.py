@@ -89,3 +89,99 @@ def test_position_outside_cache_sets_status_not_fault():
     eng.reset(); eng.pos.fill_(eng.max_len)            # one past the cache: the attention kernel must refuse, not write
     eng.forward_token(); torch.cuda.synchronize()
     assert int(eng.status.item()) == 1
+
+
+# ---- the 256-step bar on the benchmark configuration's shapes ----
+
+def build_0p6b_cut(layers=4):
+    """Qwen3-0.6B architecture (hidden 1024, MLP 3072, 16 q / 8 kv heads of 128, q/k norm, vocabulary 151936, tied table) cut
+    to `layers` layers so that Transformers can follow on the CPU; layout 0 as in the benchmark configuration."""
+    from transformers import Qwen3Config, AutoModelForCausalLM
+    from nwc_b200.decode import DecoderConfig, DecoderWeights, DecodeEngine
+    torch.manual_seed(0)
+    hf_cfg = Qwen3Config(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hidden_layers=layers, num_attention_heads=16,
+                         num_key_value_heads=8, head_dim=128, max_position_embeddings=1024, tie_word_embeddings=True, rope_theta=1e6, rms_norm_eps=1e-6)
+    hf_cfg._attn_implementation = "eager"
+    model = AutoModelForCausalLM.from_config(hf_cfg, dtype=torch.bfloat16).eval()
+    sd = model.state_dict()
+    cfg = DecoderConfig("qwen3-0.6b-cut", layers, 1024, 3072, 16, 8, 128, 151936, True, True, rope_theta=1e6, eps=1e-6)
+
+    def source(name, r, c):
+        if name in ("embed", "lm_head"): return sd["model.embed_tokens.weight"].cuda()
+        i, kind = name[1:].split(".")
+        pre = f"model.layers.{i}."
+        if kind == "qkv": return torch.cat([sd[pre + f"self_attn.{k}_proj.weight"] for k in "qkv"], 0).cuda()
+        if kind == "o": return sd[pre + "self_attn.o_proj.weight"].cuda()
+        if kind == "gate_up": return torch.cat([sd[pre + "mlp.gate_proj.weight"], sd[pre + "mlp.up_proj.weight"]], 0).cuda()
+        return sd[pre + "mlp.down_proj.weight"].cuda()
+
+    def vector(name, n):
+        if name == "final_norm": return sd["model.norm.weight"].cuda()
+        i, kind = name[1:].split(".")
+        key = {"in_norm": "input_layernorm", "post_norm": "post_attention_layernorm", "q_norm": "self_attn.q_norm", "k_norm": "self_attn.k_norm"}[kind]
+        return sd[f"model.layers.{i}.{key}.weight"].cuda()
+
+    return model, DecodeEngine(DecoderWeights(cfg, source, vector, layout=0), max_len=320)
+
+
+def _compare_choices(eng, logits, history, first):
+    """Feed `history` to the engine token by token; from position `first` on, its greedy choice must be Transformers' (the
+    argmax of `logits[t]`).  A different choice is accepted only as a tie: the engine picked Transformers' second-best and
+    Transformers' two best logits are closer than two bf16 steps (the two sides add in different orders).  Returns the tie
+    positions."""
+    eng.reset()
+    ties = []
+    for t in range(len(history)):
+        eng.cur.fill_(history[t]); eng.forward_token()
+        if t < first: continue
+        tok = int(eng.cur.item())
+        top2 = logits[t].topk(2)
+        if tok == int(top2.indices[0]): continue
+        gap = (top2.values[0] - top2.values[1]).item()
+        assert tok == int(top2.indices[1]) and gap <= 2.0 ** -7 * abs(top2.values[0].item()) + 1e-6, (t, tok, top2)
+        ties.append(t)
+    return ties
+
+
+def test_256_greedy_steps_follow_transformers_on_the_0p6b_shapes():
+    """Two runs of 256 compared choices each, Transformers (bf16, CPU) against the engine, ties aside (see _compare_choices):
+    (a) 32 prompt ids then Transformers' own greedy continuation as the history - and the engine's free-running 256 tokens
+        must equal that continuation up to the first tie;
+    (b) a random history of 288 ids (a random-init model's greedy continuation soon repeats one token, random ids keep every
+        step's state different): the greedy choice after each of the last 256 positions."""
+    from nwc_b200 import _lib as L
+    model, eng = build_0p6b_cut()
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, 151936, (1, 32), generator=g)
+    with torch.no_grad():
+        seq = model.generate(prompt, max_new_tokens=256, min_new_tokens=256, do_sample=False)[0]
+        logits = model(seq[None, :]).logits[0].float()                # teacher-forced logits, [288, V]
+    seq = seq.tolist()
+    ties = _compare_choices(eng, logits, seq[:-1], 31)
+    assert len(ties) <= 2, ties                                          # ties are rare events, not a tolerance
+    eng.prefill(seq[:32])
+    mine = eng.generate(256).tolist()
+    upto = 256 if not ties else ties[0] - 31
+    assert mine[:upto] == seq[32:32 + upto]
+    history = torch.randint(0, 151936, (1, 288), generator=g)
+    with torch.no_grad(): logits = model(history).logits[0].float()
+    ties = _compare_choices(eng, logits, history[0].tolist(), 32)
+    assert len(ties) <= 2, ties
+    assert L.lib.nwc_kernel_status(1) == 0
+
+
+def test_graph_replay_equals_eager_for_256_steps_on_the_full_0p6b_config():
+    """BASELINE configuration 1 itself (28 layers, synthetic weights, layout 0): 32 prompt ids + 256 greedy tokens, the
+    captured graph must reproduce the eager launches token for token, with and without dependent launch."""
+    from nwc_b200.decode import PRESETS, DecodeEngine, DecoderWeights
+    weights = DecoderWeights.synthetic(PRESETS["qwen3-0.6b"], layout=0, seed=0)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, 151936, (32,), generator=g)
+    runs = []
+    for dependent in (False, True):
+        eng = DecodeEngine(weights, max_len=320, dependent_launch=dependent)
+        eng.prefill(prompt); eager = eng.generate(256).tolist()
+        eng.capture(); eng.prefill(prompt); replay = eng.generate(256).tolist()
+        assert eager == replay
+        runs.append(replay)
+    assert runs[0] == runs[1]
