@@ -82,7 +82,7 @@ int nwc_linear_bf16_splits(void *stream, const uint8_t *data, const uint32_t *ba
                            int elem, uint32_t splits);
 
 /* Status word of the kernels' bounded waits: 0, 2 when a warp gave up waiting for a bulk copy (its rows are then
-   missing from y), 3 when a kernel gave up waiting for a peer rank (nwc_allreduce_add_rmsnorm, nwc_linear_fused_tp,
+   missing from y), 3 when a kernel gave up waiting for a peer rank (nwc_allreduce_add_rmsnorm, nwc_linear_fused_opt,
    nwc_argmax_tp).  Synchronises the device;
    clear != 0 resets the word. */
 int nwc_kernel_status(int clear);
@@ -158,8 +158,10 @@ int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, c
                      const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
                      uint32_t K, int elem);
 
-/* nwc_linear_fused on a tensor-parallel group of one node ("push" protocol; buffers as for nwc_allreduce_add_rmsnorm:
-   a host array of `world` exchange buffers, this rank's own at [rank]).
+/* nwc_linear_fused with options (opt == NULL is nwc_linear_fused).
+
+   Tensor-parallel group of one node ("push" protocol; `buffers` as for nwc_allreduce_add_rmsnorm: a host array of `world`
+   exchange buffers, this rank's own at [rank]; buffers == NULL: no group):
      out_slot >= 0  (row-parallel matrices: o, down) y is not written; the kernel stores its bf16 result into push slot
                     out_slot (0 or 1, used in turn) of EVERY rank's buffer with plain stores over NVLink, and its last CTA
                     raises this rank's flag in every buffer after a system-scope fence.  M <= H, no bias / scale.
@@ -168,19 +170,33 @@ int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, c
                     buffer, adds the `world` partials in rank order in fp32 (every rank gets the same bits), and continues
                     as mode 1 with that sum as delta.  After a timeout nwc_kernel_status() reports 3 and y is NaN.
    So the sum over the ranks costs no kernel of its own and one NVLink trip.  Only matrices that run on the layout-2 bf16
-   ring kernel are covered (-2 otherwise: use nwc_allreduce_add_rmsnorm).  All ranks must make the same sequence of calls;
-   calls on one device must be in stream order.  tp == NULL is nwc_linear_fused. */
+   ring kernel are covered (-2 otherwise: use nwc_allreduce_add_rmsnorm).  All ranks must make the same sequence of calls.
+
+   side != NULL  (layout 0, matrices that take the single-launch small-matrix kernel) the table nwc_build_side_table made
+                 for this matrix: four warps then decode each block in parallel, one row pair each.
+
+   Calls on one device must be in stream order (the kernels share per-device arrival counters). */
 typedef struct {
     void *const *buffers;
     int rank, world;
     int in_slot, out_slot;      /* -1: unused */
     uint32_t H;                 /* hidden size the buffers were allocated for */
-} nwc_tp_io;
-int nwc_linear_fused_tp(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
-                        const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta,
-                        uint16_t *h_out, const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp,
-                        const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
-                        uint32_t K, int elem, const nwc_tp_io *tp);
+    const uint16_t *side;
+} nwc_fused_options;
+int nwc_linear_fused_opt(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                         const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta,
+                         uint16_t *h_out, const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp,
+                         const uint16_t *bias, const float *scale, float *scratch, uint16_t *y, uint64_t n, uint32_t block,
+                         uint32_t K, int elem, const nwc_fused_options *opt);
+
+/* Layout 0 side table (no counterpart in the reference; built when a matrix is loaded, never stored in checkpoints): for
+   every block and lane the bit positions inside the lane's stream at which rows 2, 4 and 6 of the block begin - uint16
+   side[blocks][3][32], nwc_side_table_bytes(M, K) bytes of device memory.  It lets several warps decode one block in
+   parallel instead of one warp walking each 128-symbol stream from its first bit.  Returns 0, -1 for a bad shape or a
+   layout other than 0, or a CUDA error. */
+uint64_t nwc_side_table_bytes(uint64_t M, uint32_t K);
+int nwc_build_side_table(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, uint16_t *side,
+                         uint64_t n, uint32_t block, uint32_t K, int elem);
 
 /* Longest time a kernel waits for the other ranks of a tensor-parallel group (fused prologue, sharded argmax) before it
    gives up with status 3; default 2000 ms. */

@@ -44,8 +44,10 @@ _SIGNATURES = {
     "nwc_swiglu": (I, [P, P, U32, P, P]),
     "nwc_argmax": (I, [P, P, U32, P, P, P, P, U32, U32]),
     "nwc_argmax_tp": (I, [P, P, U32, P, P, P, P, U32, U32, P, I, I]),
-    "nwc_linear_fused_tp": (I, [P, P, P, P, P, P, I, P, P, P, P, P, ctypes.c_float, P, P, P, P, P, P, U64, U32, U32, I, P]),
+    "nwc_linear_fused_opt": (I, [P, P, P, P, P, P, I, P, P, P, P, P, ctypes.c_float, P, P, P, P, P, P, U64, U32, U32, I, P]),
     "nwc_comm_set_timeout_ms": (None, [U32]),
+    "nwc_side_table_bytes": (U64, [U64, U32]),
+    "nwc_build_side_table": (I, [P, P, P, P, P, U64, U32, U32, I]),
     "nwc_linear_bf16_static": (I, [P, P, P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_matvec": (I, [P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_dequant": (I, [P, P, P, P, P, P, P, U64, U32, U32, I]),
@@ -70,11 +72,11 @@ for _name, (_res, _args) in _SIGNATURES.items():
 
 
 
-class TpIo(ctypes.Structure):
-    """nwc_tp_io of include/nwc_ops.h: the exchange buffers of a tensor-parallel group and the push slots one
-    nwc_linear_fused_tp call reads (in_slot) and writes (out_slot); -1 = unused."""
+class FusedOptions(ctypes.Structure):
+    """nwc_fused_options of include/nwc_ops.h: the exchange buffers of a tensor-parallel group with the push slots one
+    nwc_linear_fused_opt call reads (in_slot) and writes (out_slot), -1 = unused; and a layout-0 matrix's side table."""
     _fields_ = [("buffers", ctypes.c_void_p), ("rank", ctypes.c_int), ("world", ctypes.c_int), ("in_slot", ctypes.c_int),
-                ("out_slot", ctypes.c_int), ("H", ctypes.c_uint32)]
+                ("out_slot", ctypes.c_int), ("H", ctypes.c_uint32), ("side", ctypes.c_void_p)]
 
 
 VERSION = lib.nwc_info(0)

@@ -40,10 +40,10 @@ class PeerBuffers:
         dist.barrier(group=group)                                   # every buffer is zeroed and open before the first kernel
 
     def io(self, in_slot: int = -1, out_slot: int = -1):
-        """nwc_tp_io argument of nwc_linear_fused_tp (kept alive by this object: the library reads it at launch time)."""
+        """nwc_fused_options argument of nwc_linear_fused_opt (kept alive by this object: the library reads it at launch time)."""
         key = (in_slot, out_slot)
         if key not in self._io:
-            self._io[key] = L.TpIo(ctypes.cast(self.table, ctypes.c_void_p), self.rank, self.world, in_slot, out_slot, self.hidden)
+            self._io[key] = L.FusedOptions(ctypes.cast(self.table, ctypes.c_void_p), self.rank, self.world, in_slot, out_slot, self.hidden)
         return ctypes.byref(self._io[key])
 
     def slot(self, i: int) -> ctypes.c_void_p:

@@ -108,7 +108,7 @@ unsigned long long g_peer_timeout_ns = 2000000000ull;
 static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                         const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
                         const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
-                        float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, const nwc_tp_io *tp) {
+                        float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, const nwc_fused_options *tp) {
     if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1 || mode < 0 || mode > 2) return -1;
     if (!aligned16(data) || !aligned16(low) || !aligned16(lut)) return -1;
     if (mode == kInputNorm && (!h_in || !norm_w || h_out == h_in)) return -1;
@@ -119,11 +119,12 @@ static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases
     if (!sms) return (int)cudaErrorNoDevice;
     const uint32_t M = (uint32_t)(n / K);
     const Geometry g(M, K, layout_of(elem));
-    const bool peer_in = tp && tp->in_slot >= 0, peer_out = tp && tp->out_slot >= 0;
+    const bool peer_in = tp && tp->buffers && tp->in_slot >= 0, peer_out = tp && tp->buffers && tp->out_slot >= 0;
+    const uint16_t *side = tp && layout_of(elem) == 0 ? tp->side : nullptr;
     PeerOutput push{};
     int in_mode = mode;
     if (peer_in || peer_out) {
-        if (!tp->buffers || tp->world < 1 || tp->world > (int)kCommMaxRanks || tp->rank < 0 || tp->rank >= tp->world || !tp->H || (tp->H & 7u)) return -1;
+        if (tp->world < 1 || tp->world > (int)kCommMaxRanks || tp->rank < 0 || tp->rank >= tp->world || !tp->H || (tp->H & 7u)) return -1;
         for (int r = 0; r < tp->world; r++) if (!tp->buffers[r]) return -1;
         if (peer_in && (mode != kInputNorm || K != tp->H || tp->in_slot > 1 || delta)) return -1;
         if (peer_out && (M > tp->H || tp->out_slot > 1 || bias || scale)) return -1;
@@ -139,7 +140,7 @@ static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases
     if (peer_in) { in.comm = static_cast<const uint8_t *>(tp->buffers[tp->rank]); in.world = (uint32_t)tp->world; in.slot = (uint32_t)tp->in_slot; }
     if (!peer_in && !peer_out && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) {
         SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
-        return (int)launch_small_layout0(elem, sms, (cudaStream_t)stream, a, in);
+        return (int)launch_small_layout0(elem, sms, (cudaStream_t)stream, a, in, side);
     }
     if (token_path_fuses_input(elem, M, K, in_mode)) {              /* the ring kernel builds x itself (a plain x too) */
         SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
@@ -164,11 +165,23 @@ NWC_EXPORT int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_
     return linear_fused(stream, data, bases, hdr, lut, low, mode, x, h_in, delta, h_out, norm_w, eps, gate_up, xtmp, bias, scale, scratch, y, n, block, K, elem, nullptr);
 }
 
-NWC_EXPORT int nwc_linear_fused_tp(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+NWC_EXPORT int nwc_linear_fused_opt(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                                    const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta, uint16_t *h_out,
                                    const uint16_t *norm_w, float eps, const uint16_t *gate_up, uint16_t *xtmp, const uint16_t *bias, const float *scale,
-                                   float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, const nwc_tp_io *tp) {
+                                   float *scratch, uint16_t *y, uint64_t n, uint32_t block, uint32_t K, int elem, const nwc_fused_options *tp) {
     return linear_fused(stream, data, bases, hdr, lut, low, mode, x, h_in, delta, h_out, norm_w, eps, gate_up, xtmp, bias, scale, scratch, y, n, block, K, elem, tp);
+}
+
+NWC_EXPORT uint64_t nwc_side_table_bytes(uint64_t M, uint32_t K) {
+    if (!M || !K || M > 0xFFFFFFFFull) return 0;
+    return (uint64_t)Geometry((uint32_t)M, K, 0).nb * 192u;
+}
+
+NWC_EXPORT int nwc_build_side_table(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, uint16_t *side, uint64_t n, uint32_t block,
+                                    uint32_t K, int elem) {
+    if (!shape_ok(n, block, K) || layout_of(elem) != 0 || type_of(elem) > 1 || !side) return -1;
+    if (!device_sms()) return (int)cudaErrorNoDevice;
+    return (int)launch_side_table(elem, (cudaStream_t)stream, data, bases, hdr, side, Geometry((uint32_t)(n / K), K, 0).nb);
 }
 
 NWC_EXPORT void nwc_comm_set_timeout_ms(uint32_t ms) { g_peer_timeout_ns = (unsigned long long)(ms ? ms : 1u) * 1000000ull; }

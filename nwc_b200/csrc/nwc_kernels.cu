@@ -1240,6 +1240,183 @@ __global__ void __launch_bounds__(kSmallThreads, NWC_SMALL_RESIDENT) small_kerne
     }
 }
 
+/* ---- layout 0, small matrices, four warps per block --------------------------------------------------------------- */
+/* A lane's stream of a layout-0 block is 128 symbols that only one lane can walk from bit 0: 32 dependent four-symbol
+   steps, about 5 us, whatever the GPU.  The side table breaks that chain: for every block and lane it holds the bit
+   position at which rows 2, 4 and 6 begin (3 x 32 x 2 bytes per block; built once when a matrix is loaded, never stored in
+   checkpoints).  A TEAM of four warps then decodes one block, warp r the row pair (2r, 2r + 1): eight dependent steps
+   instead of 32.  A CTA is two teams; the teams of a CTA split the column blocks of the row group(s) they own and add up
+   through shared memory; the block's stream is copied once per team (double-buffered bulk copies, one mbarrier per stage,
+   a 128-thread named barrier frees a stage for its next copy). */
+constexpr uint32_t kSplitThreads = 256, kSplitTeams = 2, kSplitTeamWarps = 4;
+constexpr uint32_t kSideBytesPerBlock = 3u * kLanes * 2u;
+
+/* one thread per lane stream: walk 96 symbols with the code's length rule (r zeros, a one, the sign: r + 2 bits; bf16
+   ranks beyond 14: 24 bits) and record the bit positions after 32, 64 and 96 symbols */
+template <int ELEM>
+__global__ void side_table_kernel(const uint8_t *__restrict__ data, const uint32_t *__restrict__ bases, const uint8_t *__restrict__ hdr, uint16_t *__restrict__ side, uint32_t nb) {
+    constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
+    const uint32_t lane = threadIdx.x & 31u, b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= nb) return;
+    uint32_t total;
+    const uint32_t words = __ldg(hdr + (uint64_t)b * kLanes + lane), before = warp_exclusive_sum(words, lane, total);
+    const uint32_t *stream = reinterpret_cast<const uint32_t *>(data + __ldg(bases + b)) + before;
+    uint32_t pos = 0;
+    for (uint32_t part = 0; part < 3u; part++) {
+        for (uint32_t i = 0; i < 32u; i++) {
+            const uint32_t w = pos >> 5, v = __funnelshift_l(__ldg(stream + w + 1u), __ldg(stream + w), pos & 31u);
+            const uint32_t zeros = min((uint32_t)__clz((int)v), 15u);
+            pos += (ELEM == kFp8 || zeros < MR) ? zeros + 2u : 24u;
+        }
+        side[((uint64_t)b * 3u + part) * kLanes + lane] = (uint16_t)pos;
+    }
+}
+
+/* rows (2 rp, 2 rp + 1) of one block for this warp: returns the quad partial sums through `stash` (16 floats), lane 0 / 1 then
+   hold the sums of the even / odd row over the block's 512 columns */
+template <class WIN, int ELEM>
+__device__ __forceinline__ float split_row_pair(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t rp, uint32_t lane,
+                                                uint32_t table, uint32_t sym, uint32_t four, float *stash, uint32_t xs) {
+    const uint32_t r = lane >> 2, q = lane & 3u, row0 = rb * 8u + 2u * rp, col0 = cb * kBlockCols + lane * 16u;
+    const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16;
+    const bool col_ok = col0 < g.K16, diag = q == (r >> 1);
+    XFrag8<false> xa, xb;
+    if (!col_ok) { xa.zero(); xb.zero(); } else { xa.load_shared(xs + col0 * 2u); xb.load_shared(xs + col0 * 2u + 16u); }
+    const uint8_t *rawp = a.low + (uint64_t)row0 * stride + (ELEM == kFp8 ? (col0 >> 1) : col0);
+    const uint4 rawA = raw_row16<ELEM>(rawp, col_ok && row0 < g.M), rawB = raw_row16<ELEM>(rawp + stride, col_ok && row0 + 1u < g.M);
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t wa[4] = {rawA.x, rawA.y, rawA.z, rawA.w}, wb[4] = {rawB.x, rawB.y, rawB.z, rawB.w};
+    uint32_t even0[4], even1[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        uint32_t e01, e23; W.quad(table, sym, four, e01, e23);
+        even0[k] = weave<0>(wa[k], e01); even1[k] = weave<2>(wa[k], e23);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        uint32_t e01, e23; W.quad(table, sym, four, e01, e23);
+        const XFrag8<false> &xf = k < 2 ? xa : xb;
+        const int w = 2 * (k & 1);
+        mma_bf16(d, even0[k], weave<0>(wb[k], e01), even1[k], weave<2>(wb[k], e23), xf.head[w], xf.head[w + 1]);
+    }
+    if (diag) { stash[r] = (r & 1u) ? d[1] : d[0]; stash[8u + r] = (r & 1u) ? d[3] : d[2]; }
+    __syncwarp();
+    float sum = 0.f;
+    if (lane < 2u) {
+        const float4 s0 = *reinterpret_cast<const float4 *>(stash + lane * 8u), s1 = *reinterpret_cast<const float4 *>(stash + lane * 8u + 4u);
+        sum = ((s0.x + s0.y) + (s0.z + s0.w)) + ((s1.x + s1.y) + (s1.z + s1.w));
+    }
+    __syncwarp();
+    return sum;
+}
+
+template <int ELEM>
+__global__ void __launch_bounds__(kSplitThreads, 3) small_split_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four, const uint16_t *__restrict__ side) {
+    constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
+    extern __shared__ __align__(128) uint8_t small_smem[];
+    uint32_t *tables = reinterpret_cast<uint32_t *>(small_smem);
+    float *stash_all = reinterpret_cast<float *>(small_smem + 16416u);                 /* [8 warps][16] */
+    float *red = stash_all + 8u * 16u;                                                  /* [2 teams][8 rows] */
+    float *scal = red + kSplitTeams * 8u;                                               /* [8] block reduction scratch */
+    uint8_t *stage_all = reinterpret_cast<uint8_t *>(scal + 8u);                        /* [2 teams][2][kPrefixStageBytes] */
+    uint64_t *bar_all = reinterpret_cast<uint64_t *>(stage_all + kSplitTeams * 2u * kPrefixStageBytes);
+    uint16_t *xs = reinterpret_cast<uint16_t *>(bar_all + 2u * kSplitTeams);            /* [K16] activation vector */
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const uint32_t team = warp >> 2, rp = warp & 3u;                                    /* this warp's team and row pair */
+    const Geometry g(a.M, a.K, 0);
+    uint16_t *nw = xs + g.K16;
+    const uint32_t stage0 = smem_addr(stage_all) + team * 2u * kPrefixStageBytes, bar0 = smem_addr(bar_all) + team * 16u;
+    if (rp == 0u && lane == 0) { mbar_init(bar0, 1u); mbar_init(bar0 + 8u, 1u); mbar_init_fence(); }
+    /* teams per row group: both teams share a row group with several column blocks, else each takes its own row group */
+    const uint32_t share = g.CB > 1u ? kSplitTeams : 1u, per_pass = kSplitTeams / share;
+    const uint32_t my_group = team / share, j = team - my_group * share, passes = (g.groups + per_pass - 1u) / per_pass;
+    /* the team's blocks in decode order; (pass, cb) -> next valid one */
+    auto settle = [&](uint32_t &pass, uint32_t &cb) -> bool {
+        while (pass < passes) {
+            if (pass * per_pass + my_group < g.groups && cb < g.CB) return true;
+            pass += gridDim.x; cb = j;
+        }
+        return false;
+    };
+    struct Ahead { uint32_t pass, cb, b, words, start, bytes; bool valid; } next;
+    /* metadata of the team's block after (pass, cb) and, by the team's first lane, the bulk copy of its stream into stage
+       `which`; every warp of the team runs this with the same arguments */
+    auto prefetch_block = [&](uint32_t pass, uint32_t cb, uint32_t which) {
+        next.pass = pass; next.cb = cb; next.valid = settle(next.pass, next.cb);
+        if (!next.valid) return;
+        const uint32_t rb = next.pass * per_pass + my_group;
+        next.b = rb * g.CB + next.cb;
+        next.words = __ldg(a.hdr + (uint64_t)next.b * kLanes + lane);
+        const uint32_t base = __ldg(a.bases + next.b);
+        uint32_t len;
+        if (next.b + 1u < g.nb) len = __ldg(a.bases + next.b + 1u) - base;
+        else { uint32_t t; warp_exclusive_sum(next.words, lane, t); len = 4u * t; }
+        next.start = base & ~15u;
+        next.bytes = (base + len + 16u - next.start + 15u) & ~15u;
+        if (next.bytes > kPrefixStageBytes) next.bytes = 0u;
+        if (next.bytes && rp == 0u && lane == 0) {
+            async_proxy_fence(); mbar_expect(bar0 + 8u * which, next.bytes);
+            bulk_load(stage0 + which * kPrefixStageBytes, a.data + next.start, next.bytes, bar0 + 8u * which);
+        }
+        const uint32_t stride = ELEM == kFp8 ? (g.K16 >> 1) : g.K16, row = rb * 8u + 2u * rp + (lane >> 4), off = next.cb * (ELEM == kFp8 ? 256u : 512u) + (lane & 15u) * 32u;
+        if (row < g.M && off < stride) prefetch_l2(a.low + (uint64_t)row * stride + off);
+    };
+    __syncthreads();                                                                     /* barriers initialised before anyone arms them */
+    prefetch_block(blockIdx.x, j, 0u);
+    stage_tables(tables, a.lut, tid, kSplitThreads);
+    stage_norm_weight<kSplitThreads>(in, a.K, nw);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    build_activation<kSplitThreads>(in, a.x, a.K, g.K16, xs, nw, scal);
+    const uint32_t xs_addr = smem_addr(xs), table = smem_addr(tables), sym = table + 4u * kTableWords;
+    float *stash = stash_all + warp * 16u;
+    uint32_t phases = 0, which = 0;
+    for (uint32_t pass = blockIdx.x; pass < passes; pass += gridDim.x) {
+        const uint32_t rb = pass * per_pass + my_group;
+        float row_sum = 0.f;                                     /* lanes 0, 1: rows rb * 8 + 2 rp + lane */
+        if (rb < g.groups) {
+            for (uint32_t cb = j; cb < g.CB; cb += share) {
+                const Ahead cur = next;
+                /* the other stage held the block before this one: every warp of the team must be done with it */
+                asm volatile("bar.sync %0, %1;" ::"r"(1u + team), "r"(kSplitTeamWarps * 32u) : "memory");
+                prefetch_block(pass, cb + share, which ^ 1u);
+                uint32_t total;
+                const uint32_t before = warp_exclusive_sum(cur.words, lane, total), base = __ldg(a.bases + cur.b);
+                /* where this lane's row pair starts inside its stream */
+                const uint32_t bit = rp ? (uint32_t)__ldg(side + ((uint64_t)cur.b * 3u + (rp - 1u)) * kLanes + lane) : 0u;
+                if (cur.bytes) {
+                    const bool landed = mbar_wait(bar0 + 8u * which, (phases >> which) & 1u);
+                    phases ^= 1u << which;
+                    if (landed) {
+                        SmemWindow<MR> W; W.open(stage0 + which * kPrefixStageBytes + (base - cur.start) + 4u * (before + (bit >> 5)));
+                        W.consume(bit & 31u);
+                        row_sum += split_row_pair<SmemWindow<MR>, ELEM>(W, a, g, rb, cb, rp, lane, table, sym, four, stash, xs_addr);
+                    }
+                } else {
+                    GlobalWindow<MR> W; W.sym_ptr = reinterpret_cast<const uint8_t *>(tables + kTableWords);
+                    W.open(reinterpret_cast<const uint32_t *>(a.data + base) + before + (bit >> 5));
+                    W.consume(bit & 31u);
+                    row_sum += split_row_pair<GlobalWindow<MR>, ELEM>(W, a, g, rb, cb, rp, lane, table, sym, four, stash, xs_addr);
+                }
+                which ^= 1u;
+            }
+        }
+        if (lane < 2u) red[team * 8u + 2u * rp + lane] = row_sum;
+        __syncthreads();
+        if (j == 0u && rp == 0u && lane < 8u && rb < g.groups) {
+            float v = 0.f;
+            for (uint32_t k = 0; k < share; k++) v += red[(team + k) * 8u + lane];
+            const uint32_t row = rb * 8u + lane;
+            if (row < a.M) {
+                if (a.scale) v *= __ldg(a.scale + row);
+                if (a.bias) v += bf16_to_float(__ldg(a.bias + row));
+                a.y[row] = bf16_round(v);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 /* ---- the persistent segment kernel -------------------------------------------------------------------------------- */
 template <int LAYOUT, int ELEM, int MODE, bool XF32>
 __global__ void __launch_bounds__(kSegmentThreads, 1) segment_kernel(const SegmentArgs a) {
@@ -1310,12 +1487,20 @@ static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 bloc
 }
 
 constexpr uint32_t kSmallFixedSmem = 16416u + kSmallWarps * 64u * 4u + kSmallWarps * 8u * 4u + 32u + kSmallWarps * 2u * kPrefixStageBytes + kSmallWarps * 16u;
-cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in) {
+constexpr uint32_t kSplitFixedSmem = 16416u + 8u * 16u * 4u + kSplitTeams * 8u * 4u + 32u + kSplitTeams * 2u * kPrefixStageBytes + kSplitTeams * 16u;
+cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in, const uint16_t *side) {
     const Geometry g(a.M, a.K, 0);
+    if (side) {                                                   /* four warps per block along the side table */
+        const uint32_t share = g.CB > 1u ? kSplitTeams : 1u, passes = (g.groups + kSplitTeams / share - 1u) / (kSplitTeams / share);
+        const uint32_t grid = passes < 6u * (uint32_t)sms ? passes : 6u * (uint32_t)sms;
+        const size_t smem = kSplitFixedSmem + (size_t)g.K16 * (norm_like(in.mode) ? 4u : 2u);
+        if (type_of(code) == kFp8) return launch_kernel(small_split_kernel_layout0<kFp8>, dim3(grid), dim3(kSplitThreads), smem, st, a, in, 4u, side);
+        return launch_kernel(small_split_kernel_layout0<kBf16>, dim3(grid), dim3(kSplitThreads), smem, st, a, in, 4u, side);
+    }
     const uint32_t wg = small_group_warps(g.CB), per_pass = kSmallWarps / wg;
     const uint32_t passes = (g.groups + per_pass - 1u) / per_pass;
     const uint32_t grid = passes < 4u * (uint32_t)sms ? passes : 4u * (uint32_t)sms;
-    const size_t smem = kSmallFixedSmem + (size_t)g.K16 * (in.mode == kInputNorm ? 4u : 2u);
+    const size_t smem = kSmallFixedSmem + (size_t)g.K16 * (norm_like(in.mode) ? 4u : 2u);
     if (type_of(code) == kFp8) return launch_kernel(small_kernel_layout0<kFp8>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
     return launch_kernel(small_kernel_layout0<kBf16>, dim3(grid), dim3(kSmallThreads), smem, st, a, in, 4u);
 }
@@ -1443,7 +1628,16 @@ static ClusterRoom cluster_room(int sms) {
     return cache[dev];
 }
 
+cudaError_t launch_side_table(int code, cudaStream_t st, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, uint16_t *side, uint32_t nb) {
+    const unsigned grid = (nb + 3u) / 4u;
+    if (type_of(code) == kFp8) side_table_kernel<kFp8><<<grid, 128, 0, st>>>(data, bases, hdr, side, nb);
+    else side_table_kernel<kBf16><<<grid, 128, 0, st>>>(data, bases, hdr, side, nb);
+    return cudaGetLastError();
+}
+
 void configure_segment_kernels() {
+    cudaFuncSetAttribute(small_split_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(small_split_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);

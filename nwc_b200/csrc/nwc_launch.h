@@ -48,7 +48,9 @@ struct FusedInput {
     uint32_t world, slot;
     unsigned long long timeout_ns;   /* longest wait for the peers' flags */
 };
-cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in);
+/* side: per block and lane the bit positions where rows 2, 4, 6 begin (launch_side_table), or null */
+cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in, const uint16_t *side = nullptr);
+cudaError_t launch_side_table(int code, cudaStream_t st, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, uint16_t *side, uint32_t nb);
 void set_dependent_launch(bool on);           /* programmatic dependent launch for the decode-step launches */
 bool dependent_launch();
 

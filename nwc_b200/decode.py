@@ -164,7 +164,7 @@ class DecoderWeights:
     def bytes_per_token(self):
         """Compressed bytes one decode step streams: every matvec matrix once (the embedding lookup reads one row)."""
         ws = [self.lm_head] + [l[k] for l in self.layers for k in ("qkv", "o", "gate_up", "down")]
-        return sum(w.bytes for w in ws)
+        return sum(w.bytes + w.side_bytes for w in ws)
 
 
 def rope_tables(cfg, max_len, device):
@@ -176,7 +176,7 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push"):
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push", side_tables=True):
         """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None.
         tp_reduce, how the ranks' partial o / down outputs are summed:
           "push"  the row-parallel matvec stores its partial into every rank's exchange buffer over NVLink and the next
@@ -196,6 +196,11 @@ class DecodeEngine:
             from .comm import PeerBuffers
             self.peers = PeerBuffers(tp_group, weights.cfg.hidden)
         self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
+        self._opts = {}
+        if side_tables:     # layout-0 matrices small enough for the single-launch kernel: four warps per block along a side table
+            for m in weights.matrices():
+                blocks = -(-m.out_features // 8) * -(-m.in_features // 512)
+                if m.layout == 0 and blocks <= 2 * L.SM_COUNT * 32 and m.K16 <= 40960: m.build_side_table()
         c = self.cfg
         bf = lambda n: torch.zeros(n, dtype=torch.bfloat16, device=device)
         pad32 = lambda n: (n + 31) // 32 * 32
@@ -237,12 +242,25 @@ class DecodeEngine:
         2: x = SwiGLU(gate_up)), through nwc_linear_fused.  tp_in / tp_out: push slots of the tensor-parallel exchange
         (delta = the ranks' summed partials of slot tp_in; y pushed to every rank's slot tp_out instead of written)."""
         out = y if isinstance(y, ctypes.c_void_p) else L.ptr(y)      # a raw device pointer: this rank's slot of the exchange buffer
-        tp = self.peers.io(tp_in, tp_out) if (tp_in >= 0 or tp_out >= 0) else None
-        err = L.lib.nwc_linear_fused_tp(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
+        tp = self._options(w, tp_in, tp_out)
+        err = L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
                                         L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), self.cfg.eps, L.ptr(gate_up), L.ptr(self.xtmp), None, L.ptr(w.scale),
                                         L.ptr(w.scratch), out, w.n, w.block, w.in_features, w.code, tp)
         if err: raise RuntimeError(f"nwc_linear_fused error {err}")
         self._count += L.lib.nwc_linear_launches(w.n, w.in_features, w.code, mode)
+
+    def _options(self, w, tp_in, tp_out):
+        """nwc_fused_options of one call (kept alive by the engine: the library reads them at launch time), or None."""
+        if w.side is None and tp_in < 0 and tp_out < 0: return None
+        key = (id(w), tp_in, tp_out)
+        if key not in self._opts:
+            side = None if w.side is None else w.side.data_ptr()
+            if tp_in >= 0 or tp_out >= 0:
+                p = self.peers
+                self._opts[key] = L.FusedOptions(ctypes.cast(p.table, ctypes.c_void_p), p.rank, p.world, tp_in, tp_out, p.hidden, side)
+            else:
+                self._opts[key] = L.FusedOptions(None, 0, 0, -1, -1, 0, side)
+        return ctypes.byref(self._opts[key])
 
     def _argmax(self, c, st):
         """Greedy token from this rank's logits; with exchange buffers the ranks swap one (value, index) word each."""

@@ -116,6 +116,20 @@ class NWCWeight:
         self.bytes_bf16 = 2 * self.n
         self.bytes_native = self.n + 4 * self.out_features if self.elem == ELEM_FP8 else 2 * self.n
         self.scratch = torch.empty(sizes.scratch_floats, dtype=torch.float32, device=device)
+        self.side, self.side_bytes = None, 0
+
+    def build_side_table(self):
+        """Layout 0: the engine-private table of per-lane bit positions at which rows 2, 4 and 6 of every block begin
+        (nwc_build_side_table), so that four warps can decode a block in parallel.  Never stored in checkpoints; its bytes
+        are read by every token matvec that uses it and are counted in `side_bytes`."""
+        if self.layout != 0: raise ValueError("side tables exist for layout 0 only")
+        if getattr(self, "side", None) is None:
+            nbytes = L.lib.nwc_side_table_bytes(self.out_features, self.in_features)
+            side = torch.empty(nbytes // 2, dtype=torch.int16, device=self.data.device)
+            err = L.lib.nwc_build_side_table(L.stream(), L.ptr(self.data), L.ptr(self.bases), L.ptr(self.hdr), L.ptr(side), *self._shape_args())
+            if err: raise RuntimeError(f"nwc_build_side_table error {err}")
+            self.side, self.side_bytes = side, nbytes
+        return self.side
 
     @property
     def code(self):

@@ -96,13 +96,13 @@ def test_two_local_ranks_add_in_rank_order_and_missing_peer_times_out():
 def _tp_linear(L, nw, mode, tp, x=None, h_in=None, h_out=None, norm_w=None, gate_up=None, y=None, K=None):
     pad = (nw.in_features + 31) // 32 * 32
     xtmp = torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
-    return L.lib.nwc_linear_fused_tp(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), mode, L.ptr(x), L.ptr(h_in), None,
+    return L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), mode, L.ptr(x), L.ptr(h_in), None,
                                      L.ptr(h_out), L.ptr(norm_w), 1e-6, L.ptr(gate_up), L.ptr(xtmp), None, None, L.ptr(nw.scratch), L.ptr(y), nw.n, nw.block,
                                      nw.in_features, nw.code, tp)
 
 
 def _io(L, table, rank, world, in_slot, out_slot, H):
-    io = L.TpIo(ctypes.cast(table, ctypes.c_void_p), rank, world, in_slot, out_slot, H)
+    io = L.FusedOptions(ctypes.cast(table, ctypes.c_void_p), rank, world, in_slot, out_slot, H)
     return io, ctypes.byref(io)
 
 

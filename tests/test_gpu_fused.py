@@ -65,3 +65,78 @@ def test_fused_modes_match_separate_kernels(M, K, layout, elem):
     want0 = O.bf16_to_f32(O.linear_bf16(p, O.bf16_to_f32(bits(x0[:K]))))
     assert rel_l2(O.bf16_to_f32(bits(fused(0, x=x0))), want0) <= 2e-3
     assert L.lib.nwc_kernel_status(1) == 0
+
+
+# ---- layout 0 with a side table: four warps per block ----
+
+def _python_side_table(p):
+    """Bit positions after 32, 64 and 96 symbols of every lane stream, walked with the code's length rule on the CPU."""
+    M, K = p.M, p.K
+    groups, CB = -(-M // 8), -(-K // 512)
+    max_rank = 10 if p.elem else 15
+    out = np.zeros((groups * CB, 3, 32), np.uint16)
+    hdr = p.hdr.reshape(-1, 32).astype(np.int64)
+    for b in range(groups * CB):
+        words = np.frombuffer(p.data.tobytes()[int(p.bases[b]): int(p.bases[b]) + 4 * int(hdr[b].sum()) + 16], dtype="<u4")
+        start = 0
+        for lane in range(32):
+            bits = "".join(format(int(w), "032b") for w in words[start: start + int(hdr[b, lane]) + 2])
+            pos = 0
+            for part in range(3):
+                for _ in range(32):
+                    zeros = 0
+                    while zeros < 15 and bits[pos + zeros] == "0": zeros += 1
+                    pos += zeros + 2 if (p.elem or zeros < max_rank) else 24
+                out[b, part, lane] = pos
+            start += int(hdr[b, lane])
+    return out
+
+
+@pytest.mark.parametrize("M,K,elem", [(13, 40, 0), (100, 1000, 0), (64, 2048, 0), (100, 1000, 1), (1024, 3072, 0)])
+def test_side_table_matches_a_python_walk_of_the_streams(M, K, elem):
+    from gpu_helpers import make_case, to_weight
+    p, _, _ = make_case(M, K, elem, 0, seed=M + K, escapes=True)
+    nw = to_weight(p)
+    side = nw.build_side_table().cpu().numpy().view(np.uint16).reshape(-1, 3, 32)
+    if M * K <= 200000: assert np.array_equal(side, _python_side_table(p))
+    assert (np.diff(side.astype(np.int64), axis=1) >= 64).all() and (side[:, 0] >= 64).all()      # 32 symbols of at least two bits each
+    assert nw.side_bytes == side.size * 2
+
+
+@pytest.mark.parametrize("M,K,elem", [(4096, 1024, 0), (1024, 2048, 0), (6144, 1024, 0), (1024, 3072, 0), (100, 1000, 0), (13, 40, 0), (8, 512, 0), (1024, 5120, 0),
+                                      (256, 1024, 1), (1001, 1000, 1)])
+def test_split_kernel_matches_the_single_warp_kernel_and_the_oracle(M, K, elem):
+    """nwc_linear_fused_opt with a side table (four warps per block) against the same call without one and the oracle, in
+    all three input modes; escapes planted so that lanes leave the fast path in the middle of a row pair."""
+    import ctypes
+    from gpu_helpers import bits, make_case, to_weight
+    from nwc_b200 import _lib as L
+    p, values, _ = make_case(M, K, elem, 0, seed=3 * M + K, escapes=True)
+    nw = to_weight(p)
+    nw.build_side_table()
+    g = torch.Generator().manual_seed(K)
+    pad = (K + 31) // 32 * 32
+    def vec(n, scale=1.0): return (torch.randn(n, generator=g) * scale).to(torch.bfloat16).cuda()
+    x0, h_in, delta, norm_w, gate_up = vec(pad), vec(pad), vec(pad, 0.5), (1.0 + 0.1 * torch.randn(pad, generator=g)).to(torch.bfloat16).cuda(), vec(2 * K)
+    x0[K:] = 0
+    xtmp = torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
+    opt = L.FusedOptions(None, 0, 0, -1, -1, 0, nw.side.data_ptr())
+
+    def run(mode, with_side):
+        y, h_out = torch.empty(M, dtype=torch.bfloat16, device="cuda"), torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
+        err = L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), mode, L.ptr(x0), L.ptr(h_in),
+                                         L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), 1e-6, L.ptr(gate_up), L.ptr(xtmp), None, L.ptr(nw.scale), L.ptr(nw.scratch),
+                                         L.ptr(y), nw.n, nw.block, K, nw.code, ctypes.byref(opt) if with_side else None)
+        assert err == 0, err
+        torch.cuda.synchronize()
+        return O.bf16_to_f32(bits(y)), h_out
+
+    for mode in (0, 1, 2):
+        a, ha = run(mode, True)
+        b, hb = run(mode, False)
+        assert np.isfinite(a).all() and rel_l2(a, b) <= 2e-3, (mode, rel_l2(a, b))
+        assert np.abs(a - b).max() <= 2.0 ** -7 * np.abs(b).max() + 1e-6, mode
+        assert torch.equal(ha, hb)
+    want = O.bf16_to_f32(O.linear_bf16(p, O.bf16_to_f32(bits(x0[:K]))))
+    assert rel_l2(run(0, True)[0], want) <= 2e-3
+    assert L.lib.nwc_kernel_status(1) == 0
