@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--prompt", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="", help="time one token matvec alone: lm_head | qkv | o | gate_up | down | MxK (small case for ncu)")
+    ap.add_argument("--op", default="", help="time one of the other kernels alone (small cases for ncu): gather:N | attention:POS | encode:MxK | prefill:MxKxT | native_fp8:MxK")
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
@@ -262,6 +263,94 @@ def kernel_only(a, cfg):
                       "note": "%d calls on %d rotating copies replayed as one CUDA graph, CUDA events around the replay (a call includes its finalize launch when it needs one)" % (reps, copies)}))
 
 
+def op_only(a, cfg):
+    """One of the kernels around the token matvec, timed alone with CUDA events (median of --steps runs after --warmup);
+    prints one JSON line.  Small cases, so that the same command can be captured under ncu."""
+    import torch
+    from nwc_b200 import NWCWeight, _lib as L
+    from nwc_b200.decode import synthetic_matrix
+    torch.cuda.set_device(0)
+    what, _, arg = a.op.partition(":")
+    peak, kind = measured_peak()
+
+    def timed(call, reps=1):
+        times = []
+        for i in range(a.warmup + a.steps):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(reps): call()
+            t1.record(); torch.cuda.synchronize()
+            if i >= a.warmup: times.append(t0.elapsed_time(t1) / reps)
+        return statistics.median(times) * 1e3                      # microseconds
+
+    out = {"op": a.op, "elem": a.elem, "layout": a.layout}
+    if what == "gather":            # compressed embedding lookup: N random rows of the model's table
+        n = int(arg or 512)
+        w = NWCWeight(synthetic_matrix(cfg.vocab, cfg.hidden, 1), layout=a.layout, elem="bf16")
+        ids = torch.randint(0, cfg.vocab, (n,), device="cuda")
+        us = timed(lambda: w.gather(ids))
+        out.update({"rows": n, "us": us, "kernel": "gather_kernel", "output_GBs": n * w.K16 * 2 / us / 1e3, "table_bits_per_weight": 8 * w.bytes / w.n})
+    elif what == "attention":       # one token of grouped-query attention over POS cached positions
+        pos = int(arg or 256)
+        c = cfg
+        bf = lambda *shape: torch.randn(*shape, device="cuda").to(torch.bfloat16)
+        qkv, k_cache, v_cache = bf(c.qkv_rows), bf(c.n_kv, pos + 8, c.head_dim), bf(c.n_kv, pos + 8, c.head_dim)
+        from nwc_b200.decode import rope_tables
+        cos, sin = rope_tables(c, pos + 8, "cuda")
+        norm = torch.ones(c.head_dim, dtype=torch.bfloat16, device="cuda") if c.qk_norm else None
+        p = torch.full((1,), pos, dtype=torch.int32, device="cuda"); status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        o = torch.empty(c.n_q * c.head_dim, dtype=torch.bfloat16, device="cuda")
+        def call():
+            err = L.lib.nwc_attention_decode(L.stream(), L.ptr(qkv), L.ptr(norm), L.ptr(norm), L.ptr(cos), L.ptr(sin), L.ptr(k_cache), L.ptr(v_cache), L.ptr(p), c.n_q, c.n_kv,
+                                             c.head_dim, pos + 8, c.eps, L.ptr(o), L.ptr(status))
+            if err: raise RuntimeError(f"nwc_attention_decode error {err}")
+        us = timed(call, reps=8)
+        cache_bytes = 2 * c.n_kv * pos * c.head_dim * 2
+        out.update({"positions": pos, "heads": [c.n_q, c.n_kv], "us": us, "kernel": "attention_decode_kernel", "cache_GBs": cache_bytes / us / 1e3})
+    elif what == "encode":          # GPU encoder on a matrix that already lives in HBM
+        M, K = (int(v) for v in (arg or "4096x4096").lower().split("x"))
+        w = synthetic_matrix(M, K, 1)
+        us = timed(lambda: NWCWeight(w, layout=a.layout, elem=a.elem))
+        out.update({"shape": [M, K], "us": us, "Mweights_per_s": M * K / us, "kernel": "measure_kernel / pack_kernel (whole NWCWeight construction, host table build and allocation included)"})
+        if a.vs_ref:                # the reference's own host encoder (one thread, as written) on the same matrix; bounded to 16 M weights
+            import numpy as np
+            import oracle as O
+            if O.ref_available():
+                rows = max(16, min(M, (16 << 20) // K) // 16 * 16)
+                bits = w[:rows].cpu().view(torch.int16).numpy().view(np.uint16)
+                src = O.quantize_fp8(bits)[0] if a.elem == "fp8" else bits
+                t = time.perf_counter(); O.ref_encode(src, O.code_of(1 if a.elem == "fp8" else 0, a.layout)); dt = time.perf_counter() - t
+                out["reference_host_encoder_Mweights_per_s"] = rows * K / dt / 1e6
+                out["reference_sample"] = f"first {rows} rows, 1 thread"
+    elif what == "prefill":         # T tokens at once: tile-wise decode into the tcgen05 GEMM against dequantise + dense matmul
+        M, K, T = (int(v) for v in (arg or "6144x2560x512").lower().split("x"))
+        w = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
+        x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+        dense_us = timed(lambda: torch.nn.functional.linear(x, w.dequant()))
+        out.update({"shape": [M, K, T], "dequant_plus_dense_matmul_us": dense_us, "dense_TFLOPs": 2 * M * K * T / dense_us / 1e6})
+        if w.linear_prefill(x) is not None:
+            us = timed(lambda: w.linear_prefill(x))
+            out.update({"us": us, "TFLOPs": 2 * M * K * T / us / 1e6, "kernel": "prefill_kernel_layout2"})
+    elif what == "native_fp8":      # the uncompressed fp8 weight-only matvec (bandwidth baseline of the fp8 configuration)
+        from nwc_b200.weight import quantize_fp8
+        M, K = (int(v) for v in (arg or "19456x2560").lower().split("x"))
+        n8 = max(1, min(16, -(-(320 << 20) // (M * K))))
+        q8 = [quantize_fp8(synthetic_matrix(M, K, 1 + i)) for i in range(n8)]
+        xf, y8 = torch.randn(K, device="cuda"), torch.empty(M, dtype=torch.bfloat16, device="cuda")
+        it = [0]
+        def call():
+            q, sc = q8[it[0] % n8]; it[0] += 1
+            err = L.lib.nwc_ref_fp8(L.stream(), L.ptr(q.view(torch.uint8)), L.ptr(sc), L.ptr(xf), L.ptr(y8), M, K)
+            if err: raise RuntimeError(f"nwc_ref_fp8 error {err}")
+        us = timed(call, reps=n8)
+        out.update({"shape": [M, K], "us": us, "kernel": "native_fp8_kernel", "roofline": {"bound": "hbm", "achieved": (M * K + 4 * M) / us / 1e3, "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                                                                                               "frac": (M * K + 4 * M) / us / 1e3 / peak}})
+    else:
+        raise SystemExit(f"unknown --op {a.op}")
+    if L.lib.nwc_kernel_status(1): raise RuntimeError("a bounded wait inside a kernel gave up")
+    print(json.dumps(out))
+
+
 def matvec_shares(eng, weights, cfg, reps_target=24):
     """Each of the five kinds of token matvec timed alone: the layers' own matrices of that kind back to back (plain x,
     mode 0) inside one CUDA graph, CUDA events around the replay.  Returns {kind: (us per launch, bytes per launch, launches
@@ -310,6 +399,9 @@ def main():
         return
     if a.kernel:
         if rank == 0: kernel_only(a, cfg)
+        return
+    if a.op:
+        if rank == 0: op_only(a, cfg)
         return
     import torch
     from nwc_b200.decode import DecodeEngine, DecoderWeights  # the package import fails loudly when the CUDA library is missing

@@ -126,8 +126,9 @@ int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, con
    GPU that loads the library carries it until the process exits.  The call allocates and frees nothing.
    Limit: padded rows x column blocks (the scratch size nwc_layout reports) must not exceed NWC_STATIC_SCRATCH_FLOATS,
    otherwise nothing is launched and NWC_ERR_STATIC_SCRATCH is returned.  Other return codes as nwc_linear_bf16.
-   The first call on each device looks up the area's device address; make that first call with the device current and
-   before any stream capture begins.  All calls on a device share the one area and it keeps whatever the last call
+   The area's device address is looked up once per device, when the device is prepared (nwc_setup, or the first call of
+   any entry point with that device current) - or, failing that, by the first call of this entry point on the device; so
+   call nwc_setup (or this entry point once) with the device current before any stream capture begins.  All calls on a device share the one area and it keeps whatever the last call
    left there: two calls whose kernels overlap on the GPU (different streams) race with each other, so keep calls on
    one device in stream order.  Nothing in the area needs clearing between calls. */
 #define NWC_STATIC_SCRATCH_FLOATS 1048576

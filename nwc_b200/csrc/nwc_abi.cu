@@ -26,6 +26,7 @@ int device_sms() {
     configure_segment_kernels();
     configure_model_kernels();
     configure_prefill_kernels();
+    prepare_static_scratch();
     g_sm_count[dev] = sms;
     return sms;
 }

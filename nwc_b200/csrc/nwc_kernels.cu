@@ -329,17 +329,87 @@ __device__ __forceinline__ bool wait_for_pushes(const FusedInput &in) {
     return ok;
 }
 
-/* before the dependency wait: the RMSNorm weight (a constant) goes to shared memory */
+/* two fp32 values -> bf16x2 (first value in the low half), round to nearest even in hardware */
+__device__ __forceinline__ uint32_t cvt_pair(float lo, float hi) { return pack_bf16x2(hi, lo); }
+
+/* RMSNorm weights of the chunks a thread owns, kept in registers across the dependency wait */
+constexpr uint32_t kNormRegChunks = 4;
+struct NormWeights { uint4 w[kNormRegChunks]; bool in_regs; };
+
+/* Before the dependency wait: the RMSNorm weight (a constant).  Vectors of up to kNormRegChunks * 8 * THREADS values stay in
+   the registers of the threads that will normalise those chunks (no shared-memory round trip, nothing to wait for before
+   griddepcontrol.wait returns); longer ones go to shared memory. */
 template <uint32_t THREADS>
-__device__ __forceinline__ void stage_norm_weight(const FusedInput &in, uint32_t K, uint16_t *nw) {
+__device__ __forceinline__ void stage_norm_weight(const FusedInput &in, uint32_t K, uint16_t *nw, NormWeights &nr) {
+    nr.in_regs = false;
     if (!norm_like(in.mode) || (K & 7u) != 0u) return;
+    const uint32_t live = K >> 3;
+    if (live <= kNormRegChunks * THREADS) {
+        nr.in_regs = true;
+#pragma unroll
+        for (uint32_t i = 0; i < kNormRegChunks; i++) {
+            const uint32_t c = threadIdx.x + i * THREADS;
+            nr.w[i] = c < live ? __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        return;
+    }
     const uint32_t nw_addr = smem_addr(nw);
-    for (uint32_t c = threadIdx.x; c < (K >> 3); c += THREADS) sts128(nw_addr + c * 16u, __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c));
+    for (uint32_t c = threadIdx.x; c < live; c += THREADS) sts128(nw_addr + c * 16u, __ldg(reinterpret_cast<const uint4 *>(in.norm_w) + c));
+}
+
+/* eight values of h_in + delta (delta = a local vector, or the sum of the ranks' pushed partials in rank order), rounded to
+   bf16 as the residual stream is: four bf16x2 words; *ss gets the sum of their squares in element order */
+__device__ __forceinline__ void residual_chunk(const FusedInput &in, bool peer, uint32_t K, uint32_t c, uint32_t (&out)[4], float &ss) {
+    const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
+    const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+    if (peer) {                                                  /* all loads in flight before the first add */
+        uint4 part[kCommMaxRanks];
+#pragma unroll
+        for (uint32_t r = 0; r < kCommMaxRanks; r++)
+            part[r] = r < in.world ? ld_volatile128(in.comm + comm_push_offset(K, in.slot, r) + (uint64_t)c * 16u) : make_uint4(0u, 0u, 0u, 0u);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (uint32_t r = 0; r < kCommMaxRanks; r++) {
+            if (r < in.world) {
+                const uint32_t pw[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) { acc[2 * k] += bf16_lo(pw[k]); acc[2 * k + 1] += bf16_hi(pw[k]); }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t d = cvt_pair(acc[2 * k], acc[2 * k + 1]);               /* the sum is a bf16 vector, like a local delta */
+            out[k] = cvt_pair(bf16_lo(hw[k]) + bf16_lo(d), bf16_hi(hw[k]) + bf16_hi(d));
+        }
+    } else if (in.delta) {
+        const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c);
+        const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) out[k] = cvt_pair(bf16_lo(hw[k]) + bf16_lo(dw[k]), bf16_hi(hw[k]) + bf16_hi(dw[k]));
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; k++) out[k] = hw[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) { const float v0 = bf16_lo(out[k]), v1 = bf16_hi(out[k]); ss += v0 * v0; ss += v1 * v1; }
+}
+
+/* x = bf16(weight * bf16(h * inv)) for eight values */
+__device__ __forceinline__ uint4 normalised_chunk(const uint32_t (&h)[4], uint4 weight, float inv) {
+    const uint32_t ww[4] = {weight.x, weight.y, weight.z, weight.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const uint32_t n = cvt_pair(bf16_lo(h[k]) * inv, bf16_hi(h[k]) * inv);
+        o[k] = cvt_pair(bf16_lo(ww[k]) * bf16_lo(n), bf16_hi(ww[k]) * bf16_hi(n));
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 /* after the dependency wait; ends with __syncthreads().  scal: THREADS / 32 floats of shared memory. */
 template <uint32_t THREADS>
-__device__ __forceinline__ void build_activation(const FusedInput &in, const void *x, uint32_t K, uint32_t cols, uint16_t *xs, uint16_t *nw, float *scal) {
+__device__ __forceinline__ void build_activation(const FusedInput &in, const void *x, uint32_t K, uint32_t cols, uint16_t *xs, uint16_t *nw, float *scal,
+                                                 const NormWeights &nr) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t xs_addr = smem_addr(xs), nw_addr = smem_addr(nw), chunks = cols >> 3, live = K >> 3;   /* chunks of eight values */
     const bool vec = (K & 7u) == 0u;
@@ -350,49 +420,30 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
             __syncthreads();
             return;
         }
-        const bool have_delta = peer || in.delta != nullptr;
+        const bool write_h = blockIdx.x == 0 && in.h_out != nullptr;
         float ss = 0.f;
-        if (vec) {
-            for (uint32_t c = tid; c < chunks; c += THREADS) {
-                uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        uint32_t held[kNormRegChunks][4];                        /* register path: the thread's chunks of h_out */
+        if (vec && nr.in_regs) {
+#pragma unroll
+            for (uint32_t i = 0; i < kNormRegChunks; i++) {
+                const uint32_t c = tid + i * THREADS;
                 if (c < live) {
-                    const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
-                    const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
-                    uint32_t dw[4] = {0u, 0u, 0u, 0u}, ow[4];
-                    if (peer) {                                  /* the ranks' partials, all loads in flight, added in rank order */
-                        uint4 part[kCommMaxRanks];
-#pragma unroll
-                        for (uint32_t r = 0; r < kCommMaxRanks; r++)
-                            part[r] = r < in.world ? ld_volatile128(in.comm + comm_push_offset(K, in.slot, r) + (uint64_t)c * 16u) : make_uint4(0u, 0u, 0u, 0u);
-                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                        for (uint32_t r = 0; r < kCommMaxRanks; r++) {
-                            if (r < in.world) {
-                                const uint32_t pw[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
-#pragma unroll
-                                for (int k = 0; k < 4; k++) { acc[2 * k] += bf16_lo(pw[k]); acc[2 * k + 1] += bf16_hi(pw[k]); }
-                            }
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; k++) dw[k] = bf16_pack(acc[2 * k], acc[2 * k + 1]);
-                    } else if (in.delta) { const uint4 d = *(reinterpret_cast<const uint4 *>(in.delta) + c); dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w; }
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        float v0 = bf16_lo(hw[k]), v1 = bf16_hi(hw[k]);
-                        if (have_delta) { v0 = bf16_rt(v0 + bf16_lo(dw[k])); v1 = bf16_rt(v1 + bf16_hi(dw[k])); }
-                        ss += v0 * v0; ss += v1 * v1;
-                        ow[k] = bf16_pack(v0, v1);
-                    }
-                    o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                    if (blockIdx.x == 0 && in.h_out) *(reinterpret_cast<uint4 *>(in.h_out) + c) = o;
+                    residual_chunk(in, peer, K, c, held[i], ss);
+                    if (write_h) *(reinterpret_cast<uint4 *>(in.h_out) + c) = make_uint4(held[i][0], held[i][1], held[i][2], held[i][3]);
                 }
-                sts128(xs_addr + c * 16u, o);
+            }
+        } else if (vec) {
+            for (uint32_t c = tid; c < live; c += THREADS) {
+                uint32_t o[4];
+                residual_chunk(in, peer, K, c, o, ss);
+                if (write_h) *(reinterpret_cast<uint4 *>(in.h_out) + c) = make_uint4(o[0], o[1], o[2], o[3]);
+                sts128(xs_addr + c * 16u, make_uint4(o[0], o[1], o[2], o[3]));
             }
         } else {
             for (uint32_t i = tid; i < K; i += THREADS) {
                 float v = bf16_to_float(in.h_in[i]);
                 if (in.delta) v = bf16_rt(v + bf16_to_float(in.delta[i]));
-                if (blockIdx.x == 0 && in.h_out) in.h_out[i] = bf16_round_nan(v);
+                if (write_h) in.h_out[i] = bf16_round_nan(v);
                 xs[i] = bf16_round_nan(v);
                 ss += v * v;
             }
@@ -404,37 +455,46 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
         float tot = 0.f;
         for (uint32_t i = 0; i < THREADS / 32u; i++) tot += scal[i];
         const float inv = rsqrtf(tot / (float)K + in.eps);
-        if (vec) {
-            for (uint32_t c = tid; c < live; c += THREADS) {
-                const uint4 v = lds128(xs_addr + c * 16u), w = lds128(nw_addr + c * 16u);
-                const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, ww[4] = {w.x, w.y, w.z, w.w};
-                uint32_t ow[4];
+        if (vec && nr.in_regs) {
 #pragma unroll
-                for (int k = 0; k < 4; k++) ow[k] = bf16_pack(bf16_lo(ww[k]) * bf16_rt(bf16_lo(vw[k]) * inv), bf16_hi(ww[k]) * bf16_rt(bf16_hi(vw[k]) * inv));
-                sts128(xs_addr + c * 16u, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+            for (uint32_t i = 0; i < kNormRegChunks; i++) {
+                const uint32_t c = tid + i * THREADS;
+                if (c < live) sts128(xs_addr + c * 16u, normalised_chunk(held[i], nr.w[i], inv));
+            }
+            for (uint32_t c = live + tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0u, 0u, 0u, 0u));
+        } else if (vec) {
+            for (uint32_t c = tid; c < chunks; c += THREADS) {   /* each thread re-reads the chunks it wrote itself */
+                uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                if (c < live) {
+                    const uint4 v = lds128(xs_addr + c * 16u);
+                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                    o = normalised_chunk(vw, lds128(nw_addr + c * 16u), inv);
+                }
+                sts128(xs_addr + c * 16u, o);
             }
         } else {
             for (uint32_t i = tid; i < cols; i += THREADS)
                 xs[i] = i < K ? bf16_round_nan(bf16_to_float(in.norm_w[i]) * bf16_rt(bf16_to_float(xs[i]) * inv)) : (uint16_t)0;
         }
     } else if (in.mode == kInputSwiglu) {
-        if (vec) {                                               /* four values per step: the exponentials spread evenly over the threads */
-            const uint2 *gate = reinterpret_cast<const uint2 *>(in.gate_up), *up = reinterpret_cast<const uint2 *>(in.gate_up + K);
-#pragma unroll 3
-            for (uint32_t c = tid; c < (cols >> 2); c += THREADS) {
-                uint2 o = make_uint2(0u, 0u);
-                if (c < (K >> 2)) {
-                    const uint2 gv = gate[c], uv = up[c];
-                    const uint32_t gw[2] = {gv.x, gv.y}, uw[2] = {uv.x, uv.y};
-                    uint32_t ow[2];
+        if (vec) {                                               /* eight values per step; exponentials and quotients by the fast hardware paths */
+            const uint4 *gate = reinterpret_cast<const uint4 *>(in.gate_up), *up = reinterpret_cast<const uint4 *>(in.gate_up + K);
+#pragma unroll 2
+            for (uint32_t c = tid; c < chunks; c += THREADS) {
+                uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                if (c < live) {
+                    const uint4 gv = gate[c], uv = up[c];
+                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+                    uint32_t ow[4];
 #pragma unroll
-                    for (int k = 0; k < 2; k++) {
+                    for (int k = 0; k < 4; k++) {
                         const float g0 = bf16_lo(gw[k]), g1 = bf16_hi(gw[k]);
-                        ow[k] = bf16_pack(bf16_rt(g0 / (1.f + __expf(-g0))) * bf16_lo(uw[k]), bf16_rt(g1 / (1.f + __expf(-g1))) * bf16_hi(uw[k]));
+                        const uint32_t act = cvt_pair(__fdividef(g0, 1.f + __expf(-g0)), __fdividef(g1, 1.f + __expf(-g1)));
+                        ow[k] = cvt_pair(bf16_lo(act) * bf16_lo(uw[k]), bf16_hi(act) * bf16_hi(uw[k]));
                     }
-                    o = make_uint2(ow[0], ow[1]);
+                    o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
-                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xs_addr + c * 8u), "r"(o.x), "r"(o.y) : "memory");
+                sts128(xs_addr + c * 16u, o);
             }
         } else {
             for (uint32_t i = tid; i < cols; i += THREADS) {
@@ -470,8 +530,11 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
 #ifndef NWC_RING_THREADS
 #define NWC_RING_THREADS 512
 #endif
+#ifndef NWC_RING_CTAS_PER_SM
+#define NWC_RING_CTAS_PER_SM 1
+#endif
 
-constexpr uint32_t kRingThreads = NWC_RING_THREADS, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES;
+constexpr uint32_t kRingThreads = NWC_RING_THREADS, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES, kRingCtasPerSm = NWC_RING_CTAS_PER_SM;
 constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
 constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes;
 constexpr uint32_t kRingBarrierBytes = (kRingThreads / 32u) * kRingStages * 8u;
@@ -480,18 +543,60 @@ constexpr uint32_t kRingMaxSmem = 232448u;                       /* 227 KB opt-i
 __host__ __device__ static inline uint32_t ring_x_bytes(const Geometry &g) { return (g.slots * 64u + 127u) & ~127u; }
 static inline uint32_t ring_smem_bytes(const Geometry &g, int input_mode = kInputPlain) { return (norm_like(input_mode) ? 2u : 1u) * ring_x_bytes(g) + 2u * (kRingThreads / 32u) * 68u + 256u + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes; }
 
+/* CTAs of the layout-2 ring kernel the launcher plans for: kRingCtasPerSm per SM while that many fit an SM's shared memory
+   side by side (each CTA also costs the SM 1 KB of bookkeeping), otherwise one per SM */
+/* the layout-2 ring kernel covers bf16, and fp8 matrices whose row groups hold an even number of slots (K % 64 in [1, 32] is
+   the exception: its last pair would straddle two row groups) */
+static inline bool ring_covers(int code, const Geometry &g, int input_mode) {
+    if (layout_of(code) != 2 || ring_smem_bytes(g, input_mode) > kRingMaxSmem || (uint64_t)g.groups * g.slots >= (1ull << 31)) return false;
+    return type_of(code) == kBf16 || (g.slots & 1u) == 0u;
+}
+static inline int ring_ctas(const Geometry &g, int input_mode, int sms) {
+    const uint32_t per_cta = ring_smem_bytes(g, input_mode) + 1024u;
+    return sms * (int)(per_cta * kRingCtasPerSm <= 233472u ? kRingCtasPerSm : 1u);
+}
+
+/* n / d for 32-bit n and a divisor fixed on the host: one multiply-high, one add, one shift (the kernels' index
+   arithmetic sits on the critical path of launches that last a few microseconds; a hardware-less 64-bit division costs
+   hundreds of cycles there).  m = ceil(2^(32 + s) / d) - 2^32 with s = ceil(log2 d). */
+struct FastDiv {
+    uint32_t d, m, s;
+    void set(uint32_t divisor) {
+        d = divisor ? divisor : 1u;
+        s = 0; while ((1ull << s) < d) s++;
+        m = (uint32_t)((((1ull << (32u + s)) + d - 1u) / d) - (1ull << 32));
+    }
+    __host__ __device__ __forceinline__ uint32_t div(uint32_t n) const {
+#if defined(__CUDA_ARCH__)
+        return (uint32_t)(((uint64_t)__umulhi(n, m) + n) >> s);
+#else
+        return (uint32_t)(((((uint64_t)n * m) >> 32) + n) >> s);
+#endif
+    }
+};
+
+/* Contiguous runs of `chunks` pieces of work for `warps` workers: chunks = q * warps + r, worker w owns q + (w < r) chunks
+   starting at chunk w * q + min(w, r).  All counts fit 32 bits (the launchers check). */
 struct FlatPlan {
-    uint32_t units_per_group;   /* slots (layout 2) or blocks (layouts 0, 1) per row group                              */
+    uint32_t units_per_group;   /* slots (layout 2; fp8: slot pairs) or blocks (layouts 0, 1) per row group             */
     uint32_t grain;             /* run boundaries are multiples of this many units (a whole row group when CB == 1)      */
     uint32_t chunks;            /* total units / grain                                                                 */
-    uint32_t warps;             /* warps that take part; warp w owns chunks [w * chunks / warps, (w + 1) * chunks / warps) */
-    uint32_t parts;             /* row stride of the partial sums = most warps that can share a row group               */
-    uint32_t direct;            /* 1: no row group is cut, warps write y themselves                                      */
+    uint32_t warps;             /* workers that take part                                                               */
+    uint32_t parts;             /* row stride of the partial sums = most workers that can share a row group             */
+    uint32_t direct;            /* 1: no row group is cut, workers write y themselves                                    */
     uint32_t fix;               /* 1 (layout 2 ring kernel, direct == 0): a cut row group is completed inside the kernel by
                                    the CTA that arrives last at the group's counter, no finalize launch                   */
-    __host__ __device__ __forceinline__ uint64_t start(uint32_t w) const { return ((uint64_t)w * chunks / warps) * grain; }
-    /* the warp whose run holds unit u */
-    __host__ __device__ __forceinline__ uint32_t owner(uint64_t u) const { return (uint32_t)(((u / grain + 1u) * warps - 1u) / chunks); }
+    uint32_t q, r;
+    FastDiv by_grain, by_q, by_q1, by_group;
+    void finish() { q = chunks / warps; r = chunks % warps; by_grain.set(grain); by_q.set(q); by_q1.set(q + 1u); by_group.set(units_per_group); }
+    __host__ __device__ __forceinline__ uint32_t start(uint32_t w) const { return (w * q + (w < r ? w : r)) * grain; }
+    /* the worker whose run holds unit u */
+    __host__ __device__ __forceinline__ uint32_t owner(uint32_t u) const {
+        const uint32_t c = by_grain.div(u), split = r * (q + 1u);
+        return c < split ? by_q1.div(c) : r + by_q.div(c - split);
+    }
+    /* the row group that holds unit u */
+    __host__ __device__ __forceinline__ uint32_t group_of(uint32_t u) const { return by_group.div(u); }
 };
 
 __device__ __forceinline__ void emit_flat(const SegmentArgs &a, const FlatPlan &p, uint32_t row, uint32_t part, float v) {
@@ -531,15 +636,17 @@ __device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, u
 /* Exceptions of one block (column block cb) for this lane: sum of value * x over the lane's `count` entries, split by
    fragment half; `base` is the block's offset in `data`.  Called once per 16 slots, so it stays out of line to keep the
    slot loop short. */
+template <int ELEM>
 __device__ __noinline__ float2 ring_exceptions(uint32_t count, uint32_t base, const uint8_t *__restrict__ data, uint32_t xs, uint32_t cb, uint32_t lane) {
+    constexpr uint32_t ES = ELEM == kFp8 ? 2u : 3u;              /* bytes per entry: stream index, then the fp8 byte or the bf16 value */
     float lo = 0.f, hi = 0.f;
     uint32_t sum;
     const uint32_t before = warp_exclusive_sum(count, lane, sum);
     if (sum) {
-        const uint8_t *ep = data + base + (uint64_t)before * 3u;
-        for (uint32_t k = 0; k < count; k++, ep += 3) {
+        const uint8_t *ep = data + base + (uint64_t)before * ES;
+        for (uint32_t k = 0; k < count; k++, ep += ES) {
             const uint32_t i = ep[0], jj = i & 15u, col = cb * kBlockCols + (i >> 4) * 32u + frag_col(lane, jj);
-            const float wv = __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
+            const float wv = ELEM == kFp8 ? fp8_to_float(ep[1]) : __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
             uint16_t xb;
             asm volatile("ld.shared.u16 %0, [%1];" : "=h"(xb) : "r"(xs + col * 2u));
             const float xv = bf16_to_float(xb);
@@ -556,7 +663,15 @@ constexpr uint32_t kRingEntries = 2u * (kRingThreads / 32u);
 constexpr uint32_t kRingShareBytes = kRingEntries * 4u + kRingEntries * 16u * 4u;
 constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 
-__global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
+/* ELEM = fp8: the raw plane holds 3-bit fields, 96 bits per lane and PAIR of slots (384 B per pair), so the unit of all
+   counting below is a pair of slots; the launcher takes this kernel only when every row group has an even number of slots. */
+template <int ELEM>
+__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
+    constexpr uint32_t U = ELEM == kFp8 ? 2u : 1u;               /* slots per unit                                  */
+    constexpr uint32_t kUnits = kRingSlots / U;                  /* units per stage                                 */
+    constexpr uint32_t kNibUnit = 256u * U, kRawUnit = ELEM == kFp8 ? 384u : 512u;      /* bytes of a unit in the two planes */
+    constexpr uint32_t kBlockUnits = 16u / U;                    /* units per 512-column block                      */
+    static_assert(kRingSlots % U == 0u, "a stage holds whole units");
     extern __shared__ __align__(128) uint8_t ring_smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Geometry g(a.M, a.K, 2);
@@ -575,39 +690,40 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t cluster_ctas = cluster.num_blocks(), cta_rank = cluster.block_rank(), cluster_id = blockIdx.x / cluster_ctas;
-    const uint64_t k0 = plan.start(cluster_id), k1 = plan.start(cluster_id + 1u);
-    const uint64_t c0 = k0 + (k1 - k0) * cta_rank / cluster_ctas, c1 = k0 + (k1 - k0) * (cta_rank + 1u) / cluster_ctas;
-    const uint32_t cn = (uint32_t)(c1 - c0), w0 = (uint32_t)((uint64_t)cn * warp / (kRingThreads / 32u)), w1 = (uint32_t)((uint64_t)cn * (warp + 1u) / (kRingThreads / 32u));
-    const uint64_t u0 = c0 + w0;
-    const uint32_t count = w1 - w0, n_stage = (count + kRingSlots - 1u) / kRingSlots;
-    const uint8_t *nib_next = a.low + u0 * 256u, *raw_next = a.low + g.nibble_plane_bytes() + u0 * 512u;
-    uint32_t left = count;                                       /* slots not yet requested */
+    const uint32_t k0 = plan.start(cluster_id), k1 = plan.start(cluster_id + 1u), cluster_shift = (uint32_t)__ffs((int)cluster_ctas) - 1u;   /* clusters of 1, 2, 4 or 8 */
+    const uint32_t c0 = k0 + (((k1 - k0) * cta_rank) >> cluster_shift), c1 = k0 + (((k1 - k0) * (cta_rank + 1u)) >> cluster_shift);
+    const uint32_t cn = c1 - c0, w0 = cn * warp / (kRingThreads / 32u), w1 = cn * (warp + 1u) / (kRingThreads / 32u);
+    const uint32_t u0 = c0 + w0;
+    const uint32_t count = w1 - w0, n_stage = (count + kUnits - 1u) / kUnits;
+    const uint8_t *nib_next = a.low + (uint64_t)u0 * kNibUnit, *raw_next = a.low + g.nibble_plane_bytes() + (uint64_t)u0 * kRawUnit;
+    uint32_t left = count;                                       /* units not yet requested */
     if (lane == 0) {
         for (uint32_t b = 0; b < kRingStages; b++) mbar_init(bars + b * 8u, 1u);
         mbar_init_fence();
         for (uint32_t b = 0; b < kRingStages && left; b++) {     /* fill the ring before anything else */
-            const uint32_t n = min(kRingSlots, left), dst = ring + b * kRingStageBytes;
-            mbar_expect(bars + b * 8u, n * 768u);
-            bulk_load(dst, nib_next, n * 256u, bars + b * 8u);
-            bulk_load(dst + kRingSlots * 256u, raw_next, n * 512u, bars + b * 8u);
-            nib_next += n * 256u; raw_next += n * 512u; left -= n;
+            const uint32_t n = min(kUnits, left), dst = ring + b * kRingStageBytes;
+            mbar_expect(bars + b * 8u, n * (kNibUnit + kRawUnit));
+            bulk_load(dst, nib_next, n * kNibUnit, bars + b * 8u);
+            bulk_load(dst + kRingSlots * 256u, raw_next, n * kRawUnit, bars + b * 8u);
+            nib_next += n * kNibUnit; raw_next += n * kRawUnit; left -= n;
         }
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     FixedTables t; t.load(a.lut);
-    const uint32_t slots = g.slots;
-    uint32_t rb = (uint32_t)(u0 / slots), s = (uint32_t)(u0 - (uint64_t)rb * slots);      /* row group and slot inside it */
+    const uint32_t slots = g.slots / U;                          /* units per row group */
+    uint32_t rb = plan.group_of(u0), s = u0 - rb * slots;         /* row group and unit inside it */
     /* exception count of this lane and data offset of the next block to start in this run, fetched one block ahead */
-    uint32_t next_block = rb * g.CB + ((s + 15u) >> 4), next_count = 0, next_base = 0;
+    uint32_t next_block = rb * g.CB + ((s + kBlockUnits - 1u) / kBlockUnits), next_count = 0, next_base = 0;
     if (next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
     /* The weights do not depend on the kernel before this one, the activation vector does.  It is built in shared
        memory, zero beyond K (the last slot may cover columns past K16). */
-    stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes));
+    NormWeights norm_regs;
+    stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes), norm_regs);
     if (threadIdx.x < kRingEntries) share_group[threadIdx.x] = kNoGroup;
     if (threadIdx.x < 2u) cta_group[threadIdx.x] = kNoGroup;
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal);
-    const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * 16u, xq = xs + (lane & 3u) * 16u;
+    build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
+    const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * (ELEM == kFp8 ? 4u : 16u), xq = xs + (lane & 3u) * 16u;
     uint32_t seg_first = s, entry = 2u * warp;                   /* first slot of the current segment; where a shared one goes */
     float d[4] = {0.f, 0.f, 0.f, 0.f}, ex_lo = 0.f, ex_hi = 0.f;
     /* the segment [seg_first, s) of row group rb is complete */
@@ -622,7 +738,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
                 const float vlo = __shfl_sync(0xffffffffu, lo, src), vhi = __shfl_sync(0xffffffffu, hi, src);
                 if (lane < 16u) emit_group(a, rb, lane, (lane & 8u) ? vhi : vlo, 0x0000FFFFu);
             } else if ((lane & 3u) == 0u) {
-                const uint32_t part = cluster_id - plan.owner((uint64_t)rb * slots);
+                const uint32_t part = cluster_id - plan.owner(rb * slots);
                 emit_flat(a, plan, rb * 16u + r, part, lo); emit_flat(a, plan, rb * 16u + r + 8u, part, hi);
             }
         } else {
@@ -640,48 +756,58 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
             for (uint32_t b = 0; b < kRingStages; b++) for (uint32_t i = 0; i < 64u && !mbar_poll(bars + b * 8u, parity ^ (b < buf ? 1u : 0u)); i++) {}
             break;
         }
-        /* one slot: 16 weights per lane against 32 columns of x */
-        auto slot = [&](uint32_t j, uint32_t column_slot) {
-            const uint2 nib = lds64(src + j * 256u + lane8);
-            const uint4 raw = lds128(src + j * 512u + lane16);
-            const uint4 xv = lds128(xq + column_slot * 64u);
+        /* one unit: per slot 16 weights per lane against 32 columns of x (fp8: two slots that share one 96-bit field group) */
+        auto slot = [&](uint32_t j, uint32_t column_unit) {
             uint32_t a0, a1, a2, a3;
-            fixed_half<kBf16, 0>(t, nib.x, raw.x, raw.y, 0u, 0u, 0u, a0, a1, a2, a3);
-            mma_bf16(d, a0, a1, a2, a3, xv.x, xv.y);
-            fixed_half<kBf16, 2>(t, nib.y, raw.z, raw.w, 0u, 0u, 0u, a0, a1, a2, a3);
-            mma_bf16(d, a0, a1, a2, a3, xv.z, xv.w);
+            if (ELEM == kFp8) {
+                const uint32_t f0 = lds32(src + j * 384u + lane16), f1 = lds32(src + j * 384u + 128u + lane16), f2 = lds32(src + j * 384u + 256u + lane16);
+                const uint2 n0 = lds64(src + (2u * j) * 256u + lane8), n1 = lds64(src + (2u * j + 1u) * 256u + lane8);
+                const uint4 x0 = lds128(xq + (2u * column_unit) * 64u), x1 = lds128(xq + (2u * column_unit + 1u) * 64u);
+                fixed_half<kFp8, 0>(t, n0.x, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x0.x, x0.y);
+                fixed_half<kFp8, 2>(t, n0.y, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x0.z, x0.w);
+                fixed_half<kFp8, 4>(t, n1.x, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x1.x, x1.y);
+                fixed_half<kFp8, 6>(t, n1.y, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x1.z, x1.w);
+            } else {
+                const uint2 nib = lds64(src + j * 256u + lane8);
+                const uint4 raw = lds128(src + j * 512u + lane16);
+                const uint4 xv = lds128(xq + column_unit * 64u);
+                fixed_half<kBf16, 0>(t, nib.x, raw.x, raw.y, 0u, 0u, 0u, a0, a1, a2, a3);
+                mma_bf16(d, a0, a1, a2, a3, xv.x, xv.y);
+                fixed_half<kBf16, 2>(t, nib.y, raw.z, raw.w, 0u, 0u, 0u, a0, a1, a2, a3);
+                mma_bf16(d, a0, a1, a2, a3, xv.z, xv.w);
+            }
         };
-        /* the block whose first slot is f starts here: this warp adds the block's exceptions */
+        /* the block whose first unit is f starts here: this warp adds the block's exceptions */
         auto exceptions = [&](uint32_t f) {
-            const float2 e = ring_exceptions(next_count, next_base, a.data, xs, f >> 4, lane);
+            const float2 e = ring_exceptions<ELEM>(next_count, next_base, a.data, xs, f / kBlockUnits, lane);
             ex_lo += e.x; ex_hi += e.y;
             if (++next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
         };
-        if (todo >= kRingSlots && s + kRingSlots <= slots) {     /* a full stage inside one row group: no per-slot checks */
+        if (todo >= kUnits && s + kUnits <= slots) {             /* a full stage inside one row group: no per-unit checks */
 #pragma unroll
-            for (uint32_t j = 0; j < kRingSlots; j++) slot(j, s + j);
-            const uint32_t to_block = (0u - s) & 15u;            /* slots from s to the next first slot of a block */
-            if (to_block < kRingSlots) exceptions(s + to_block);
-            s += kRingSlots;
+            for (uint32_t j = 0; j < kUnits; j++) slot(j, s + j);
+            const uint32_t to_block = (0u - s) & (kBlockUnits - 1u);      /* units from s to the next first unit of a block */
+            if (to_block < kUnits) exceptions(s + to_block);
+            s += kUnits;
             if (s == slots) { flush(); s = 0; seg_first = 0; rb++; }
         } else {
-            const uint32_t n = min(todo, kRingSlots);
+            const uint32_t n = min(todo, kUnits);
 #pragma unroll 1
             for (uint32_t j = 0; j < n; j++) {
                 slot(j, s);
-                if ((s & 15u) == 0u) exceptions(s);
+                if ((s & (kBlockUnits - 1u)) == 0u) exceptions(s);
                 if (++s == slots) { flush(); s = 0; seg_first = 0; rb++; }
             }
         }
-        todo -= min(todo, kRingSlots);
+        todo -= min(todo, kUnits);
         __syncwarp();
         if (lane == 0 && left) {                                 /* refill the stage just read */
-            const uint32_t n = min(kRingSlots, left);
+            const uint32_t n = min(kUnits, left);
             async_proxy_fence();
-            mbar_expect(bar, n * 768u);
-            bulk_load(src, nib_next, n * 256u, bar);
-            bulk_load(src + kRingSlots * 256u, raw_next, n * 512u, bar);
-            nib_next += n * 256u; raw_next += n * 512u; left -= n;
+            mbar_expect(bar, n * (kNibUnit + kRawUnit));
+            bulk_load(src, nib_next, n * kNibUnit, bar);
+            bulk_load(src + kRingSlots * 256u, raw_next, n * kRawUnit, bar);
+            nib_next += n * kNibUnit; raw_next += n * kRawUnit; left -= n;
         }
         if (++buf == kRingStages) { buf = 0; parity ^= 1u; }
     }
@@ -701,7 +827,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
                 const uint32_t gn = share_group[n];
                 if (gn == grp) v += share_value[n * 16u + row]; else if (gn != kNoGroup) break;
             }
-            const uint64_t g0 = (uint64_t)grp * slots;
+            const uint32_t g0 = grp * slots;
             const bool inside = g0 >= c0 && g0 + slots <= c1;
             const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16u);
             if (plan.direct ? (cluster_ctas == 1u || inside) : (plan.fix && inside)) emit_group(a, grp, row, v, half_mask);
@@ -718,7 +844,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
         if (threadIdx.x < 32u) {
             const uint32_t which = threadIdx.x >> 4, row = threadIdx.x & 15u, grp = cta_group[which];
             /* this CTA is the first of its cluster to hold the group unless the group began before its run */
-            if (grp != kNoGroup && !((uint64_t)grp * slots < c0 && cta_rank > 0u)) {
+            if (grp != kNoGroup && !(grp * slots < c0 && cta_rank > 0u)) {
                 float v = cta_value[which * 16u + row];
                 for (uint32_t r = cta_rank + 1u; r < cluster_ctas; r++) {        /* later CTAs hold it as their first group, in rank order */
                     const uint32_t theirs = cluster.map_shared_rank(cta_group, r)[0];
@@ -737,9 +863,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) ring_kernel_layout2(const Seg
         __syncthreads();                                            /* this CTA's partials are written */
         if (warp == 0u && cn != 0u) {
             const uint32_t half = lane >> 4, sub = lane & 15u, half_mask = 0xFFFFu << (16u * half);
-            const uint32_t first_group = (uint32_t)(c0 / slots), last_group = (uint32_t)((c1 - 1u) / slots);
+            const uint32_t first_group = plan.group_of(c0), last_group = plan.group_of(c1 - 1u);
             const uint32_t grp = half ? last_group : first_group;
-            const uint64_t g0 = (uint64_t)grp * slots;
+            const uint32_t g0 = grp * slots;
             const bool cut = !(g0 >= c0 && g0 + slots <= c1);
             if (cut && !(half && last_group == first_group)) {
                 const uint32_t first_owner = plan.owner(g0), holders = plan.owner(g0 + slots - 1u) - first_owner + 1u;
@@ -782,7 +908,7 @@ __global__ void finalize_flat_kernel(const float *__restrict__ partial, const ui
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (i >= M) return;
-    const uint64_t first_unit = (uint64_t)(i / rows) * plan.units_per_group;
+    const uint32_t first_unit = (i / rows) * plan.units_per_group;
     const uint32_t n = plan.owner(first_unit + plan.units_per_group - 1u) - plan.owner(first_unit) + 1u;
     float v = 0.f;
     for (uint32_t p = 0; p < n; p++) v += partial[(uint64_t)i * plan.parts + p];
@@ -809,6 +935,7 @@ static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t
     p.fix = 0u;
     p.parts = p.direct ? 1u : (uint32_t)((units_per_group - 1u) / (total / use)) + 2u;
     if (p.parts > g.CB) p.parts = g.CB;                                        /* bound above guarantees the true count fits */
+    p.finish();
 }
 
 /* Layout 2: the plan's "warps" are CTAs (the 32 warps of a CTA split its run evenly and add up in shared memory).
@@ -832,7 +959,9 @@ static ClusterRoom cluster_room(int sms);
    is worth about kFixSlots slots (a CTA barrier, one atomic and a few dependent loads at the kernel's end). */
 constexpr uint64_t kFixSlots = 64;
 static bool g_disable_ring = false, g_disable_fixup = false;     /* A/B switches of the tests (set_ring_kernels, set_fixup_plans) */
-static void make_cta_plan_layout2(const Geometry &g, int sms, FlatPlan &p, uint32_t &cluster, bool allow_fix = false) {
+static void make_cta_plan_layout2(const Geometry &g0, int elem, int sms, FlatPlan &p, uint32_t &cluster, bool allow_fix = false) {
+    Geometry g = g0;
+    if (elem == kFp8) g.slots >>= 1;                              /* fp8: the kernel counts in pairs of slots; the slot-based costs below scale alike */
     const uint64_t total = (uint64_t)g.groups * g.slots;
     const ClusterRoom room = cluster_room(sms);
     if (sms > (int)kFixCounters || g_disable_fixup) allow_fix = false;
@@ -1043,7 +1172,7 @@ __device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const Fla
     const Geometry g(a.M, a.K, LAYOUT);
     const uint32_t w = warp * gridDim.x + blockIdx.x;           /* interleaved: a short plan still spreads over all SMs */
     if (w >= plan.warps) return;
-    const uint32_t b0 = (uint32_t)plan.start(w), b1 = (uint32_t)plan.start(w + 1u);
+    const uint32_t b0 = plan.start(w), b1 = plan.start(w + 1u);
     if (lane == 0) { mbar_init(bars, 1u); mbar_init(bars + 8u, 1u); mbar_init_fence(); }
     __syncwarp();
     /* byte span of block b inside data: [start, start + bytes), rounded out to 16; bytes == 0 means "does not fit a stage" */
@@ -1093,7 +1222,7 @@ __device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const Fla
         if (b + 2u < b1) issue(b + 2u, words_after);              /* the stage just decoded is free again (all lanes passed the block's last __syncwarp) */
         words = words_next; words_next = words_after;
         if (++cb == g.CB || b + 1u == b1) {                       /* the warp's share of this row group is complete */
-            const uint32_t part = w - plan.owner((uint64_t)rb * g.CB);
+            const uint32_t part = w - plan.owner(rb * g.CB);
             if (LAYOUT == 0) { if (lane < 8u) emit_flat(a, plan, rb * 8u + lane, part, row_sum); }
             else if ((lane & 3u) == 0u) { emit_flat(a, plan, rb * 16u + (lane >> 2), part, d[0]); emit_flat(a, plan, rb * 16u + (lane >> 2) + 8u, part, d[2]); }
             row_sum = 0.f; d[0] = d[1] = d[2] = d[3] = 0.f;
@@ -1191,10 +1320,11 @@ __global__ void __launch_bounds__(kSmallThreads, NWC_SMALL_RESIDENT) small_kerne
     const uint32_t early_block = next.valid ? next.b : 0xFFFFFFFFu;
     if (next.valid) first_raw_rows<ELEM>(a, g, next.pass * per_pass + my_group, next.cb, lane, early_rows[0], early_rows[1]);
     stage_tables(tables, a.lut, tid, kSmallThreads);
-    stage_norm_weight<kSmallThreads>(in, a.K, nw);
+    NormWeights norm_regs;
+    stage_norm_weight<kSmallThreads>(in, a.K, nw, norm_regs);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    build_activation<kSmallThreads>(in, a.x, a.K, g.K16, xs, nw, scal);
+    build_activation<kSmallThreads>(in, a.x, a.K, g.K16, xs, nw, scal, norm_regs);
     const uint32_t xs_addr = smem_addr(xs);
     const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords;
     float *stash = stash_all + warp * 64u;
@@ -1364,10 +1494,11 @@ __global__ void __launch_bounds__(kSplitThreads, 3) small_split_kernel_layout0(c
     __syncthreads();                                                                     /* barriers initialised before anyone arms them */
     prefetch_block(blockIdx.x, j, 0u);
     stage_tables(tables, a.lut, tid, kSplitThreads);
-    stage_norm_weight<kSplitThreads>(in, a.K, nw);
+    NormWeights norm_regs;
+    stage_norm_weight<kSplitThreads>(in, a.K, nw, norm_regs);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    build_activation<kSplitThreads>(in, a.x, a.K, g.K16, xs, nw, scal);
+    build_activation<kSplitThreads>(in, a.x, a.K, g.K16, xs, nw, scal, norm_regs);
     const uint32_t xs_addr = smem_addr(xs), table = smem_addr(tables), sym = table + 4u * kTableWords;
     float *stash = stash_all + warp * 16u;
     uint32_t phases = 0, which = 0;
@@ -1530,14 +1661,14 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_f
     FlatPlan plan;
     if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
     if (!g_disable_ring && layout == 1) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan); return plan.direct ? 1 : 2; }
-    if (!g_disable_ring && layout == 2 && elem == kBf16 && ring_smem_bytes(g) <= kRingMaxSmem) { uint32_t cluster; make_cta_plan_layout2(g, sms, plan, cluster, allow_fix); return plan.direct || plan.fix ? 1 : 2; }
+    if (!g_disable_ring && ring_covers(code, g, kInputPlain)) { uint32_t cluster; make_cta_plan_layout2(g, elem, ring_ctas(g, kInputPlain, sms), plan, cluster, allow_fix); return plan.direct || plan.fix ? 1 : 2; }
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
 /* the token path of this matrix builds its activation vector itself (nwc_linear_fused needs no prologue launch) */
 bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode) {
     const Geometry g(M, K, layout_of(code));
-    return layout_of(code) == 2 && type_of(code) == kBf16 && !g_disable_ring && ring_smem_bytes(g, input_mode) <= kRingMaxSmem;
+    return !g_disable_ring && ring_covers(code, g, input_mode);
 }
 
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input) {
@@ -1578,10 +1709,11 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     }
     FusedInput in{kInputPlain, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr, nullptr, 0u, 0u, 0ull};
     if (input) in = *input;
-    if (layout == 2 && elem == kBf16 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_smem_bytes(g, in.mode) <= kRingMaxSmem) {
+    if (mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_covers(code, g, in.mode)) {
         uint32_t cluster;
-        make_cta_plan_layout2(g, sms, plan, cluster, a.fixup != 0u);
-        err = launch_cluster_kernel(ring_kernel_layout2, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
+        make_cta_plan_layout2(g, elem, ring_ctas(g, in.mode, sms), plan, cluster, a.fixup != 0u);
+        err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in)
+                           : launch_cluster_kernel(ring_kernel_layout2<kBf16>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
         if (err == cudaSuccess && !plan.direct && !plan.fix)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
@@ -1613,7 +1745,7 @@ static ClusterRoom cluster_room(int sms) {
     if (dev < 0 || dev >= 64) dev = 0;
     if (!known[dev]) {
         ClusterRoom r{{sms, 0, 0, 0}};
-        cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+        cudaFuncSetAttribute(ring_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
         for (int lg = 1; lg < 4; lg++) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)sms / (1u << lg) * (1u << lg)); cfg.blockDim = dim3(kRingThreads); cfg.dynamicSmemBytes = kRingMaxSmem;
@@ -1621,7 +1753,7 @@ static ClusterRoom cluster_room(int sms) {
             attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 1u << lg; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr; cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
+            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
         }
         cache[dev] = r; known[dev] = true;
     }
@@ -1640,7 +1772,8 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(small_split_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(prefix_ring_kernel_layout1<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout1<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);

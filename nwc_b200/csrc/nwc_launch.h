@@ -67,6 +67,7 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_f
 cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy);
 int read_prefill_status(bool clear);
 void configure_prefill_kernels();
+void prepare_static_scratch();               /* nwc_linear_bf16_static: look up the built-in scratch area of the current device */
 int read_model_status(bool clear);           /* 0, or 3 when the sharded argmax gave up waiting for a rank */
 unsigned long long peer_timeout_ns();        /* longest wait for other ranks inside a kernel (nwc_comm_set_timeout_ms) */
 void configure_model_kernels();              /* per-device opt-ins of the decode-step kernels */

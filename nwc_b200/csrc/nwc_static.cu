@@ -9,6 +9,7 @@
  * The array's name below is only a host-side handle.  The address the kernels need is looked up once per device with
  * cudaGetSymbolAddress while that device is current, and only that address is ever passed to a launch.
  */
+#include <atomic>
 #include <mutex>
 #include "../../include/nwc_ops.h"
 #include "nwc_launch.h"
@@ -19,7 +20,7 @@ static __device__ __align__(256) float g_static_scratch[NWC_STATIC_SCRATCH_FLOAT
 
 namespace {
 constexpr int kMaxDevices = 64;
-float *g_scratch_address[kMaxDevices];      /* device address of g_static_scratch on each device, null until looked up */
+std::atomic<float *> g_scratch_address[kMaxDevices];      /* device address of g_static_scratch on each device, null until looked up */
 std::mutex g_lookup_lock;
 
 /* device address of the scratch array on the current device; null (and *err set) when it cannot be had */
@@ -27,17 +28,26 @@ float *scratch_on_current_device(int *err) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { *err = e != cudaSuccess ? (int)e : (int)cudaErrorInvalidDevice; return nullptr; }
-    if (g_scratch_address[dev]) return g_scratch_address[dev];
+    if (float *known = g_scratch_address[dev].load(std::memory_order_acquire)) return known;
     std::lock_guard<std::mutex> hold(g_lookup_lock);
-    if (!g_scratch_address[dev]) {
+    float *known = g_scratch_address[dev].load(std::memory_order_relaxed);
+    if (!known) {
         void *p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || !p) { *err = e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol; return nullptr; }
-        g_scratch_address[dev] = static_cast<float *>(p);
+        known = static_cast<float *>(p);
+        g_scratch_address[dev].store(known, std::memory_order_release);
     }
-    return g_scratch_address[dev];
+    return known;
 }
 }  // namespace
+
+namespace nwc {
+/* Called when a device is prepared (nwc_setup and the first call of any entry point on that device): looks the area's
+   address up right away, so that a later nwc_linear_bf16_static - even one made while a stream is being captured - finds
+   it cached.  A failure here is not fatal; the entry point reports it when it is used. */
+void prepare_static_scratch() { int ignored = 0; scratch_on_current_device(&ignored); }
+}  // namespace nwc
 
 NWC_EXPORT int nwc_linear_bf16_static(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                                       const uint8_t *low, const float *x, const uint16_t *bias, const float *scale, uint16_t *y,
