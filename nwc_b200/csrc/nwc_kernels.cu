@@ -633,17 +633,13 @@ __device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, u
     }
 }
 
-/* Exceptions of one block (column block cb) for this lane: sum of value * x over the lane's `count` entries, split by
-   fragment half; `base` is the block's offset in `data`.  Called once per 16 slots, so it stays out of line to keep the
-   slot loop short. */
+/* Exceptions of one block (column block cb) for this lane: sum of value * x over the lane's `count` entries at `ep`, split
+   by fragment half.  Called once per 16 slots, so it stays out of line to keep the slot loop short. */
 template <int ELEM>
-__device__ __noinline__ float2 ring_exceptions(uint32_t count, uint32_t base, const uint8_t *__restrict__ data, uint32_t xs, uint32_t cb, uint32_t lane) {
+__device__ __noinline__ float2 ring_exceptions(uint32_t count, const uint8_t *__restrict__ ep, uint32_t xs, uint32_t cb, uint32_t lane) {
     constexpr uint32_t ES = ELEM == kFp8 ? 2u : 3u;              /* bytes per entry: stream index, then the fp8 byte or the bf16 value */
     float lo = 0.f, hi = 0.f;
-    uint32_t sum;
-    const uint32_t before = warp_exclusive_sum(count, lane, sum);
-    if (sum) {
-        const uint8_t *ep = data + base + (uint64_t)before * ES;
+    if (__any_sync(0xffffffffu, count != 0u)) {
         for (uint32_t k = 0; k < count; k++, ep += ES) {
             const uint32_t i = ep[0], jj = i & 15u, col = cb * kBlockCols + (i >> 4) * 32u + frag_col(lane, jj);
             const float wv = ELEM == kFp8 ? fp8_to_float(ep[1]) : __uint_as_float(((uint32_t)ep[1] | ((uint32_t)ep[2] << 8)) << 16);
@@ -713,14 +709,31 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
     const uint32_t slots = g.slots / U;                          /* units per row group */
     uint32_t rb = plan.group_of(u0), s = u0 - rb * slots;         /* row group and unit inside it */
     /* exception count of this lane and data offset of the next block to start in this run, fetched one block ahead */
-    uint32_t next_block = rb * g.CB + ((s + kBlockUnits - 1u) / kBlockUnits), next_count = 0, next_base = 0;
-    if (next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
+    /* Exception lists, three blocks deep so that no warp ever waits for memory at a block boundary: `ahead` = exception
+       count and data offset of the block after next (loads in flight), `next` = the next block to start in this run, its
+       count and the address of this lane's first entry, already pulled towards L1. */
+    constexpr uint32_t kEntryBytes = ELEM == kFp8 ? 2u : 3u;
+    uint32_t next_block = rb * g.CB + ((s + kBlockUnits - 1u) / kBlockUnits), next_count = 0, ahead_count = 0, ahead_base = 0;
+    const uint8_t *next_entries = a.data;
+    auto load_ahead = [&](uint32_t b) {
+        ahead_count = 0; ahead_base = 0;
+        if (b < g.nb) { ahead_count = __ldg(a.hdr + (uint64_t)b * kLanes + lane); ahead_base = __ldg(a.bases + b); }
+    };
+    auto promote = [&]() {                                       /* ahead -> next: where this lane's entries start, and fetch them */
+        uint32_t total;
+        const uint32_t before = warp_exclusive_sum(ahead_count, lane, total);
+        next_count = ahead_count;
+        next_entries = a.data + ahead_base + (uint64_t)before * kEntryBytes;
+        if (next_count) asm volatile("prefetch.global.L1 [%0];" ::"l"(next_entries));
+    };
+    load_ahead(next_block);
     /* The weights do not depend on the kernel before this one, the activation vector does.  It is built in shared
        memory, zero beyond K (the last slot may cover columns past K16). */
     NormWeights norm_regs;
     stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes), norm_regs);
     if (threadIdx.x < kRingEntries) share_group[threadIdx.x] = kNoGroup;
     if (threadIdx.x < 2u) cta_group[threadIdx.x] = kNoGroup;
+    promote(); load_ahead(next_block + 1u);                      /* (constants: before the wait) */
     asm volatile("griddepcontrol.wait;" ::: "memory");
     build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
     const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * (ELEM == kFp8 ? 4u : 16u), xq = xs + (lane & 3u) * 16u;
@@ -779,9 +792,10 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
         };
         /* the block whose first unit is f starts here: this warp adds the block's exceptions */
         auto exceptions = [&](uint32_t f) {
-            const float2 e = ring_exceptions<ELEM>(next_count, next_base, a.data, xs, f / kBlockUnits, lane);
+            const float2 e = ring_exceptions<ELEM>(next_count, next_entries, xs, f / kBlockUnits, lane);
             ex_lo += e.x; ex_hi += e.y;
-            if (++next_block < g.nb) { next_count = __ldg(a.hdr + (uint64_t)next_block * kLanes + lane); next_base = __ldg(a.bases + next_block); }
+            next_block++;
+            promote(); load_ahead(next_block + 1u);
         };
         if (todo >= kUnits && s + kUnits <= slots) {             /* a full stage inside one row group: no per-unit checks */
 #pragma unroll
@@ -956,8 +970,12 @@ static ClusterRoom cluster_room(int sms);
    cluster the finer the split but the fewer SMs), or equal runs of slots per CTA with per-CTA partials and the finalize
    launch.  Cost = slots the busiest CTA streams, plus what the extra synchronisation or launch is worth in slots. */
 /* With allow_fix the equal runs need no second launch: cut row groups are completed inside the kernel (FlatPlan::fix), which
-   is worth about kFixSlots slots (a CTA barrier, one atomic and a few dependent loads at the kernel's end). */
-constexpr uint64_t kFixSlots = 64;
+   costs a CTA barrier, an atomic with its fences and a few dependent loads at the kernel's end: measured about 2.5 us,
+   the time a CTA streams kFixSlots slots.
+   Cost of a candidate = what its busiest CTA streams, except that CTAs which finish early leave their share of the HBM
+   bandwidth to the others, so only half of the imbalance counts (measured: 10240 x 8192 runs 5 % faster on whole row
+   groups, 4 or 5 per CTA, than on equal runs with the fix-up), plus what the extra synchronisation or launch is worth. */
+constexpr uint64_t kFixSlots = 160;
 static bool g_disable_ring = false, g_disable_fixup = false;     /* A/B switches of the tests (set_ring_kernels, set_fixup_plans) */
 static void make_cta_plan_layout2(const Geometry &g0, int elem, int sms, FlatPlan &p, uint32_t &cluster, bool allow_fix = false) {
     Geometry g = g0;
@@ -965,13 +983,15 @@ static void make_cta_plan_layout2(const Geometry &g0, int elem, int sms, FlatPla
     const uint64_t total = (uint64_t)g.groups * g.slots;
     const ClusterRoom room = cluster_room(sms);
     if (sms > (int)kFixCounters || g_disable_fixup) allow_fix = false;
-    uint64_t best = (total + (uint64_t)sms - 1u) / (uint64_t)sms + (allow_fix ? kFixSlots : kFinalizeSlots);
-    uint32_t best_cluster = 0;                                   /* 0 = equal runs + finalize */
+    const uint64_t even = (total + (uint64_t)sms - 1u) / (uint64_t)sms;       /* slots per CTA if all were equally loaded */
+    uint64_t best = even + (allow_fix ? kFixSlots : kFinalizeSlots);
+    uint32_t best_cluster = 0;                                   /* 0 = equal runs (+ fix-up or finalize) */
     for (uint32_t lg = 0; lg < 4u; lg++) {
         const uint64_t clusters = lg == 0u ? (uint64_t)sms : (uint64_t)room.count[lg];
         if (!clusters) continue;
         const uint64_t use = clusters < g.groups ? clusters : g.groups;
-        const uint64_t cost = (((g.groups + use - 1u) / use) * g.slots + (1u << lg) - 1u) / (1u << lg) + (lg ? kClusterSlots : 0u);
+        const uint64_t busiest = (((g.groups + use - 1u) / use) * g.slots + (1u << lg) - 1u) / (1u << lg);
+        const uint64_t cost = (busiest + (even < busiest ? even : busiest) + 1u) / 2u + (lg ? kClusterSlots : 0u);
         if (cost < best) { best = cost; best_cluster = 1u << lg; }
     }
     cluster = best_cluster ? best_cluster : 1u;

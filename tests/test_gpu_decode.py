@@ -159,8 +159,7 @@ def test_256_greedy_steps_follow_transformers_on_the_0p6b_shapes():
     seq = seq.tolist()
     ties = _compare_choices(eng, logits, seq[:-1], 31)
     assert len(ties) <= 2, ties                                          # ties are rare events, not a tolerance
-    eng.prefill(seq[:32])
-    mine = eng.generate(256).tolist()
+    mine = [int(eng.prefill(seq[:32]).item())] + eng.generate(255).tolist()      # the choice after the prompt, then its 255 successors
     upto = 256 if not ties else ties[0] - 31
     assert mine[:upto] == seq[32:32 + upto]
     history = torch.randint(0, 151936, (1, 288), generator=g)

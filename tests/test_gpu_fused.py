@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
                                              (6144, 2560, 2, 0), (2560, 9728, 2, 0), (100, 1000, 2, 0), (13, 40, 2, 0), (48, 1004, 2, 0),
                                              # layout 2 shapes whose row groups do not divide over the SMs: equal runs per CTA, cut row groups completed
                                              # inside the kernel by the last CTA to arrive (no finalize launch)
-                                             (1280, 8192, 2, 0), (2000, 4096, 2, 0), (4100, 3000, 2, 0), (16, 28672, 2, 0), (7168, 1536, 2, 0)])
+                                             (1280, 8192, 2, 0), (2000, 4096, 2, 0), (4100, 3000, 2, 0), (16, 28672, 2, 0), (32, 28672, 2, 0), (7168, 1536, 2, 0),
+                                             (512, 1024, 2, 1), (2560, 4096, 2, 1), (100, 1024, 2, 1)])
 def test_fused_modes_match_separate_kernels(M, K, layout, elem):
     from gpu_helpers import bits, bf16_tensor, make_case, to_weight
     from nwc_b200 import _lib as L
