@@ -233,6 +233,10 @@ int nwc_attention_decode(void *stream, const uint16_t *qkv, const uint16_t *q_no
                          const int32_t *pos, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_len, float eps,
                          uint16_t *out, int *status);
 
+/* on != 0 sends every head size through the general attention kernel (one thread per cached position) instead of the
+   lane-per-dimension kernel that head sizes 64, 128 and 256 normally take (A/B tests). */
+void nwc_set_plain_attention(int on);
+
 /* a16 <- bf16(bf16(silu(gate)) * up) with gate = gate_up[0..I), up = gate_up[I..2I); a32 (may be NULL) as fp32 */
 int nwc_swiglu(void *stream, const uint16_t *gate_up, uint32_t I, uint16_t *a16, float *a32);
 

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "nwc_linear_launches": (I, [U64, U32, I, I]),
     "nwc_linear_prefill": (I, [P, P, P, P, P, P, P, U32, U32, P, P, P, U32, U64, U32, U32, I]),
     "nwc_attention_decode": (I, [P, P, P, P, P, P, P, P, P, U32, U32, U32, U32, ctypes.c_float, P, P]),
+    "nwc_set_plain_attention": (None, [I]),
     "nwc_swiglu": (I, [P, P, U32, P, P]),
     "nwc_argmax": (I, [P, P, U32, P, P, P, P, U32, U32]),
     "nwc_argmax_tp": (I, [P, P, U32, P, P, P, P, U32, U32, P, I, I]),

@@ -180,6 +180,144 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const uint16_t *_
     }
 }
 
+/* The same token of attention for head sizes of 64, 128 or 256 (VPL = head_dim / 32 values per lane), organised for
+   latency: one CTA of eight warps per query head, and inside a warp every lane owns VPL consecutive dimensions, so a cached
+   row is one coalesced load per warp, a score is VPL multiply-adds and five shuffles, and nothing between the prologue and
+   the final combine needs a CTA barrier.  Warp w takes the cached positions w, w + 8, ... with an online softmax (running
+   maximum, denominator and weighted value sum in fp32); the eight partial results meet once in shared memory.  The query
+   (per-head RMSNorm, rotary embedding, bf16 rounding per step as in the kernel above) is computed by every warp for its own
+   lanes - the rotary partner of a dimension lives in lane ^ 16 - and warp 0 also prepares the new key, appends key and value
+   to the cache (first query head of the group) and scores the current position from registers. */
+template <int VPL> struct LaneRow;
+template <> struct LaneRow<2> { using T = uint32_t; };
+template <> struct LaneRow<4> { using T = uint2; };
+template <> struct LaneRow<8> { using T = uint4; };
+template <int VPL> __device__ __forceinline__ void unpack_row(const typename LaneRow<VPL>::T &w, float (&v)[VPL]);
+template <> __device__ __forceinline__ void unpack_row<2>(const uint32_t &w, float (&v)[2]) { v[0] = __uint_as_float(w << 16); v[1] = __uint_as_float(w & 0xFFFF0000u); }
+template <> __device__ __forceinline__ void unpack_row<4>(const uint2 &w, float (&v)[4]) {
+    v[0] = __uint_as_float(w.x << 16); v[1] = __uint_as_float(w.x & 0xFFFF0000u); v[2] = __uint_as_float(w.y << 16); v[3] = __uint_as_float(w.y & 0xFFFF0000u);
+}
+template <> __device__ __forceinline__ void unpack_row<8>(const uint4 &w, float (&v)[8]) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) { v[2 * j] = __uint_as_float(u[j] << 16); v[2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u); }
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) attention_decode_lanes_kernel(const uint16_t *__restrict__ qkv, const uint16_t *__restrict__ q_norm, const uint16_t *__restrict__ k_norm,
+                                                                      const uint16_t *__restrict__ cos_t, const uint16_t *__restrict__ sin_t, uint16_t *__restrict__ k_cache,
+                                                                      uint16_t *__restrict__ v_cache, const int32_t *__restrict__ pos_ptr, uint32_t n_q, uint32_t n_kv,
+                                                                      uint32_t max_len, float eps, float scale, uint16_t *__restrict__ out, int *__restrict__ status) {
+    constexpr uint32_t hd = 32u * VPL, kWarps = 8;
+    using Row = typename LaneRow<VPL>::T;
+    __shared__ float part_max[kWarps], part_den[kWarps], part_acc[kWarps][hd];
+    const uint32_t head = blockIdx.x, kvh = head / (n_q / n_kv), tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, d0 = lane * VPL;
+    /* before the dependency wait: constants and what earlier tokens left (position, rotary row, norm weights, cached rows) */
+    const int32_t pos = *pos_ptr;
+    const bool pos_ok = pos >= 0 && (uint32_t)pos < max_len;
+    float cs[VPL], sn[VPL], qw[VPL], kw[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; j++) { cs[j] = sn[j] = 0.f; qw[j] = kw[j] = 1.f; }
+    const uint16_t *kc = k_cache + (uint64_t)kvh * max_len * hd, *vc = v_cache + (uint64_t)kvh * max_len * hd;
+    if (pos_ok) {
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            cs[j] = bf2f(cos_t[(uint64_t)pos * hd + d0 + j]); sn[j] = bf2f(sin_t[(uint64_t)pos * hd + d0 + j]);
+            if (q_norm) { qw[j] = bf2f(q_norm[d0 + j]); kw[j] = bf2f(k_norm[d0 + j]); }
+        }
+        const uint32_t lines_per_row = (hd * 2u + 127u) >> 7, lines = (uint32_t)pos * lines_per_row;
+        for (uint32_t i = tid; i < lines && i < 1024u; i += 256u) {          /* up to 128 KB of each: what L1 can hold */
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(kc) + (uint64_t)i * 128u));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(vc) + (uint64_t)i * 128u));
+        }
+    }
+    dependency_sync();
+    if (!pos_ok) { if (tid == 0) atomicExch(status, 1); return; }
+    /* per-head RMSNorm (Qwen3), then rotary embedding with bf16 rounding per operation; partner dimension = lane ^ 16 */
+    auto prepare = [&](const uint16_t *src, const float (&w)[VPL], bool norm, float (&v)[VPL]) {
+        Row raw = *reinterpret_cast<const Row *>(src + d0);
+        unpack_row<VPL>(raw, v);
+        if (norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPL; j++) ss += v[j] * v[j];
+            const float inv = rsqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+            for (int j = 0; j < VPL; j++) v[j] = bfround(w[j] * bfround(v[j] * inv));
+        }
+        const float sgn = lane < 16u ? -1.f : 1.f;
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            v[j] = bfround(bfround(v[j] * cs[j]) + bfround(sgn * other * sn[j]));
+        }
+    };
+    float q[VPL];
+    prepare(qkv + (uint64_t)head * hd, qw, q_norm != nullptr, q);
+#pragma unroll
+    for (int j = 0; j < VPL; j++) q[j] *= scale;
+    float m = -INFINITY, den = 0.f, acc[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; j++) acc[j] = 0.f;
+    auto absorb = [&](const float (&kr)[VPL], const float (&vr)[VPL]) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPL; j++) s = fmaf(q[j], kr[j], s);
+        s = warp_sum(s);
+        const float m_new = fmaxf(m, s), corr = __expf(m - m_new), p = __expf(s - m_new);
+        den = den * corr + p;
+#pragma unroll
+        for (int j = 0; j < VPL; j++) acc[j] = fmaf(p, vr[j], acc[j] * corr);
+        m = m_new;
+    };
+    if (warp == 0) {                                                 /* the current position: key and value of this token, from registers */
+        float k[VPL], v[VPL];
+        prepare(qkv + (uint64_t)(n_q + kvh) * hd, kw, k_norm != nullptr, k);
+        const Row vraw = *reinterpret_cast<const Row *>(qkv + (uint64_t)(n_q + n_kv + kvh) * hd + d0);
+        unpack_row<VPL>(vraw, v);
+        if (head == kvh * (n_q / n_kv)) {                            /* first query head of the group appends to the cache */
+#pragma unroll
+            for (int j = 0; j < VPL; j++) k_cache[((uint64_t)kvh * max_len + pos) * hd + d0 + j] = f2bf(k[j]);
+            *reinterpret_cast<Row *>(v_cache + ((uint64_t)kvh * max_len + pos) * hd + d0) = vraw;
+        }
+        absorb(k, v);
+    }
+    /* cached positions: two rows of each cache in flight per step */
+    int32_t t = (int32_t)warp;
+    for (; t + (int32_t)kWarps < pos; t += 2 * (int32_t)kWarps) {
+        const Row ka = *reinterpret_cast<const Row *>(kc + (uint64_t)t * hd + d0), kb = *reinterpret_cast<const Row *>(kc + (uint64_t)(t + kWarps) * hd + d0);
+        const Row va = *reinterpret_cast<const Row *>(vc + (uint64_t)t * hd + d0), vb = *reinterpret_cast<const Row *>(vc + (uint64_t)(t + kWarps) * hd + d0);
+        float kr[VPL], vr[VPL];
+        unpack_row<VPL>(ka, kr); unpack_row<VPL>(va, vr); absorb(kr, vr);
+        unpack_row<VPL>(kb, kr); unpack_row<VPL>(vb, vr); absorb(kr, vr);
+    }
+    if (t < pos) {
+        float kr[VPL], vr[VPL];
+        unpack_row<VPL>(*reinterpret_cast<const Row *>(kc + (uint64_t)t * hd + d0), kr); unpack_row<VPL>(*reinterpret_cast<const Row *>(vc + (uint64_t)t * hd + d0), vr);
+        absorb(kr, vr);
+    }
+    /* combine the eight warps: common maximum, then denominators and value sums rescaled to it, in warp order */
+    if (lane == 0) { part_max[warp] = m; part_den[warp] = den; }
+#pragma unroll
+    for (int j = 0; j < VPL; j++) part_acc[warp][d0 + j] = acc[j];
+    __syncthreads();
+    if (tid < hd) {
+        float top = part_max[0];
+        for (uint32_t w = 1; w < kWarps; w++) top = fmaxf(top, part_max[w]);
+        float total = 0.f, o = 0.f;
+        for (uint32_t w = 0; w < kWarps; w++) {
+            const float f = __expf(part_max[w] - top);                /* a warp without positions: exp(-inf) = 0 */
+            total = fmaf(part_den[w], f, total); o = fmaf(part_acc[w][tid], f, o);
+        }
+        out[(uint64_t)head * hd + tid] = f2bf(o / total);
+    }
+}
+
 /* a <- bf16(bf16(silu(gate)) * up), gate = gu[0..I), up = gu[I..2I); optional fp32 copy */
 __global__ void swiglu_kernel(const uint16_t *__restrict__ gu, uint32_t I, uint16_t *__restrict__ a16, float *__restrict__ a32) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -275,6 +413,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const uint16_t *__restrict_
     }
 }
 
+bool g_plain_attention = false;          /* tests: route every head size through the general kernel */
+
 template <class... Params, class... Args>
 cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, void *stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -303,9 +443,18 @@ NWC_EXPORT int nwc_attention_decode(void *stream, const uint16_t *qkv, const uin
     const size_t floats = 2 * (size_t)head_dim + max_len, need = (256u / (head_dim / 8u)) * (size_t)head_dim;   /* scores, or the group partials */
     const size_t smem = (floats > need ? floats : need) * sizeof(float);
     if (!nwc_setup()) return (int)cudaErrorNoDevice;             /* prepares this device's kernels on first use */
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    if (!g_plain_attention && (head_dim == 64 || head_dim == 128 || head_dim == 256) && !((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15u)) {
+        const dim3 grid(n_q), block(256);
+        if (head_dim == 64) return (int)launch(attention_decode_lanes_kernel<2>, grid, block, 0, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, max_len, eps, scale, out, status);
+        if (head_dim == 128) return (int)launch(attention_decode_lanes_kernel<4>, grid, block, 0, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, max_len, eps, scale, out, status);
+        return (int)launch(attention_decode_lanes_kernel<8>, grid, block, 0, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, max_len, eps, scale, out, status);
+    }
     return (int)launch(attention_decode_kernel, dim3(n_q), dim3(256), smem, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, head_dim,
                        max_len, eps, 1.0f / sqrtf((float)head_dim), out, status);
 }
+
+NWC_EXPORT void nwc_set_plain_attention(int on) { g_plain_attention = on != 0; }
 
 NWC_EXPORT int nwc_swiglu(void *stream, const uint16_t *gate_up, uint32_t I, uint16_t *a16, float *a32) {
     if (!I) return -1;
