@@ -273,12 +273,24 @@ def op_only(a, cfg):
     what, _, arg = a.op.partition(":")
     peak, kind = measured_peak()
 
-    def timed(call, reps=1):
+    def timed(call, reps=1, graph=True):
+        """Median microseconds per call; `reps` calls per measurement, replayed as one CUDA graph so that short kernels are
+        not timed by the host's launch rate."""
+        runner = None
+        if graph:
+            side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side): call()
+            torch.cuda.current_stream().wait_stream(side)
+            runner = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(runner):
+                for _ in range(reps): call()
         times = []
         for i in range(a.warmup + a.steps):
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
-            for _ in range(reps): call()
+            if runner is not None: runner.replay()
+            else:
+                for _ in range(reps): call()
             t1.record(); torch.cuda.synchronize()
             if i >= a.warmup: times.append(t0.elapsed_time(t1) / reps)
         return statistics.median(times) * 1e3                      # microseconds
@@ -288,7 +300,11 @@ def op_only(a, cfg):
         n = int(arg or 512)
         w = NWCWeight(synthetic_matrix(cfg.vocab, cfg.hidden, 1), layout=a.layout, elem="bf16")
         ids = torch.randint(0, cfg.vocab, (n,), device="cuda")
-        us = timed(lambda: w.gather(ids))
+        out_rows = torch.empty(n, w.K16, dtype=torch.bfloat16, device="cuda")
+        def lookup():
+            err = L.lib.nwc_gather(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(ids), n, L.ptr(out_rows), w.n, w.block, w.in_features, w.code)
+            if err: raise RuntimeError(f"nwc_gather error {err}")
+        us = timed(lookup, reps=4)
         out.update({"rows": n, "us": us, "kernel": "gather_kernel", "output_GBs": n * w.K16 * 2 / us / 1e3, "table_bits_per_weight": 8 * w.bytes / w.n})
     elif what == "attention":       # one token of grouped-query attention over POS cached positions
         pos = int(arg or 256)
@@ -310,7 +326,7 @@ def op_only(a, cfg):
     elif what == "encode":          # GPU encoder on a matrix that already lives in HBM
         M, K = (int(v) for v in (arg or "4096x4096").lower().split("x"))
         w = synthetic_matrix(M, K, 1)
-        us = timed(lambda: NWCWeight(w, layout=a.layout, elem=a.elem))
+        us = timed(lambda: NWCWeight(w, layout=a.layout, elem=a.elem), graph=False)        # the encoder synchronises: not capturable
         out.update({"shape": [M, K], "us": us, "Mweights_per_s": M * K / us, "kernel": "measure_kernel / pack_kernel (whole NWCWeight construction, host table build and allocation included)"})
         if a.vs_ref:                # the reference's own host encoder (one thread, as written) on the same matrix; bounded to 16 M weights
             import numpy as np
@@ -326,10 +342,10 @@ def op_only(a, cfg):
         M, K, T = (int(v) for v in (arg or "6144x2560x512").lower().split("x"))
         w = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
         x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
-        dense_us = timed(lambda: torch.nn.functional.linear(x, w.dequant()))
+        dense_us = timed(lambda: torch.nn.functional.linear(x, w.dequant()), graph=False)
         out.update({"shape": [M, K, T], "dequant_plus_dense_matmul_us": dense_us, "dense_TFLOPs": 2 * M * K * T / dense_us / 1e6})
         if w.linear_prefill(x) is not None:
-            us = timed(lambda: w.linear_prefill(x))
+            us = timed(lambda: w.linear_prefill(x), graph=False)
             out.update({"us": us, "TFLOPs": 2 * M * K * T / us / 1e6, "kernel": "prefill_kernel_layout2"})
     elif what == "native_fp8":      # the uncompressed fp8 weight-only matvec (bandwidth baseline of the fp8 configuration)
         from nwc_b200.weight import quantize_fp8

@@ -832,22 +832,15 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
        whole group (or the plan keeps per-cluster partials anyway); otherwise it is this CTA's share of a group that
        other CTAs of the cluster also hold, and goes to the cluster-level entries. */
     {
-        const uint32_t e = threadIdx.x >> 4, row = threadIdx.x & 15u;
-        /* all entries' groups and this row's values at once (independent loads, no chain of dependent ones); a group's
-           entries are adjacent, so "an earlier entry has my group" means somebody else leads it */
-        uint32_t group_of[kRingEntries]; float value_of[kRingEntries];
-#pragma unroll
-        for (uint32_t n = 0; n < kRingEntries; n++) { group_of[n] = share_group[n]; value_of[n] = share_value[n * 16u + row]; }
-        const uint32_t grp = share_group[e];
+        const uint32_t e = threadIdx.x >> 4, row = threadIdx.x & 15u, grp = share_group[e];
         bool leader = grp != kNoGroup;
-        float v = 0.f;
-#pragma unroll
-        for (uint32_t n = 0; n < kRingEntries; n++) {
-            const bool same = group_of[n] == grp;
-            if (same && n < e) leader = false;
-            if (same && n >= e) v += value_of[n];                 /* in entry order, whoever finished first */
-        }
+        for (uint32_t p = e; leader && p-- > 0u;) { const uint32_t gp = share_group[p]; if (gp == grp) leader = false; else if (gp != kNoGroup) break; }
         if (leader) {
+            float v = share_value[e * 16u + row];
+            for (uint32_t n = e + 1u; n < kRingEntries; n++) {
+                const uint32_t gn = share_group[n];
+                if (gn == grp) v += share_value[n * 16u + row]; else if (gn != kNoGroup) break;
+            }
             const uint32_t g0 = grp * slots;
             const bool inside = g0 >= c0 && g0 + slots <= c1;
             const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16u);

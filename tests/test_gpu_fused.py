@@ -141,3 +141,32 @@ def test_split_kernel_matches_the_single_warp_kernel_and_the_oracle(M, K, elem):
     want = O.bf16_to_f32(O.linear_bf16(p, O.bf16_to_f32(bits(x0[:K]))))
     assert rel_l2(run(0, True)[0], want) <= 2e-3
     assert L.lib.nwc_kernel_status(1) == 0
+
+
+@pytest.mark.parametrize("M,K", [(4100, 3000), (2368, 3008), (4736, 1504)])
+def test_row_groups_that_end_on_warp_boundaries(M, K):
+    """Shapes on which a CTA of the layout-2 ring kernel owns exactly two row groups and the boundary between them falls
+    between two of its warps: every warp then contributes only partial row sums, added up in shared memory.  Several weight
+    and activation draws, both entry points, each result against the oracle."""
+    from gpu_helpers import bits, make_case, to_weight
+    from nwc_b200 import _lib as L
+    pad = (K + 31) // 32 * 32
+    xtmp = torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
+    for seed in range(4):
+        p, _, _ = make_case(M, K, 0, 2, seed=M + 3 * K + seed, escapes=bool(seed & 1))
+        nw = to_weight(p)
+        g = torch.Generator().manual_seed(K + seed)
+        x0 = torch.randn(pad, generator=g).to(torch.bfloat16).cuda(); x0[K:] = 0
+        want = O.bf16_to_f32(O.linear_bf16(p, O.bf16_to_f32(bits(x0[:K]))))
+        for fused in (True, False):
+            y = torch.empty(M, dtype=torch.bfloat16, device="cuda")
+            if fused:
+                err = L.lib.nwc_linear_fused(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), 0, L.ptr(x0), None, None, None, None, 1e-6,
+                                             None, L.ptr(xtmp), None, None, L.ptr(nw.scratch), L.ptr(y), nw.n, nw.block, K, nw.code)
+            else:
+                err = L.lib.nwc_linear_x16(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), L.ptr(x0), None, None, L.ptr(nw.scratch), L.ptr(y),
+                                           nw.n, nw.block, K, nw.code)
+            assert err == 0
+            torch.cuda.synchronize()
+            assert rel_l2(O.bf16_to_f32(bits(y)), want) <= 2e-3, (seed, fused)
+    assert L.lib.nwc_kernel_status(1) == 0
