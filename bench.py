@@ -52,6 +52,7 @@ def parse():
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
+    ap.add_argument("--side-tables", type=int, default=1, help="0: layout 0 decoder-layer matrices on one warp per block instead of four along a side table (A/B)")
     ap.add_argument("--fixup", type=int, default=1, help="0: work splits of whole row groups instead of equal runs with in-kernel fix-up (A/B)")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     a = ap.parse_args()
@@ -438,7 +439,7 @@ def main():
         a.tp_reduce = eng.tp_reduce                                  # what actually runs (push needs layout 2 bf16)
     else:
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank if world > 1 else 0)
-        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch))
+        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch), side_tables=bool(a.side_tables))
     trace("weights built")
     if dist is not None: torch.cuda.synchronize(); dist.barrier()    # ranks start their first kernels together (bounded waits inside)
     eng.capture()

@@ -1488,15 +1488,17 @@ __global__ void __launch_bounds__(kSplitThreads, 3) small_split_kernel_layout0(c
         }
         return false;
     };
-    struct Ahead { uint32_t pass, cb, b, words, start, bytes; bool valid; } next;
-    /* metadata of the team's block after (pass, cb) and, by the team's first lane, the bulk copy of its stream into stage
-       `which`; every warp of the team runs this with the same arguments */
+    struct Ahead { uint32_t pass, cb, b, words, start, bytes, bit; bool valid; } next;
+    /* metadata of the team's block after (pass, cb) - header, offsets and this lane's side-table entry, all loads in flight
+       one block ahead - and, by the team's first lane, the bulk copy of its stream into stage `which`; every warp of the
+       team runs this with the same arguments */
     auto prefetch_block = [&](uint32_t pass, uint32_t cb, uint32_t which) {
         next.pass = pass; next.cb = cb; next.valid = settle(next.pass, next.cb);
         if (!next.valid) return;
         const uint32_t rb = next.pass * per_pass + my_group;
         next.b = rb * g.CB + next.cb;
         next.words = __ldg(a.hdr + (uint64_t)next.b * kLanes + lane);
+        next.bit = rp ? (uint32_t)__ldg(side + ((uint64_t)next.b * 3u + (rp - 1u)) * kLanes + lane) : 0u;     /* where this lane's row pair starts */
         const uint32_t base = __ldg(a.bases + next.b);
         uint32_t len;
         if (next.b + 1u < g.nb) len = __ldg(a.bases + next.b + 1u) - base;
@@ -1533,8 +1535,7 @@ __global__ void __launch_bounds__(kSplitThreads, 3) small_split_kernel_layout0(c
                 prefetch_block(pass, cb + share, which ^ 1u);
                 uint32_t total;
                 const uint32_t before = warp_exclusive_sum(cur.words, lane, total), base = __ldg(a.bases + cur.b);
-                /* where this lane's row pair starts inside its stream */
-                const uint32_t bit = rp ? (uint32_t)__ldg(side + ((uint64_t)cur.b * 3u + (rp - 1u)) * kLanes + lane) : 0u;
+                const uint32_t bit = cur.bit;
                 if (cur.bytes) {
                     const bool landed = mbar_wait(bar0 + 8u * which, (phases >> which) & 1u);
                     phases ^= 1u << which;
@@ -1643,7 +1644,7 @@ cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const Segme
     const Geometry g(a.M, a.K, 0);
     if (side) {                                                   /* four warps per block along the side table */
         const uint32_t share = g.CB > 1u ? kSplitTeams : 1u, passes = (g.groups + kSplitTeams / share - 1u) / (kSplitTeams / share);
-        const uint32_t grid = passes < 6u * (uint32_t)sms ? passes : 6u * (uint32_t)sms;
+        const uint32_t grid = passes < 3u * (uint32_t)sms ? passes : 3u * (uint32_t)sms;      /* one resident wave; CTAs loop over further passes */
         const size_t smem = kSplitFixedSmem + (size_t)g.K16 * (norm_like(in.mode) ? 4u : 2u);
         if (type_of(code) == kFp8) return launch_kernel(small_split_kernel_layout0<kFp8>, dim3(grid), dim3(kSplitThreads), smem, st, a, in, 4u, side);
         return launch_kernel(small_split_kernel_layout0<kBf16>, dim3(grid), dim3(kSplitThreads), smem, st, a, in, 4u, side);
