@@ -52,7 +52,7 @@ def parse():
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
-    ap.add_argument("--side-tables", type=int, default=1, help="0: layout 0 decoder-layer matrices on one warp per block instead of four along a side table (A/B)")
+    ap.add_argument("--side-tables", type=int, default=0, help="1: layout 0 decoder-layer matrices on four warps per block along a side table instead of one (A/B)")
     ap.add_argument("--fixup", type=int, default=1, help="0: work splits of whole row groups instead of equal runs with in-kernel fix-up (A/B)")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
     a = ap.parse_args()

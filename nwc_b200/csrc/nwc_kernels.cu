@@ -21,6 +21,7 @@
  * Interfaces replaced (reference: csrc/nwc_ops.cu): kern_block 446-550, kern_block1 632-703, kern_block2 884-981,
  * kern_f32_to_bf16_bias 553-565.
  */
+#include <cstdlib>
 #include <cooperative_groups.h>
 #include "nwc_decode.cuh"
 #include "nwc_async.cuh"
@@ -1644,7 +1645,7 @@ cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const Segme
     const Geometry g(a.M, a.K, 0);
     if (side) {                                                   /* four warps per block along the side table */
         const uint32_t share = g.CB > 1u ? kSplitTeams : 1u, passes = (g.groups + kSplitTeams / share - 1u) / (kSplitTeams / share);
-        const uint32_t grid = passes < 3u * (uint32_t)sms ? passes : 3u * (uint32_t)sms;      /* one resident wave; CTAs loop over further passes */
+        const uint32_t grid = passes < 3u * (uint32_t)sms ? passes : 3u * (uint32_t)sms;      /* one resident wave (measured: fewer, longer-running CTAs are slower); CTAs loop over further passes */
         const size_t smem = kSplitFixedSmem + (size_t)g.K16 * (norm_like(in.mode) ? 4u : 2u);
         if (type_of(code) == kFp8) return launch_kernel(small_split_kernel_layout0<kFp8>, dim3(grid), dim3(kSplitThreads), smem, st, a, in, 4u, side);
         return launch_kernel(small_split_kernel_layout0<kBf16>, dim3(grid), dim3(kSplitThreads), smem, st, a, in, 4u, side);

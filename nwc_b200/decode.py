@@ -176,7 +176,7 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push", side_tables=True):
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push", side_tables=False):
         """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None.
         tp_reduce, how the ranks' partial o / down outputs are summed:
           "push"  the row-parallel matvec stores its partial into every rank's exchange buffer over NVLink and the next
@@ -197,7 +197,11 @@ class DecodeEngine:
             self.peers = PeerBuffers(tp_group, weights.cfg.hidden)
         self.w, self.cfg, self.max_len, self.device = weights, weights.cfg, max_len, torch.device(device)
         self._opts = {}
-        if side_tables:     # layout-0 matrices small enough for the single-launch kernel: four warps per block along a side table
+        # Optional: layout-0 matrices small enough for the single-launch kernel decoded by four warps per block along a side
+        # table.  Off by default: measured on B200 (Qwen3-0.6B shapes) the launch is bound by its prologue (offsets -> bulk
+        # copy -> stream, table staging) and by kernel-to-kernel release, not by the serial walk of a block, and the fourfold
+        # warp count leaves no room for the next kernel's blocks to start early: 761 tokens/s with, 826 without.
+        if side_tables:
             for m in weights.matrices():
                 blocks = -(-m.out_features // 8) * -(-m.in_features // 512)
                 if m.layout == 0 and blocks <= 2 * L.SM_COUNT * 32 and m.K16 <= 40960: m.build_side_table()
