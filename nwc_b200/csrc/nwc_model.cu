@@ -208,6 +208,14 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+/* Long caches: gridDim.y CTAs per query head, CTA y takes an equal share of the cached positions (the first one also the
+   current position).  Each CTA leaves its (maximum, denominator, value sum) in a per-device work area; the CTA of a head that
+   arrives last at the head's counter combines the shares in split order and writes the output (so the result does not depend
+   on timing).  One work area per device: calls on one device must not overlap. */
+constexpr uint32_t kAttnMaxSplits = 8, kAttnMaxHeads = 256, kAttnMaxDim = 256;
+static __device__ float g_attn_share[kAttnMaxHeads * kAttnMaxSplits * (kAttnMaxDim + 2u)];
+static __device__ unsigned int g_attn_arrived[kAttnMaxHeads];
+
 template <int VPL>
 __global__ void __launch_bounds__(256) attention_decode_lanes_kernel(const uint16_t *__restrict__ qkv, const uint16_t *__restrict__ q_norm, const uint16_t *__restrict__ k_norm,
                                                                       const uint16_t *__restrict__ cos_t, const uint16_t *__restrict__ sin_t, uint16_t *__restrict__ k_cache,
@@ -216,7 +224,9 @@ __global__ void __launch_bounds__(256) attention_decode_lanes_kernel(const uint1
     constexpr uint32_t hd = 32u * VPL, kWarps = 8;
     using Row = typename LaneRow<VPL>::T;
     __shared__ float part_max[kWarps], part_den[kWarps], part_acc[kWarps][hd];
+    __shared__ unsigned int last_of_head;
     const uint32_t head = blockIdx.x, kvh = head / (n_q / n_kv), tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, d0 = lane * VPL;
+    const uint32_t split = blockIdx.y, splits = gridDim.y;
     /* before the dependency wait: constants and what earlier tokens left (position, rotary row, norm weights, cached rows) */
     const int32_t pos = *pos_ptr;
     const bool pos_ok = pos >= 0 && (uint32_t)pos < max_len;
@@ -275,7 +285,9 @@ __global__ void __launch_bounds__(256) attention_decode_lanes_kernel(const uint1
         for (int j = 0; j < VPL; j++) acc[j] = fmaf(p, vr[j], acc[j] * corr);
         m = m_new;
     };
-    if (warp == 0) {                                                 /* the current position: key and value of this token, from registers */
+    /* this CTA's share of the cached positions [t_begin, t_end) */
+    const int32_t share_len = (pos + (int32_t)splits - 1) / (int32_t)splits, t_begin = (int32_t)split * share_len, t_end = min(pos, t_begin + share_len);
+    if (warp == 0 && split == 0) {                                   /* the current position: key and value of this token, from registers */
         float k[VPL], v[VPL];
         prepare(qkv + (uint64_t)(n_q + kvh) * hd, kw, k_norm != nullptr, k);
         const Row vraw = *reinterpret_cast<const Row *>(qkv + (uint64_t)(n_q + n_kv + kvh) * hd + d0);
@@ -288,15 +300,15 @@ __global__ void __launch_bounds__(256) attention_decode_lanes_kernel(const uint1
         absorb(k, v);
     }
     /* cached positions: two rows of each cache in flight per step */
-    int32_t t = (int32_t)warp;
-    for (; t + (int32_t)kWarps < pos; t += 2 * (int32_t)kWarps) {
+    int32_t t = t_begin + (int32_t)warp;
+    for (; t + (int32_t)kWarps < t_end; t += 2 * (int32_t)kWarps) {
         const Row ka = *reinterpret_cast<const Row *>(kc + (uint64_t)t * hd + d0), kb = *reinterpret_cast<const Row *>(kc + (uint64_t)(t + kWarps) * hd + d0);
         const Row va = *reinterpret_cast<const Row *>(vc + (uint64_t)t * hd + d0), vb = *reinterpret_cast<const Row *>(vc + (uint64_t)(t + kWarps) * hd + d0);
         float kr[VPL], vr[VPL];
         unpack_row<VPL>(ka, kr); unpack_row<VPL>(va, vr); absorb(kr, vr);
         unpack_row<VPL>(kb, kr); unpack_row<VPL>(vb, vr); absorb(kr, vr);
     }
-    if (t < pos) {
+    if (t < t_end) {
         float kr[VPL], vr[VPL];
         unpack_row<VPL>(*reinterpret_cast<const Row *>(kc + (uint64_t)t * hd + d0), kr); unpack_row<VPL>(*reinterpret_cast<const Row *>(vc + (uint64_t)t * hd + d0), vr);
         absorb(kr, vr);
@@ -306,16 +318,40 @@ __global__ void __launch_bounds__(256) attention_decode_lanes_kernel(const uint1
 #pragma unroll
     for (int j = 0; j < VPL; j++) part_acc[warp][d0 + j] = acc[j];
     __syncthreads();
+    float top = part_max[0], total = 0.f, o = 0.f;
+    for (uint32_t w = 1; w < kWarps; w++) top = fmaxf(top, part_max[w]);
     if (tid < hd) {
-        float top = part_max[0];
-        for (uint32_t w = 1; w < kWarps; w++) top = fmaxf(top, part_max[w]);
-        float total = 0.f, o = 0.f;
         for (uint32_t w = 0; w < kWarps; w++) {
-            const float f = __expf(part_max[w] - top);                /* a warp without positions: exp(-inf) = 0 */
+            const float f = top == -INFINITY ? 0.f : __expf(part_max[w] - top);      /* a warp without positions: exp(-inf) = 0 */
             total = fmaf(part_den[w], f, total); o = fmaf(part_acc[w][tid], f, o);
         }
-        out[(uint64_t)head * hd + tid] = f2bf(o / total);
     }
+    if (splits == 1u) {
+        if (tid < hd) out[(uint64_t)head * hd + tid] = f2bf(o / total);
+        return;
+    }
+    /* several CTAs per head: leave this share, the last CTA to arrive combines all of them in split order */
+    float *mine = g_attn_share + ((uint64_t)head * kAttnMaxSplits + split) * (kAttnMaxDim + 2u);
+    if (tid < hd) mine[2u + tid] = o;
+    if (tid == 0) { mine[0] = top; mine[1] = total; }
+    __syncthreads();
+    if (tid == 0) { __threadfence(); last_of_head = atomicAdd(&g_attn_arrived[head], 1u) == splits - 1u ? 1u : 0u; }
+    __syncthreads();
+    if (!last_of_head) return;
+    __threadfence();
+    const float *shares = g_attn_share + (uint64_t)head * kAttnMaxSplits * (kAttnMaxDim + 2u);
+    float best = -INFINITY;
+    for (uint32_t y = 0; y < splits; y++) best = fmaxf(best, __ldcg(shares + y * (kAttnMaxDim + 2u)));
+    if (tid < hd) {
+        float den_all = 0.f, sum = 0.f;
+        for (uint32_t y = 0; y < splits; y++) {
+            const float *sh = shares + y * (kAttnMaxDim + 2u);
+            const float my = __ldcg(sh), f = my == -INFINITY ? 0.f : __expf(my - best);
+            den_all = fmaf(__ldcg(sh + 1), f, den_all); sum = fmaf(__ldcg(sh + 2u + tid), f, sum);
+        }
+        out[(uint64_t)head * hd + tid] = f2bf(sum / den_all);
+    }
+    if (tid == 0) g_attn_arrived[head] = 0u;
 }
 
 /* a <- bf16(bf16(silu(gate)) * up), gate = gu[0..I), up = gu[I..2I); optional fp32 copy */
@@ -445,7 +481,9 @@ NWC_EXPORT int nwc_attention_decode(void *stream, const uint16_t *qkv, const uin
     if (!nwc_setup()) return (int)cudaErrorNoDevice;             /* prepares this device's kernels on first use */
     const float scale = 1.0f / sqrtf((float)head_dim);
     if (!g_plain_attention && (head_dim == 64 || head_dim == 128 || head_dim == 256) && !((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15u)) {
-        const dim3 grid(n_q), block(256);
+        /* the grid is fixed when a decode graph is captured, the position is not: the split count follows the cache length */
+        const uint32_t splits = n_q > kAttnMaxHeads ? 1u : (max_len <= 384u ? 1u : (max_len <= 1024u ? 2u : (max_len <= 2048u ? 4u : kAttnMaxSplits)));
+        const dim3 grid(n_q, splits), block(256);
         if (head_dim == 64) return (int)launch(attention_decode_lanes_kernel<2>, grid, block, 0, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, max_len, eps, scale, out, status);
         if (head_dim == 128) return (int)launch(attention_decode_lanes_kernel<4>, grid, block, 0, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, max_len, eps, scale, out, status);
         return (int)launch(attention_decode_lanes_kernel<8>, grid, block, 0, stream, qkv, q_norm, k_norm, cos_t, sin_t, k_cache, v_cache, pos, n_q, n_kv, max_len, eps, scale, out, status);

@@ -31,10 +31,10 @@ def reference(qkv, q_norm, k_norm, cos, sin, k_cache, v_cache, pos, n_q, n_kv, h
 
 
 @pytest.mark.parametrize("hd,n_q,n_kv,norm", [(128, 16, 8, True), (128, 8, 1, False), (64, 4, 2, True), (256, 4, 4, False), (96, 4, 2, True)])
-@pytest.mark.parametrize("pos", [0, 1, 7, 8, 9, 100, 700])
-def test_attention_decode_matches_reference_and_the_general_kernel(hd, n_q, n_kv, norm, pos):
+@pytest.mark.parametrize("pos,max_len", [(0, 768), (1, 768), (7, 768), (8, 768), (9, 768), (100, 768), (700, 768), (100, 256), (5, 2304), (1000, 2304), (2300, 2304)])
+def test_attention_decode_matches_reference_and_the_general_kernel(hd, n_q, n_kv, norm, pos, max_len):
+    """max_len decides over how many CTAs a head's cached positions are split (1, 2, 4 or 8); each split count is covered."""
     from nwc_b200 import _lib as L
-    max_len = 768
     g = torch.Generator().manual_seed(hd + pos)
     rnd = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16)
     qkv, kc, vc = rnd((n_q + 2 * n_kv) * hd), rnd(n_kv, max_len, hd), rnd(n_kv, max_len, hd)
