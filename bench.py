@@ -52,6 +52,7 @@ def parse():
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
+    ap.add_argument("--prefetch-next", type=int, default=1, help="0: matvecs do not ask L2 for the next matrix's first bytes at their end (A/B)")
     ap.add_argument("--side-tables", type=int, default=0, help="1: layout 0 decoder-layer matrices on four warps per block along a side table instead of one (A/B)")
     ap.add_argument("--fixup", type=int, default=1, help="0: work splits of whole row groups instead of equal runs with in-kernel fix-up (A/B)")
     ap.add_argument("--dependent-launch", type=int, default=1, help="programmatic dependent launch between the decode-step kernels")
@@ -323,7 +324,7 @@ def op_only(a, cfg):
             if err: raise RuntimeError(f"nwc_attention_decode error {err}")
         us = timed(call, reps=8)
         cache_bytes = 2 * c.n_kv * pos * c.head_dim * 2
-        out.update({"positions": pos, "heads": [c.n_q, c.n_kv], "us": us, "kernel": "attention_decode_kernel", "cache_GBs": cache_bytes / us / 1e3})
+        out.update({"positions": pos, "heads": [c.n_q, c.n_kv], "us": us, "kernel": "attention_decode_lanes_kernel", "cache_GBs": cache_bytes / us / 1e3})
     elif what == "encode":          # GPU encoder on a matrix that already lives in HBM
         M, K = (int(v) for v in (arg or "4096x4096").lower().split("x"))
         w = synthetic_matrix(M, K, 1)
@@ -385,7 +386,7 @@ def matvec_shares(eng, weights, cfg, reps_target=24):
         torch.cuda.current_stream().wait_stream(side)
         kg = torch.cuda.CUDAGraph()
         with torch.cuda.graph(kg):
-            for i in range(reps): eng._linear(mats[i % len(mats)], x, y)
+            for i in range(reps): eng._linear(mats[i % len(mats)], x, y, then=(mats[(i + 1) % len(mats)], 0))
         for _ in range(3): kg.replay()
         torch.cuda.synchronize()
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -435,11 +436,11 @@ def main():
     max_len = a.prompt + 2 * (a.warmup + a.steps) + 16
     if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=0, tp_rank=rank, tp_world=world)
-        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD, tp_reduce=a.tp_reduce)
+        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch), tp_group=dist.group.WORLD, tp_reduce=a.tp_reduce, prefetch_next=bool(a.prefetch_next))
         a.tp_reduce = eng.tp_reduce                                  # what actually runs (push needs layout 2 bf16)
     else:
         weights = DecoderWeights.synthetic(cfg, layout=a.layout, elem=a.elem, seed=rank if world > 1 else 0)
-        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch), side_tables=bool(a.side_tables))
+        eng = DecodeEngine(weights, max_len=max_len, dependent_launch=bool(a.dependent_launch), side_tables=bool(a.side_tables), prefetch_next=bool(a.prefetch_next))
     trace("weights built")
     if dist is not None: torch.cuda.synchronize(); dist.barrier()    # ranks start their first kernels together (bounded waits inside)
     eng.capture()

@@ -183,6 +183,15 @@ typedef struct {
     int in_slot, out_slot;      /* -1: unused */
     uint32_t H;                 /* hidden size the buffers were allocated for */
     const uint16_t *side;
+    /* A hint, all zero = none: the matrix that the NEXT nwc_linear_fused[_opt] call on this stream will read (its `low`
+       pointer, n, K, elem and fused mode).  When both calls take the layout-2 ring kernel, this call's warps ask L2 for the
+       first bytes the next call will request as soon as their own last copy is under way, so HBM keeps streaming across
+       the kernel boundary.  A wrong hint costs bandwidth, never correctness; next_low must be readable device memory of
+       that matrix's size. */
+    const void *next_low;
+    uint64_t next_n;
+    uint32_t next_K;
+    int next_elem, next_mode;
 } nwc_fused_options;
 int nwc_linear_fused_opt(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                          const uint8_t *low, int mode, const uint16_t *x, const uint16_t *h_in, const uint16_t *delta,

@@ -75,9 +75,11 @@ for _name, (_res, _args) in _SIGNATURES.items():
 
 class FusedOptions(ctypes.Structure):
     """nwc_fused_options of include/nwc_ops.h: the exchange buffers of a tensor-parallel group with the push slots one
-    nwc_linear_fused_opt call reads (in_slot) and writes (out_slot), -1 = unused; and a layout-0 matrix's side table."""
+    nwc_linear_fused_opt call reads (in_slot) and writes (out_slot), -1 = unused; a layout-0 matrix's side table; and the hint that names the matrix the next call on the stream reads."""
     _fields_ = [("buffers", ctypes.c_void_p), ("rank", ctypes.c_int), ("world", ctypes.c_int), ("in_slot", ctypes.c_int),
-                ("out_slot", ctypes.c_int), ("H", ctypes.c_uint32), ("side", ctypes.c_void_p)]
+                ("out_slot", ctypes.c_int), ("H", ctypes.c_uint32), ("side", ctypes.c_void_p),
+                ("next_low", ctypes.c_void_p), ("next_n", ctypes.c_uint64), ("next_K", ctypes.c_uint32), ("next_elem", ctypes.c_int),
+                ("next_mode", ctypes.c_int)]
 
 
 VERSION = lib.nwc_info(0)

@@ -146,7 +146,11 @@ static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases
     if (token_path_fuses_input(elem, M, K, in_mode)) {              /* the ring kernel builds x itself (a plain x too) */
         SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
         a.fixup = 1u; a.push = push;
-        return (int)launch_segments(0, elem, sms, (cudaStream_t)stream, a, &in);
+        NextMatrix next{};
+        if (tp && tp->next_low && tp->next_K && tp->next_n && tp->next_n / tp->next_K <= 0xFFFFFFFFull && aligned16(tp->next_low) &&
+            layout_of(tp->next_elem) == 2 && type_of(tp->next_elem) <= 1 && tp->next_mode >= 0 && tp->next_mode <= 2)
+            next = NextMatrix{static_cast<const uint8_t *>(tp->next_low), (uint32_t)(tp->next_n / tp->next_K), tp->next_K, tp->next_elem, tp->next_mode, 1u};
+        return (int)launch_segments(0, elem, sms, (cudaStream_t)stream, a, &in, &next);
     }
     const uint16_t *xin = x;
     if (mode != kInputPlain) {

@@ -524,18 +524,7 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
    lane-contiguous) and every warp keeps kRingStages stages in flight.  Measured on B200 (4096 x 4096 up to
    151936 x 2560): 16 warps with 6-slot stages beat 32 warps with 2- or 3-slot stages and 8 warps with 12-slot stages,
    because the per-stage work (barrier wait, refill, bulk-copy operands) is issue-slot cost, not hidden latency. */
-#ifndef NWC_RING_SLOTS
-#define NWC_RING_SLOTS 6
-#define NWC_RING_STAGES 2
-#endif
-#ifndef NWC_RING_THREADS
-#define NWC_RING_THREADS 512
-#endif
-#ifndef NWC_RING_CTAS_PER_SM
-#define NWC_RING_CTAS_PER_SM 1
-#endif
-
-constexpr uint32_t kRingThreads = NWC_RING_THREADS, kRingSlots = NWC_RING_SLOTS, kRingStages = NWC_RING_STAGES, kRingCtasPerSm = NWC_RING_CTAS_PER_SM;
+constexpr uint32_t kRingThreads = 512, kRingSlots = 6, kRingStages = 2, kRingCtasPerSm = 1;
 constexpr uint32_t kRingStageBytes = kRingSlots * (256u + 512u);
 constexpr uint32_t kRingWarpBytes = kRingStages * kRingStageBytes;
 constexpr uint32_t kRingBarrierBytes = (kRingThreads / 32u) * kRingStages * 8u;
@@ -653,6 +642,38 @@ __device__ __noinline__ float2 ring_exceptions(uint32_t count, const uint8_t *__
     return make_float2(lo, hi);
 }
 
+/* What the ring kernel that FOLLOWS this launch on the stream reads first: its plan and the two planes of its matrix.
+   A kernel boundary leaves HBM idle for a few microseconds (the last CTAs' reductions, the SMs' hand-over, the first
+   copies' latency); weights do not depend on the activations, so every warp, once its own last copy is under way, asks
+   L2 for the bytes that the same warp of the next launch will request first.  They travel during the boundary and the
+   next launch's ring fills from L2.  nib == null: nothing known about the next launch. */
+struct NextFill {
+    const uint8_t *nib, *raw;
+    FlatPlan plan;
+    uint32_t blocks;            /* CTAs of the next launch                    */
+    uint32_t cluster_shift;     /* log2 of its cluster size                    */
+    uint32_t nib_unit, raw_unit;/* bytes of a unit in the two planes           */
+    uint32_t units;             /* most units per warp worth fetching ahead    */
+};
+__device__ __forceinline__ void l2_prefetch(const uint8_t *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+/* one lane per warp: the first units of warp `warp` of every CTA of the next launch that maps to this CTA */
+__device__ __forceinline__ void prefetch_next_fill(const NextFill &nx, uint32_t warp) {
+    if (nx.nib == nullptr) return;
+    for (uint32_t b = blockIdx.x; b < nx.blocks; b += gridDim.x) {
+        const uint32_t cl = b >> nx.cluster_shift, rank = b & ((1u << nx.cluster_shift) - 1u);
+        const uint32_t k0 = nx.plan.start(cl), k1 = nx.plan.start(cl + 1u);
+        const uint32_t c0 = k0 + (((k1 - k0) * rank) >> nx.cluster_shift), c1 = k0 + (((k1 - k0) * (rank + 1u)) >> nx.cluster_shift);
+        const uint32_t cn = c1 - c0, w0 = cn * warp / (kRingThreads / 32u), w1 = cn * (warp + 1u) / (kRingThreads / 32u);
+        const uint32_t n = min(w1 - w0, nx.units);
+        if (n) {
+            l2_prefetch(nx.nib + (uint64_t)(c0 + w0) * nx.nib_unit, n * nx.nib_unit);
+            l2_prefetch(nx.raw + (uint64_t)(c0 + w0) * nx.raw_unit, n * nx.raw_unit);
+        }
+    }
+}
+
 /* Shared memory behind the rings: what each warp contributes to row groups it shares with other warps of its CTA.
    A warp's run is contiguous, so only its first and its last row group can be shared: entry 2 * warp is the first one
    ("head"), entry 2 * warp + 1 the last one ("tail", used only when it differs from the head's group). */
@@ -663,7 +684,7 @@ constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 /* ELEM = fp8: the raw plane holds 3-bit fields, 96 bits per lane and PAIR of slots (384 B per pair), so the unit of all
    counting below is a pair of slots; the launcher takes this kernel only when every row group has an even number of slots. */
 template <int ELEM>
-__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in) {
+__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in, const NextFill nx) {
     constexpr uint32_t U = ELEM == kFp8 ? 2u : 1u;               /* slots per unit                                  */
     constexpr uint32_t kUnits = kRingSlots / U;                  /* units per stage                                 */
     constexpr uint32_t kNibUnit = 256u * U, kRawUnit = ELEM == kFp8 ? 384u : 512u;      /* bytes of a unit in the two planes */
@@ -763,6 +784,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
         d[0] = d[1] = d[2] = d[3] = 0.f; ex_lo = ex_hi = 0.f;
     };
     uint32_t buf = 0, parity = 0, todo = count;
+    bool hinted = false;                                         /* the next launch's first bytes are on their way to L2 */
 #pragma unroll 1
     for (uint32_t st = 0; st < n_stage; st++) {
         const uint32_t bar = bars + buf * 8u, src = ring + buf * kRingStageBytes;
@@ -816,16 +838,19 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
         }
         todo -= min(todo, kUnits);
         __syncwarp();
-        if (lane == 0 && left) {                                 /* refill the stage just read */
-            const uint32_t n = min(kUnits, left);
-            async_proxy_fence();
-            mbar_expect(bar, n * (kNibUnit + kRawUnit));
-            bulk_load(src, nib_next, n * kNibUnit, bar);
-            bulk_load(src + kRingSlots * 256u, raw_next, n * kRawUnit, bar);
-            nib_next += n * kNibUnit; raw_next += n * kRawUnit; left -= n;
+        if (lane == 0) {
+            if (left) {                                          /* refill the stage just read */
+                const uint32_t n = min(kUnits, left);
+                async_proxy_fence();
+                mbar_expect(bar, n * (kNibUnit + kRawUnit));
+                bulk_load(src, nib_next, n * kNibUnit, bar);
+                bulk_load(src + kRingSlots * 256u, raw_next, n * kRawUnit, bar);
+                nib_next += n * kNibUnit; raw_next += n * kRawUnit; left -= n;
+            } else if (!hinted) { prefetch_next_fill(nx, warp); hinted = true; }      /* this warp's last copy is under way */
         }
         if (++buf == kRingStages) { buf = 0; parity ^= 1u; }
     }
+    if (lane == 0 && !hinted) prefetch_next_fill(nx, warp);
     if (s != seg_first) flush();
     __syncthreads();
     /* Shared row groups: entries of one group are adjacent in entry order.  The first entry of each group adds the
@@ -957,10 +982,7 @@ static void make_flat_plan(const Geometry &g, uint32_t units_per_group, uint64_t
    Whole row groups per CTA need no second launch but leave some CTAs one group short; equal runs of slots keep every
    CTA busy to the end but need the finalize launch; measured on B200 that second launch and its kernel boundary cost
    4 to 5 us, the time one CTA streams about kFinalizeSlots slots. */
-#ifndef NWC_FINALIZE_SLOTS
-#define NWC_FINALIZE_SLOTS 256
-#endif
-constexpr uint64_t kFinalizeSlots = NWC_FINALIZE_SLOTS;
+constexpr uint64_t kFinalizeSlots = 256;
 /* How many clusters of 2 / 4 / 8 CTAs of the layout-2 kernel one device runs at once (a cluster needs its SMs inside one
    GPC, so fewer SMs are usable the larger the cluster); asked from the runtime once per device. */
 constexpr uint64_t kClusterSlots = 128;                          /* measured: a cluster launch pays off only beyond this many slots saved per CTA */
@@ -1010,10 +1032,7 @@ static void make_cta_plan_layout2(const Geometry &g0, int elem, int sms, FlatPla
    bit windows refill from shared memory with 32-bit addresses and no lane ever waits for a 4-byte global load.  Raw
    rows still come straight from global memory (coalesced 512 B per row and warp, two rows ahead).
    A block whose stream does not fit a stage (escape-heavy data) is decoded through the global-memory window instead. */
-#ifndef NWC_PREFIX_THREADS
-#define NWC_PREFIX_THREADS 1024
-#endif
-constexpr uint32_t kPrefixThreads = NWC_PREFIX_THREADS, kPrefixStageBytes = 2560, kPrefixWarpBytes = 2u * kPrefixStageBytes + 256u + 16u;
+constexpr uint32_t kPrefixThreads = 1024, kPrefixStageBytes = 2560, kPrefixWarpBytes = 2u * kPrefixStageBytes + 256u + 16u;
 constexpr uint32_t kPrefixSmemBytes = 16416u + (kPrefixThreads / 32u) * kPrefixWarpBytes;
 
 /* bit window over a stream staged in shared memory; table look-ups form their address with one shift and one IMAD */
@@ -1277,11 +1296,9 @@ constexpr uint32_t kSmallThreads = 256, kSmallWarps = kSmallThreads / 32u;
 /* warps that share one row group: the smallest power of two that covers its column blocks (at most the CTA) */
 __host__ __device__ static inline uint32_t small_group_warps(uint32_t CB) { return CB > 4u ? 8u : (CB > 2u ? 4u : (CB > 1u ? 2u : 1u)); }
 
-#ifndef NWC_SMALL_RESIDENT
-#define NWC_SMALL_RESIDENT 2
-#endif
+constexpr uint32_t kSmallResident = 2;      /* CTAs of the small kernel per SM the register budget is set for */
 template <int ELEM>
-__global__ void __launch_bounds__(kSmallThreads, NWC_SMALL_RESIDENT) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
+__global__ void __launch_bounds__(kSmallThreads, kSmallResident) small_kernel_layout0(const SegmentArgs a, const FusedInput in, const uint32_t four) {
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
     extern __shared__ __align__(128) uint8_t small_smem[];
     uint32_t *tables = reinterpret_cast<uint32_t *>(small_smem);
@@ -1693,7 +1710,28 @@ bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode) {
     return !g_disable_ring && ring_covers(code, g, input_mode);
 }
 
-cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input) {
+static uint32_t g_next_fill_stages = kRingStages;
+void set_next_fill_stages(uint32_t stages) { g_next_fill_stages = stages; }
+
+/* the ring kernel's view of the launch that follows (all zero when that launch is unknown or takes another kernel) */
+static NextFill make_next_fill(const NextMatrix *next, int sms) {
+    NextFill nx{};
+    if (!next || !next->low || g_next_fill_stages == 0u || g_disable_ring || next->M == 0u || next->K == 0u) return nx;
+    const Geometry g(next->M, next->K, layout_of(next->code));
+    if (!ring_covers(next->code, g, next->input_mode)) return nx;
+    const int elem = type_of(next->code);
+    uint32_t cluster;
+    make_cta_plan_layout2(g, elem, ring_ctas(g, next->input_mode, sms), nx.plan, cluster, next->fixup != 0u);
+    const uint32_t U = elem == kFp8 ? 2u : 1u;
+    nx.nib = next->low; nx.raw = next->low + g.nibble_plane_bytes();
+    nx.blocks = nx.plan.warps * cluster;
+    nx.cluster_shift = cluster == 8u ? 3u : (cluster == 4u ? 2u : (cluster == 2u ? 1u : 0u));
+    nx.nib_unit = 256u * U; nx.raw_unit = elem == kFp8 ? 384u : 512u;
+    nx.units = g_next_fill_stages * (kRingSlots / U);
+    return nx;
+}
+
+cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input, const NextMatrix *next) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(a.M, a.K, layout);
     a.splits_forced = a.splits;
@@ -1734,8 +1772,9 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     if (mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_covers(code, g, in.mode)) {
         uint32_t cluster;
         make_cta_plan_layout2(g, elem, ring_ctas(g, in.mode, sms), plan, cluster, a.fixup != 0u);
-        err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in)
-                           : launch_cluster_kernel(ring_kernel_layout2<kBf16>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in);
+        const NextFill nx = make_next_fill(next, sms);
+        err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                           : launch_cluster_kernel(ring_kernel_layout2<kBf16>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
         if (err == cudaSuccess && !plan.direct && !plan.fix)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;

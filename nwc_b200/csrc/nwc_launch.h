@@ -48,6 +48,15 @@ struct FusedInput {
     uint32_t world, slot;
     unsigned long long timeout_ns;   /* longest wait for the peers' flags */
 };
+/* The matrix that the launch following this one on the stream will read (a hint; null low = none).  When both launches
+   take the layout-2 ring kernel, this launch asks L2 for the next launch's first bytes while its own tail runs. */
+struct NextMatrix {
+    const uint8_t *low;
+    uint32_t M, K;
+    int code;                   /* layout / element code of the next matrix */
+    int input_mode;             /* FusedInputMode of the next launch        */
+    uint32_t fixup;             /* SegmentArgs::fixup of the next launch    */
+};
 /* side: per block and lane the bit positions where rows 2, 4, 6 begin (launch_side_table), or null */
 cudaError_t launch_small_layout0(int code, int sms, cudaStream_t st, const SegmentArgs &a, const FusedInput &in, const uint16_t *side = nullptr);
 cudaError_t launch_side_table(int code, cudaStream_t st, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, uint16_t *side, uint32_t nb);
@@ -59,7 +68,8 @@ void set_ring_kernels(bool on);               /* tests: switch the bulk-copy rin
 void set_fixup_plans(bool on);                /* tests: equal runs with in-kernel fix-up of cut row groups on / off */
 int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gave up; synchronises */
 /* input: how the token path builds its activation vector; only where token_path_fuses_input() says so, else null */
-cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input = nullptr);
+cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input = nullptr, const NextMatrix *next = nullptr);
+void set_next_fill_stages(uint32_t stages);   /* tests and tuning: ring stages per warp fetched ahead for the next launch (0 = off) */
 bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode);
 void configure_segment_kernels();
 int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_fix = false);

@@ -176,14 +176,17 @@ def rope_tables(cfg, max_len, device):
 
 
 class DecodeEngine:
-    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push", side_tables=False):
+    def __init__(self, weights: DecoderWeights, max_len=1024, device="cuda", dependent_launch=False, tp_group=None, tp_reduce="push", side_tables=False, prefetch_next=True):
         """tp_group: torch.distributed process group of the tensor-parallel ranks (weights.tp_world > 1), else None.
         tp_reduce, how the ranks' partial o / down outputs are summed:
           "push"  the row-parallel matvec stores its partial into every rank's exchange buffer over NVLink and the next
                   matvec's prologue adds them (no kernel of its own; layout 2 bf16 matrices, else "pull" is used);
           "pull"  one kernel of this library per sum reads the peers' partials over NVLink (also called "peer");
-          "nccl"  one NCCL all-reduce per sum."""
+          "nccl"  one NCCL all-reduce per sum.
+        prefetch_next: every matvec names the matrix of the matvec after it, whose first bytes then travel to L2 across the
+        kernel boundary (layout-2 matrices)."""
         L.require_cuda()
+        self.prefetch_next = bool(prefetch_next)
         self.dependent_launch = bool(dependent_launch)
         self.tp_group, self.tp_world = tp_group, weights.tp_world
         if self.tp_world > 1 and tp_group is None: raise ValueError("sharded weights need the process group of their ranks")
@@ -241,29 +244,35 @@ class DecodeEngine:
         return cls(DecoderWeights.from_checkpoint(path, device, rank, world), max_len=max_len, device=device, tp_group=tp_group, **kw)
 
     # ---- one token, eager: every call below is one or two kernels of this library on the current stream ----
-    def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None, tp_in=-1, tp_out=-1):
+    def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None, tp_in=-1, tp_out=-1, then=None):
         """y = W x with the activation prologue the mode names (0: x given; 1: x = RMSNorm(h_in + delta), h_out updated;
         2: x = SwiGLU(gate_up)), through nwc_linear_fused.  tp_in / tp_out: push slots of the tensor-parallel exchange
-        (delta = the ranks' summed partials of slot tp_in; y pushed to every rank's slot tp_out instead of written)."""
+        (delta = the ranks' summed partials of slot tp_in; y pushed to every rank's slot tp_out instead of written).
+        then = (weight, mode) of the matvec that follows on the stream: its first bytes are asked into L2 at this one's end."""
         out = y if isinstance(y, ctypes.c_void_p) else L.ptr(y)      # a raw device pointer: this rank's slot of the exchange buffer
-        tp = self._options(w, tp_in, tp_out)
+        tp = self._options(w, tp_in, tp_out, then if self.prefetch_next else None)
         err = L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, L.ptr(x), L.ptr(h_in),
                                         L.ptr(delta), L.ptr(h_out), L.ptr(norm_w), self.cfg.eps, L.ptr(gate_up), L.ptr(self.xtmp), None, L.ptr(w.scale),
                                         L.ptr(w.scratch), out, w.n, w.block, w.in_features, w.code, tp)
         if err: raise RuntimeError(f"nwc_linear_fused error {err}")
         self._count += L.lib.nwc_linear_launches(w.n, w.in_features, w.code, mode)
 
-    def _options(self, w, tp_in, tp_out):
+    def _options(self, w, tp_in, tp_out, then=None):
         """nwc_fused_options of one call (kept alive by the engine: the library reads them at launch time), or None."""
-        if w.side is None and tp_in < 0 and tp_out < 0: return None
-        key = (id(w), tp_in, tp_out)
+        if then is not None and ((then[0].code >> 4) & 15) != 2: then = None      # the hint serves layout-2 matrices only
+        if w.side is None and tp_in < 0 and tp_out < 0 and then is None: return None
+        key = (id(w), tp_in, tp_out, 0 if then is None else id(then[0]), 0 if then is None else then[1])
         if key not in self._opts:
             side = None if w.side is None else w.side.data_ptr()
             if tp_in >= 0 or tp_out >= 0:
                 p = self.peers
-                self._opts[key] = L.FusedOptions(ctypes.cast(p.table, ctypes.c_void_p), p.rank, p.world, tp_in, tp_out, p.hidden, side)
+                o = L.FusedOptions(ctypes.cast(p.table, ctypes.c_void_p), p.rank, p.world, tp_in, tp_out, p.hidden, side)
             else:
-                self._opts[key] = L.FusedOptions(None, 0, 0, -1, -1, 0, side)
+                o = L.FusedOptions(None, 0, 0, -1, -1, 0, side)
+            if then is not None:
+                nw, nmode = then
+                o.next_low, o.next_n, o.next_K, o.next_elem, o.next_mode = nw.low.data_ptr(), nw.n, nw.in_features, nw.code, nmode
+            self._opts[key] = o
         return ctypes.byref(self._opts[key])
 
     def _argmax(self, c, st):
@@ -333,16 +342,17 @@ class DecodeEngine:
         self._check(L.lib.nwc_gather(st(), L.ptr(e.data), L.ptr(e.bases), L.ptr(e.hdr), L.ptr(e.lut), L.ptr(e.low), L.ptr(self.cur), 1, L.ptr(h),
                                      e.n, e.block, e.in_features, e.code), "nwc_gather")
         for i, l in enumerate(w.layers):
-            self._linear(l["qkv"], None, self.qkv, mode=1, h_in=h, h_out=h_next, norm_w=l["in_norm"], tp_in=1 if i else -1)
+            after = (w.layers[i + 1]["qkv"], 1) if i + 1 < len(w.layers) else (w.lm_head, 1)
+            self._linear(l["qkv"], None, self.qkv, mode=1, h_in=h, h_out=h_next, norm_w=l["in_norm"], tp_in=1 if i else -1, then=(l["o"], 0))
             h, h_next = h_next, h
             self._check(L.lib.nwc_attention_decode(st(), L.ptr(self.qkv), L.ptr(l["q_norm"]), L.ptr(l["k_norm"]), L.ptr(self.cos), L.ptr(self.sin),
                                                    L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
                                                    c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
-            self._linear(l["o"], self.attn, None, tp_out=0)
-            self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, h_out=h_next, norm_w=l["post_norm"], tp_in=0)
+            self._linear(l["o"], self.attn, None, tp_out=0, then=(l["gate_up"], 1))
+            self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, h_out=h_next, norm_w=l["post_norm"], tp_in=0, then=(l["down"], 2))
             h, h_next = h_next, h
-            self._linear(l["down"], None, None, mode=2, gate_up=self.gu, tp_out=1)
-        self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, h_out=h_next, norm_w=w.final_norm, tp_in=1)
+            self._linear(l["down"], None, None, mode=2, gate_up=self.gu, tp_out=1, then=after)
+        self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, h_out=h_next, norm_w=w.final_norm, tp_in=1, then=(w.layers[0]["qkv"], 1))
         self._argmax(c, st)
 
     def close(self):
@@ -356,19 +366,20 @@ class DecodeEngine:
                                      e.n, e.block, e.in_features, e.code), "nwc_gather")
         delta = None
         for i, l in enumerate(w.layers):
-            self._linear(l["qkv"], None, self.qkv, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=l["in_norm"])
+            after = (w.layers[i + 1]["qkv"], 1) if i + 1 < len(w.layers) else (w.lm_head, 1)
+            self._linear(l["qkv"], None, self.qkv, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=l["in_norm"], then=(l["o"], 0))
             h, h_next = h_next, h
             self._check(L.lib.nwc_attention_decode(st(), L.ptr(self.qkv), L.ptr(l["q_norm"]), L.ptr(l["k_norm"]), L.ptr(self.cos), L.ptr(self.sin),
                                                    L.ptr(self.k_cache[i]), L.ptr(self.v_cache[i]), L.ptr(self.pos), c.n_q, c.n_kv, c.head_dim, self.max_len,
                                                    c.eps, L.ptr(self.attn), L.ptr(self.status)), "nwc_attention_decode")
-            self._linear(l["o"], self.attn, self.proj)
+            self._linear(l["o"], self.attn, self.proj, then=(l["gate_up"], 1))
             self._all_reduce(self.proj)
-            self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, delta=self.proj, h_out=h_next, norm_w=l["post_norm"])
+            self._linear(l["gate_up"], None, self.gu, mode=1, h_in=h, delta=self.proj, h_out=h_next, norm_w=l["post_norm"], then=(l["down"], 2))
             h, h_next = h_next, h
-            self._linear(l["down"], None, self.proj2, mode=2, gate_up=self.gu)
+            self._linear(l["down"], None, self.proj2, mode=2, gate_up=self.gu, then=after)
             self._all_reduce(self.proj2)
             delta = self.proj2
-        self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=w.final_norm)
+        self._linear(w.lm_head, None, self.logits, mode=1, h_in=h, delta=delta, h_out=h_next, norm_w=w.final_norm, then=(w.layers[0]["qkv"], 1))
         self._argmax(c, st)
 
     # ---- graph ----

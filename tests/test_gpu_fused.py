@@ -170,3 +170,37 @@ def test_row_groups_that_end_on_warp_boundaries(M, K):
             torch.cuda.synchronize()
             assert rel_l2(O.bf16_to_f32(bits(y)), want) <= 2e-3, (seed, fused)
     assert L.lib.nwc_kernel_status(1) == 0
+
+
+@pytest.mark.parametrize("elem", [0, 1])
+def test_next_matrix_hint_changes_no_result(elem):
+    """The hint that names the next call's matrix (its first bytes are asked into L2 at this call's end) leaves y bit for bit
+    as without it, whatever matrix it names: a larger one, a smaller one, the other element type, one of a layout the ring
+    kernel does not take (ignored), or the matrix itself."""
+    import ctypes
+    from gpu_helpers import bits, make_case, to_weight
+    from nwc_b200 import _lib as L
+    shapes = [(512, 1024), (2560, 4096), (100, 1024), (48, 1024), (4100, 3008)]
+    cases = [to_weight(make_case(M, K, elem, 2, seed=M + K, escapes=True)[0]) for M, K in shapes]
+    cases.append(to_weight(make_case(256, 1024, 1 - elem, 2, seed=5, escapes=False)[0]))
+    cases.append(to_weight(make_case(256, 1024, 0, 0, seed=6, escapes=False)[0]))
+    g = torch.Generator().manual_seed(9)
+    for nw in cases[:len(shapes)]:
+        K, M = nw.in_features, nw.out_features
+        pad = (K + 31) // 32 * 32
+        x0 = torch.randn(pad, generator=g).to(torch.bfloat16).cuda(); x0[K:] = 0
+        xtmp = torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
+        def run(opt):
+            y = torch.empty(M, dtype=torch.bfloat16, device="cuda")
+            err = L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), 0, L.ptr(x0), None, None, None, None,
+                                             1e-6, None, L.ptr(xtmp), None, L.ptr(nw.scale), L.ptr(nw.scratch), L.ptr(y), nw.n, nw.block, K, nw.code, opt)
+            assert err == 0, err
+            torch.cuda.synchronize()
+            return y
+        plain = run(None)
+        for nxt in cases:
+            for mode in (0, 1, 2):
+                o = L.FusedOptions(None, 0, 0, -1, -1, 0, None)
+                o.next_low, o.next_n, o.next_K, o.next_elem, o.next_mode = nxt.low.data_ptr(), nxt.n, nxt.in_features, nxt.code, mode
+                assert torch.equal(run(ctypes.byref(o)), plain), (M, K, nxt.out_features, nxt.in_features, mode)
+    assert L.lib.nwc_kernel_status(1) == 0
