@@ -52,6 +52,7 @@ def parse():
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
+    ap.add_argument("--pool", type=int, default=0, help="1: layout-2 matvecs on the kernel whose warps draw stages from a per-CTA pool instead of one fixed run per warp (A/B)")
     ap.add_argument("--prefetch-next", type=int, default=1, help="0: matvecs do not ask L2 for the next matrix's first bytes at their end (A/B)")
     ap.add_argument("--side-tables", type=int, default=0, help="1: layout 0 decoder-layer matrices on four warps per block along a side table instead of one (A/B)")
     ap.add_argument("--fixup", type=int, default=1, help="0: work splits of whole row groups instead of equal runs with in-kernel fix-up (A/B)")
@@ -192,6 +193,7 @@ def kernel_only(a, cfg):
     M, K = shapes[a.kernel] if a.kernel in shapes else tuple(int(v) for v in a.kernel.lower().split("x"))
     torch.cuda.set_device(0)
     L.lib.nwc_set_fixup_plans(int(a.fixup))
+    L.lib.nwc_set_pool_kernels(int(a.pool))
     L.lib.nwc_set_dependent_launch(int(a.dependent_launch))
     first = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
     copies = max(1, min(64, -(-(320 << 20) // first.bytes)))          # rotate over > 320 MB so that no launch finds its matrix in L2
@@ -374,7 +376,9 @@ def matvec_shares(eng, weights, cfg, reps_target=24):
     mode 0) inside one CUDA graph, CUDA events around the replay.  Returns {kind: (us per launch, bytes per launch, launches
     per token)}."""
     import torch
+    from nwc_b200 import _lib as L
     out = {}
+    L.lib.nwc_set_dependent_launch(1 if eng.dependent_launch else 0)       # launched as inside the decode step
     for kind in ("qkv", "o", "gate_up", "down", "lm_head"):
         mats = [weights.lm_head] if kind == "lm_head" else [l[kind] for l in weights.layers]
         total = sum(m.bytes for m in mats)
@@ -393,6 +397,7 @@ def matvec_shares(eng, weights, cfg, reps_target=24):
         k0.record(); kg.replay(); k1.record(); torch.cuda.synchronize()
         out[kind] = (k0.elapsed_time(k1) / reps * 1e3, total / len(mats), 1 if kind == "lm_head" else len(weights.layers), min(reps, len(mats)) * (total / len(mats)))
         del kg
+    L.lib.nwc_set_dependent_launch(0)
     return out
 
 
@@ -432,6 +437,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
     tp = is_tp(a, world)
+    L.lib.nwc_set_pool_kernels(int(a.pool))
     if tp and a.tp_reduce == "nccl": a.dependent_launch = 0         # NCCL kernels sit in the chain: keep plain stream order around them
     max_len = a.prompt + 2 * (a.warmup + a.steps) + 16
     if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence

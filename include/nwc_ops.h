@@ -114,6 +114,11 @@ void nwc_set_ring_kernels(int on);
    whose cut row groups are completed inside the kernel (A/B tests); on = 1 (default) restores them. */
 void nwc_set_fixup_plans(int on);
 
+/* on = 1 moves the layout-2 token matvec from the kernel in which every warp owns one contiguous run of its CTA's work
+   to the one whose warps draw their stages from a per-CTA pool (all warps end together, more bookkeeping per stage; A/B
+   tests); on = 0 (default) goes back. */
+void nwc_set_pool_kernels(int on);
+
 /* nwc_linear_bf16 with a bf16 activation vector for every layout (layout 0: bf16[K16]; layouts 1, 2: bf16[K rounded up
    to 32]): the decode loop keeps activations in bf16, which spares layout 0 the fp32 copy and the second mma pass. */
 int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,

@@ -262,3 +262,4 @@ NWC_EXPORT int nwc_linear_prefill(void *stream, const uint8_t *data, const uint3
 
 NWC_EXPORT void nwc_set_ring_kernels(int on) { set_ring_kernels(on != 0); }
 NWC_EXPORT void nwc_set_fixup_plans(int on) { set_fixup_plans(on != 0); }
+NWC_EXPORT void nwc_set_pool_kernels(int on) { set_pool_kernels(on != 0); }

@@ -654,6 +654,7 @@ struct NextFill {
     uint32_t cluster_shift;     /* log2 of its cluster size                    */
     uint32_t nib_unit, raw_unit;/* bytes of a unit in the two planes           */
     uint32_t units;             /* most units per warp worth fetching ahead    */
+    uint32_t pooled;            /* 1: the next launch's warps draw stages from their CTA's pool; its first 2 x 16 stages are the start of the CTA's run */
 };
 __device__ __forceinline__ void l2_prefetch(const uint8_t *p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
@@ -665,7 +666,9 @@ __device__ __forceinline__ void prefetch_next_fill(const NextFill &nx, uint32_t 
         const uint32_t cl = b >> nx.cluster_shift, rank = b & ((1u << nx.cluster_shift) - 1u);
         const uint32_t k0 = nx.plan.start(cl), k1 = nx.plan.start(cl + 1u);
         const uint32_t c0 = k0 + (((k1 - k0) * rank) >> nx.cluster_shift), c1 = k0 + (((k1 - k0) * (rank + 1u)) >> nx.cluster_shift);
-        const uint32_t cn = c1 - c0, w0 = cn * warp / (kRingThreads / 32u), w1 = cn * (warp + 1u) / (kRingThreads / 32u);
+        const uint32_t cn = c1 - c0;
+        uint32_t w0 = cn * warp / (kRingThreads / 32u), w1 = cn * (warp + 1u) / (kRingThreads / 32u);
+        if (nx.pooled) { w0 = min(warp * nx.units, cn); w1 = cn; }
         const uint32_t n = min(w1 - w0, nx.units);
         if (n) {
             l2_prefetch(nx.nib + (uint64_t)(c0 + w0) * nx.nib_unit, n * nx.nib_unit);
@@ -942,6 +945,276 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
     }
 }
 
+/* ---- layout 2, token path, second form: the warps of a CTA draw their stages from one pool ---------------------------
+   Measured on B200 with the kernel above (every warp owns one contiguous run of its CTA's units): the 16 warps of a CTA,
+   with equal runs, finish 10 % of the loop time apart (10 us of 100 on 57344 x 8192), and a warp that has finished leaves
+   its ring empty while its CTA waits for the slowest one.  Here the CTA's run is a sequence of stages (kUnits units, never
+   across a row-group boundary); a warp that has a ring buffer free takes the next stage from a shared-memory counter, so
+   all warps end within one stage of each other whatever their speeds were.
+   The result must not depend on which warp took which stage: every stage leaves its own partial sums (16 rows, fp32) in
+   shared memory, and the warp that completes a row group's last stage adds the group's stage partials in stage order.
+   Runs are equal per CTA (they may cut row groups).  A CTA works front to back, so the part of a row group that began in
+   an earlier CTA's run is complete EARLY in this CTA's run: it is published then (g_pool_partial, one entry per CTA), and
+   the CTA where the group began adds the later CTAs' parts, in CTA order, when its own part is complete at the end of its
+   run: no counter, no second launch, and normally no wait. */
+struct PoolShape {
+    uint32_t stages_per_group;  /* S = ceil(units per row group / units per stage)                     */
+    uint32_t group_slots;       /* G: row groups whose stage partials shared memory holds at once (2, 4, 8 or 16) */
+    uint32_t group_shift;       /* log2 G                                                                          */
+    FastDiv by_stages;
+};
+constexpr uint32_t kPoolEmpty = 0xFFFFFFFFu;                     /* g_pool_partial word that holds no value (a NaN pattern no sum is allowed to keep) */
+static __device__ unsigned int g_pool_partial[kFixCounters][16];  /* the part of its first row group that CTA i left for the CTA where the group began */
+constexpr uint32_t kPoolCtrlBytes = 256u;                        /* next stage | 15 spare words | 16 arrival counts | 16 generations | 16 floats for the prologue */
+constexpr unsigned long long kPoolWaitNs = 2000000000ull;        /* longest wait for another CTA's part */
+
+static inline uint32_t pool_units(int elem) { return elem == kFp8 ? kRingSlots / 2u : kRingSlots; }
+static inline PoolShape make_pool_shape(const Geometry &g, int elem) {
+    PoolShape ps;
+    const uint32_t units = elem == kFp8 ? g.slots / 2u : g.slots, per = pool_units(elem);
+    ps.stages_per_group = (units + per - 1u) / per;
+    const uint32_t S = ps.stages_per_group;
+    ps.group_shift = S >= 96u ? 1u : (S >= 24u ? 2u : (S >= 12u ? 3u : 4u));       /* more than the 16 warps' three stages each can span */
+    ps.group_slots = 1u << ps.group_shift;
+    ps.by_stages.set(S);
+    return ps;
+}
+static inline uint32_t pool_smem_bytes(const Geometry &g, int elem, int input_mode) {
+    const PoolShape ps = make_pool_shape(g, elem);
+    return (norm_like(input_mode) ? 2u : 1u) * ring_x_bytes(g) + ps.group_slots * ps.stages_per_group * 64u + kPoolCtrlBytes + kRingBarrierBytes + (kRingThreads / 32u) * kRingWarpBytes;
+}
+/* at least 6 stages per row group (the stage partials of the groups in flight must fit their 16 slots) */
+static inline bool pool_covers(int code, const Geometry &g, int input_mode) {
+    if (!ring_covers(code, g, input_mode)) return false;
+    return make_pool_shape(g, type_of(code)).stages_per_group >= 6u && pool_smem_bytes(g, type_of(code), input_mode) <= kRingMaxSmem;
+}
+
+template <int ELEM>
+__global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in, const NextFill nx, const PoolShape ps) {
+    constexpr uint32_t U = ELEM == kFp8 ? 2u : 1u;
+    constexpr uint32_t kUnits = kRingSlots / U;
+    constexpr uint32_t kNibUnit = 256u * U, kRawUnit = ELEM == kFp8 ? 384u : 512u;
+    constexpr uint32_t kBlockUnits = 16u / U;
+    constexpr uint32_t kNone = 0xFFFFFFFFu;
+    static_assert(kRingStages == 2u, "the loop below alternates between two ring buffers");
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const Geometry g(a.M, a.K, 2);
+    /* shared memory: x | RMSNorm weight (norm modes) | stage partials | control words | barriers | rings */
+    const uint32_t xs = smem_addr(ring_smem), x_bytes = ring_x_bytes(g), front = norm_like(in.mode) ? 2u * x_bytes : x_bytes;
+    const uint32_t S = ps.stages_per_group, G = ps.group_slots, part_bytes = G * S * 64u;
+    float *part = reinterpret_cast<float *>(ring_smem + front);
+    volatile uint32_t *ctrl = reinterpret_cast<volatile uint32_t *>(ring_smem + front + part_bytes);
+    uint32_t *next_stage = reinterpret_cast<uint32_t *>(ring_smem + front + part_bytes);
+    uint32_t *arrived = reinterpret_cast<uint32_t *>(ring_smem + front + part_bytes) + 16;
+    volatile uint32_t *generation = ctrl + 32;
+    float *scal = reinterpret_cast<float *>(ring_smem + front + part_bytes + 192u);
+    const uint32_t bars = xs + front + part_bytes + kPoolCtrlBytes + warp * (kRingStages * 8u);
+    const uint32_t ring = xs + front + part_bytes + kPoolCtrlBytes + kRingBarrierBytes + warp * kRingWarpBytes;
+    /* this CTA's run of units and its stages: the rest of the row group the run starts in, whole row groups, the start of a last one */
+    const uint32_t slots = g.slots / U;
+    const uint32_t c0 = plan.start(blockIdx.x), c1 = plan.start(blockIdx.x + 1u), cn = c1 - c0;
+    const uint32_t grp0 = plan.group_of(c0), off0 = c0 - grp0 * slots;
+    const uint32_t n0 = min(slots - off0, cn), S0 = (n0 + kUnits - 1u) / kUnits;
+    const uint32_t rest = cn - n0, whole = plan.group_of(rest), tail = rest - whole * slots;
+    const uint32_t n_stages = S0 + whole * S + (tail + kUnits - 1u) / kUnits;
+    const uint8_t *raw_plane = a.low + g.nibble_plane_bytes();
+    /* stage t: row group (counted from the run's first), stage inside the group's part, first unit inside the row group, units */
+    struct Stage { uint32_t gi, index, first, count, stages; };
+    auto describe = [&](uint32_t t) {
+        Stage s;
+        uint32_t end;
+        if (t < S0) { s.gi = 0u; s.index = t; s.first = off0 + t * kUnits; end = off0 + n0; s.stages = S0; }
+        else {
+            const uint32_t r = t - S0, q = ps.by_stages.div(r);
+            s.gi = 1u + q; s.index = r - q * S; s.first = s.index * kUnits;
+            end = q < whole ? slots : tail; s.stages = q < whole ? S : (tail + kUnits - 1u) / kUnits;
+        }
+        s.count = min(kUnits, end - s.first);
+        return s;
+    };
+    /* the block (if any) whose first unit lies in the stage: units from the stage's start to it, or kNone */
+    auto block_start = [&](const Stage &s) { const uint32_t d = (0u - s.first) & (kBlockUnits - 1u); return d < s.count ? d : kNone; };
+    constexpr uint32_t kEntryBytes = ELEM == kFp8 ? 2u : 3u;
+    /* ring buffer b holds stage T[b]; exception count of this lane and data offset of the block that starts in it */
+    uint32_t T0 = warp < n_stages ? warp : kNone, T1 = warp + kRingThreads / 32u < n_stages ? warp + kRingThreads / 32u : kNone;
+    uint32_t EC0 = 0, EC1 = 0, EB0 = 0, EB1 = 0, EP0 = 0, EP1 = 0;
+    auto issue = [&](uint32_t b, uint32_t t, uint32_t &ec, uint32_t &eb) {
+        const Stage s = describe(t);
+        const uint32_t u = (grp0 + s.gi) * slots + s.first;
+        if (lane == 0) {
+            const uint32_t bar = bars + b * 8u, dst = ring + b * kRingStageBytes;
+            mbar_expect(bar, s.count * (kNibUnit + kRawUnit));
+            bulk_load(dst, a.low + (uint64_t)u * kNibUnit, s.count * kNibUnit, bar);
+            bulk_load(dst + kRingSlots * 256u, raw_plane + (uint64_t)u * kRawUnit, s.count * kRawUnit, bar);
+        }
+        const uint32_t d = block_start(s);
+        ec = 0u; eb = 0u;
+        if (d != kNone) {
+            const uint32_t blk = (grp0 + s.gi) * g.CB + (s.first + d) / kBlockUnits;
+            ec = __ldg(a.hdr + (uint64_t)blk * kLanes + lane); eb = __ldg(a.bases + blk);
+        }
+    };
+    /* where this lane's entries of that block start (offset into data), and pull them towards L1 */
+    auto promote = [&](uint32_t ec, uint32_t eb, uint32_t &ep) {
+        uint32_t total;
+        const uint32_t before = warp_exclusive_sum(ec, lane, total);
+        ep = eb + before * kEntryBytes;
+        if (ec) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.data + ep));
+    };
+    if (lane == 0) {
+        for (uint32_t b = 0; b < kRingStages; b++) mbar_init(bars + b * 8u, 1u);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    if (T0 != kNone) issue(0u, T0, EC0, EB0);                    /* fill the ring before anything else */
+    if (T1 != kNone) issue(1u, T1, EC1, EB1);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    FixedTables t; t.load(a.lut);
+    NormWeights norm_regs;
+    stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes), norm_regs);
+    if (threadIdx.x < 48u) ctrl[threadIdx.x] = threadIdx.x == 0u ? 2u * (kRingThreads / 32u) : 0u;      /* (visible after build_activation's barrier) */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    promote(EC0, EB0, EP0); promote(EC1, EB1, EP1);
+    build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
+    const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * (ELEM == kFp8 ? 4u : 16u), xq = xs + (lane & 3u) * 16u;
+    bool hinted = false, failed = false;
+    uint32_t parity = 0;
+    /* One stage out of ring buffer b.  other_*: the other buffer's block, whose entries are pulled towards L1 at the end. */
+    auto consume = [&](uint32_t b, uint32_t &T, uint32_t &ec, uint32_t &eb, uint32_t &ep, uint32_t other_T, uint32_t other_ec, uint32_t other_eb, uint32_t &other_ep) {
+        const uint32_t bar = bars + b * 8u, src = ring + b * kRingStageBytes;
+        if (!mbar_wait(bar, parity)) { failed = true; return; }
+        const Stage s = describe(T);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        auto slot = [&](uint32_t j, uint32_t column_unit) {
+            uint32_t a0, a1, a2, a3;
+            if (ELEM == kFp8) {
+                const uint32_t f0 = lds32(src + j * 384u + lane16), f1 = lds32(src + j * 384u + 128u + lane16), f2 = lds32(src + j * 384u + 256u + lane16);
+                const uint2 n0v = lds64(src + (2u * j) * 256u + lane8), n1v = lds64(src + (2u * j + 1u) * 256u + lane8);
+                const uint4 x0 = lds128(xq + (2u * column_unit) * 64u), x1 = lds128(xq + (2u * column_unit + 1u) * 64u);
+                fixed_half<kFp8, 0>(t, n0v.x, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x0.x, x0.y);
+                fixed_half<kFp8, 2>(t, n0v.y, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x0.z, x0.w);
+                fixed_half<kFp8, 4>(t, n1v.x, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x1.x, x1.y);
+                fixed_half<kFp8, 6>(t, n1v.y, 0u, 0u, f0, f1, f2, a0, a1, a2, a3); mma_bf16(d, a0, a1, a2, a3, x1.z, x1.w);
+            } else {
+                const uint2 nib = lds64(src + j * 256u + lane8);
+                const uint4 raw = lds128(src + j * 512u + lane16);
+                const uint4 xv = lds128(xq + column_unit * 64u);
+                fixed_half<kBf16, 0>(t, nib.x, raw.x, raw.y, 0u, 0u, 0u, a0, a1, a2, a3);
+                mma_bf16(d, a0, a1, a2, a3, xv.x, xv.y);
+                fixed_half<kBf16, 2>(t, nib.y, raw.z, raw.w, 0u, 0u, 0u, a0, a1, a2, a3);
+                mma_bf16(d, a0, a1, a2, a3, xv.z, xv.w);
+            }
+        };
+        if (s.count == kUnits) {
+#pragma unroll
+            for (uint32_t j = 0; j < kUnits; j++) slot(j, s.first + j);
+        } else {
+#pragma unroll 1
+            for (uint32_t j = 0; j < s.count; j++) slot(j, s.first + j);
+        }
+        __syncwarp();
+        /* the buffer is read: draw the next stage and send for it before the bookkeeping below */
+        uint32_t fresh = 0u;
+        if (lane == 0) { fresh = atomicAdd(next_stage, 1u); async_proxy_fence(); }
+        fresh = __shfl_sync(0xffffffffu, fresh, 0);
+        const uint32_t mine_ec = ec, mine_ep = ep;
+        if (fresh < n_stages) { T = fresh; issue(b, fresh, ec, eb); }
+        else {
+            T = kNone;
+            if (!hinted) { if (lane == 0) prefetch_next_fill(nx, warp); hinted = true; }      /* this warp sends for nothing more */
+        }
+        float lo = d[0], hi = d[2];
+        const uint32_t bs = block_start(s);
+        if (bs != kNone) {                                       /* a block starts in this stage: its exceptions belong to the stage */
+            float2 e = ring_exceptions<ELEM>(mine_ec, a.data + mine_ep, xs, (s.first + bs) / kBlockUnits, lane);
+            e.x += __shfl_xor_sync(0xffffffffu, e.x, 1); e.x += __shfl_xor_sync(0xffffffffu, e.x, 2);
+            e.y += __shfl_xor_sync(0xffffffffu, e.y, 1); e.y += __shfl_xor_sync(0xffffffffu, e.y, 2);
+            lo += e.x; hi += e.y;
+        }
+        /* the stage's 16 row sums go to the slot of its row group; the slot is free once the group that used it before is added up */
+        const uint32_t gslot = s.gi & (G - 1u), turn = s.gi >> ps.group_shift;
+        {
+            uint32_t polls = 0;
+            while (generation[gslot] != turn && ++polls < kWaitPolls) {}
+            if (!__all_sync(0xffffffffu, polls < kWaitPolls)) { atomicExch(&g_kernel_status, kStatusWaitTimeout); failed = true; return; }
+        }
+        float *mine = part + (gslot * S + s.index) * 16u;
+        if ((lane & 3u) == 0u) { mine[lane >> 2] = lo; mine[(lane >> 2) + 8u] = hi; }
+        __syncwarp();
+        uint32_t last = 0u;
+        if (lane == 0) { __threadfence_block(); last = atomicAdd(arrived + gslot, 1u) + 1u == s.stages ? 1u : 0u; }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (other_T != kNone) promote(other_ec, other_eb, other_ep);
+        else if (T != kNone) promote(ec, eb, ep);
+        if (!last) return;
+        /* this warp completed the row group's part: add its stage partials in stage order (two interleaved chains, then the two) */
+        __threadfence_block();
+        const uint32_t row = lane & 15u, half = lane >> 4;
+        const float *p = part + gslot * S * 16u + row;
+        float v = 0.f;
+        for (uint32_t i = half; i < s.stages; i += 2u) v += p[i * 16u];
+        v += __shfl_down_sync(0xffffffffu, v, 16);
+        __syncwarp();
+        if (lane == 0) { arrived[gslot] = 0u; __threadfence_block(); generation[gslot] = turn + 1u; }
+        const uint32_t grp = grp0 + s.gi, g_first = grp * slots;
+        const bool begins_here = g_first >= c0, ends_here = g_first + slots <= c1;
+        if (begins_here && ends_here) { if (lane < 16u) emit_group(a, grp, row, v, 0x0000FFFFu); return; }
+        if (!begins_here) {                                      /* the group began in an earlier CTA's run: leave this part for that CTA */
+            if (lane < 16u) {
+                uint32_t w = __float_as_uint(v);
+                if (w == kPoolEmpty) w = 0x7FC00000u;            /* (another NaN) */
+                *reinterpret_cast<volatile unsigned int *>(&g_pool_partial[blockIdx.x][row]) = w;
+            }
+            return;
+        }
+        /* the group begins here and goes on in later CTAs: add their parts in CTA order */
+        const uint32_t holders = plan.owner(g_first + slots - 1u) - blockIdx.x;
+        bool ok = true;
+        if (lane < 16u) {
+            const unsigned long long t0 = global_timer_ns();
+            for (uint32_t h = 1; h <= holders && ok; h++) {
+                volatile unsigned int *src_word = &g_pool_partial[blockIdx.x + h][row];
+                uint32_t w = *src_word;
+                while (w == kPoolEmpty) {
+                    if (global_timer_ns() - t0 > kPoolWaitNs) { ok = false; break; }
+                    w = *src_word;
+                }
+                if (ok) { v += __uint_as_float(w); *src_word = kPoolEmpty; }
+            }
+        }
+        if (!__all_sync(0xffffffffu, ok)) { atomicExch(&g_kernel_status, kStatusWaitTimeout); v = __uint_as_float(0x7FC00000u); }
+        if (lane < 16u) emit_group(a, grp, row, v, 0x0000FFFFu);
+    };
+#pragma unroll 1
+    while ((T0 != kNone || T1 != kNone) && !failed) {
+        if (T0 != kNone) consume(0u, T0, EC0, EB0, EP0, T1, EC1, EB1, EP1);
+        if (T1 != kNone && !failed) consume(1u, T1, EC1, EB1, EP1, T0, EC0, EB0, EP0);
+        parity ^= 1u;
+    }
+    if (failed) {                                                /* gave up (status word set): let copies already issued land before the CTA leaves */
+        for (uint32_t b = 0; b < kRingStages; b++) for (uint32_t i = 0; i < 64u && !mbar_poll(bars + b * 8u, parity); i++) {}
+    }
+    if (lane == 0 && !hinted) prefetch_next_fill(nx, warp);
+    /* Tensor-parallel output: the CTA that finishes last publishes this rank's partial (as in the kernel above). */
+    if (a.push.world) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
+            __threadfence_system();
+            if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
+                own->push_done = 0u;
+                volatile uint32_t *count = &own->push_epoch[a.push.slot];
+                const uint32_t epoch = *count + 1u;
+                *count = epoch;
+                __threadfence_system();
+                for (uint32_t p = 0; p < a.push.world; p++)
+                    *reinterpret_cast<volatile uint32_t *>(&reinterpret_cast<CommControl *>(a.push.buf[p])->push_flag[a.push.slot][a.push.rank]) = epoch;
+            }
+        }
+    }
+}
+
 /* y[i] = bf16((sum of the partials of the warps that shared row i's row group, in warp order) * scale[i] + bias[i]) */
 __global__ void finalize_flat_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ bias, const float *__restrict__ scale,
                                      uint16_t *__restrict__ y, uint32_t M, uint32_t rows, const FlatPlan plan) {
@@ -1024,6 +1297,29 @@ static void make_cta_plan_layout2(const Geometry &g0, int elem, int sms, FlatPla
         cluster = 1u;
     }
     make_flat_plan(g, g.slots, cluster == 1u ? (uint64_t)sms : (uint64_t)room.count[cluster == 2u ? 1 : (cluster == 4u ? 2 : 3)], p, true);
+}
+
+/* Off unless switched on (set_pool_kernels): measured on B200 the pool's bookkeeping per stage (+30 % warp instructions)
+   costs more than the even finish gains - 263 against 242 us on 128256 x 8192, 122 against 116 us on 57344 x 8192. */
+static bool g_disable_pool = true;
+void set_pool_kernels(bool on) { g_disable_pool = !on; }
+
+/* Plan of the layout-2 token matvec for a matrix the ring kernels cover.  pool: the kernel whose warps draw stages from a
+   pool runs it - equal runs per CTA when the caller allows cut row groups (they are completed inside that kernel), else
+   whole row groups per CTA when that plan needs neither a cluster nor a second launch. */
+static void choose_ring_plan(int code, const Geometry &g, int input_mode, int sms, bool allow_fix, FlatPlan &plan, uint32_t &cluster, bool &pool) {
+    const int elem = type_of(code);
+    pool = !g_disable_pool && sms <= (int)kFixCounters && pool_covers(code, g, input_mode);
+    if (pool && allow_fix && !g_disable_fixup) {
+        Geometry gu = g;
+        if (elem == kFp8) gu.slots >>= 1;
+        make_flat_plan(gu, gu.slots, (uint64_t)sms, plan, false);
+        if (!plan.direct) plan.fix = 1u;
+        cluster = 1u;
+        return;
+    }
+    make_cta_plan_layout2(g, elem, ring_ctas(g, input_mode, sms), plan, cluster, allow_fix);
+    pool = pool && plan.direct && cluster == 1u;
 }
 
 /* ---- layouts 0 and 1, token path: lane streams staged in shared memory by bulk copies -------------------------------- */
@@ -1700,7 +1996,7 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_f
     FlatPlan plan;
     if (!g_disable_ring && layout == 0) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan); return plan.direct ? 1 : 2; }
     if (!g_disable_ring && layout == 1) { make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan); return plan.direct ? 1 : 2; }
-    if (!g_disable_ring && ring_covers(code, g, kInputPlain)) { uint32_t cluster; make_cta_plan_layout2(g, elem, ring_ctas(g, kInputPlain, sms), plan, cluster, allow_fix); return plan.direct || plan.fix ? 1 : 2; }
+    if (!g_disable_ring && ring_covers(code, g, kInputPlain)) { uint32_t cluster; bool pool; choose_ring_plan(code, g, kInputPlain, sms, allow_fix, plan, cluster, pool); return plan.direct || plan.fix ? 1 : 2; }
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
@@ -1721,7 +2017,9 @@ static NextFill make_next_fill(const NextMatrix *next, int sms) {
     if (!ring_covers(next->code, g, next->input_mode)) return nx;
     const int elem = type_of(next->code);
     uint32_t cluster;
-    make_cta_plan_layout2(g, elem, ring_ctas(g, next->input_mode, sms), nx.plan, cluster, next->fixup != 0u);
+    bool pool;
+    choose_ring_plan(next->code, g, next->input_mode, sms, next->fixup != 0u, nx.plan, cluster, pool);
+    nx.pooled = pool ? 1u : 0u;
     const uint32_t U = elem == kFp8 ? 2u : 1u;
     nx.nib = next->low; nx.raw = next->low + g.nibble_plane_bytes();
     nx.blocks = nx.plan.warps * cluster;
@@ -1771,8 +2069,15 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     if (input) in = *input;
     if (mode == kModeLinear && !g_disable_ring && a.splits_forced == 0 && ring_covers(code, g, in.mode)) {
         uint32_t cluster;
-        make_cta_plan_layout2(g, elem, ring_ctas(g, in.mode, sms), plan, cluster, a.fixup != 0u);
+        bool pool;
+        choose_ring_plan(code, g, in.mode, sms, a.fixup != 0u, plan, cluster, pool);
         const NextFill nx = make_next_fill(next, sms);
+        if (pool) {
+            const PoolShape ps = make_pool_shape(g, elem);
+            const size_t smem = pool_smem_bytes(g, elem, in.mode);
+            return elem == kFp8 ? launch_kernel(pool_kernel_layout2<kFp8>, dim3(plan.warps), dim3(kRingThreads), smem, st, a, plan, in, nx, ps)
+                                : launch_kernel(pool_kernel_layout2<kBf16>, dim3(plan.warps), dim3(kRingThreads), smem, st, a, plan, in, nx, ps);
+        }
         err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
                            : launch_cluster_kernel(ring_kernel_layout2<kBf16>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
         if (err == cudaSuccess && !plan.direct && !plan.fix)
@@ -1835,6 +2140,12 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(ring_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(ring_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(pool_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(pool_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    {                                                             /* no CTA has left a part of a row group for another one yet */
+        void *parts = nullptr;
+        if (cudaGetSymbolAddress(&parts, g_pool_partial) == cudaSuccess) cudaMemset(parts, 0xFF, sizeof(g_pool_partial)); else cudaGetLastError();
+    }
     cudaFuncSetAttribute(prefix_ring_kernel_layout1<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout1<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);

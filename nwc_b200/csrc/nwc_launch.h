@@ -65,6 +65,7 @@ bool dependent_launch();
 
 uint32_t choose_splits(const Geometry &g, int mode, int code, int sms);
 void set_ring_kernels(bool on);               /* tests: switch the bulk-copy ring kernels off to compare with the plain ones */
+void set_pool_kernels(bool on);               /* tests: layout-2 kernel whose warps draw stages from a per-CTA pool on / off */
 void set_fixup_plans(bool on);                /* tests: equal runs with in-kernel fix-up of cut row groups on / off */
 int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gave up; synchronises */
 /* input: how the token path builds its activation vector; only where token_path_fuses_input() says so, else null */

@@ -204,3 +204,43 @@ def test_next_matrix_hint_changes_no_result(elem):
                 o.next_low, o.next_n, o.next_K, o.next_elem, o.next_mode = nxt.low.data_ptr(), nxt.n, nxt.in_features, nxt.code, mode
                 assert torch.equal(run(ctypes.byref(o)), plain), (M, K, nxt.out_features, nxt.in_features, mode)
     assert L.lib.nwc_kernel_status(1) == 0
+
+
+@pytest.mark.parametrize("M,K,elem", [(10240, 8192, 0), (4100, 3000, 0), (7168, 1536, 0), (16, 28672, 0), (1280, 8192, 0), (2560, 4096, 1), (100, 1024, 0), (2368, 3008, 0)])
+def test_pool_kernel_repeats_bit_for_bit_and_agrees_with_the_ring_kernel(M, K, elem):
+    """Layout 2 on the kernel whose warps draw their stages from a per-CTA pool: which warp takes which stage changes from
+    run to run, the result must not (stage partials are added in stage order, the parts of a cut row group in CTA order) -
+    30 runs, bit for bit; and it agrees with the oracle and with the kernel of fixed per-warp runs, through both entry
+    points (equal runs with cut row groups; whole row groups)."""
+    from gpu_helpers import bits, make_case, to_weight
+    from nwc_b200 import _lib as L
+    p, _, _ = make_case(M, K, elem, 2, seed=7 * M + K, escapes=True)
+    nw = to_weight(p)
+    pad = (K + 31) // 32 * 32
+    g = torch.Generator().manual_seed(M + K)
+    x0 = torch.randn(pad, generator=g).to(torch.bfloat16).cuda(); x0[K:] = 0
+    xtmp = torch.zeros(pad, dtype=torch.bfloat16, device="cuda")
+    want = O.bf16_to_f32(O.linear_bf16(p, O.bf16_to_f32(bits(x0[:K]))))
+    def run(fused):
+        y = torch.empty(M, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            err = L.lib.nwc_linear_fused(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), 0, L.ptr(x0), None, None, None, None, 1e-6,
+                                         None, L.ptr(xtmp), None, L.ptr(nw.scale), L.ptr(nw.scratch), L.ptr(y), nw.n, nw.block, K, nw.code)
+        else:
+            err = L.lib.nwc_linear_x16(L.stream(), L.ptr(nw.data), L.ptr(nw.bases), L.ptr(nw.hdr), L.ptr(nw.lut), L.ptr(nw.low), L.ptr(x0), None, L.ptr(nw.scale), L.ptr(nw.scratch),
+                                       L.ptr(y), nw.n, nw.block, K, nw.code)
+        assert err == 0, err
+        torch.cuda.synchronize()
+        return y
+    try:
+        for fused in (True, False):
+            L.lib.nwc_set_pool_kernels(1)
+            first = run(fused)
+            assert rel_l2(O.bf16_to_f32(bits(first)), want) <= 2e-3, fused
+            for _ in range(30): assert torch.equal(run(fused), first), fused
+            L.lib.nwc_set_pool_kernels(0)
+            fixed_runs = run(fused)
+            assert rel_l2(O.bf16_to_f32(bits(fixed_runs)), O.bf16_to_f32(bits(first))) <= 2e-3, fused
+    finally:
+        L.lib.nwc_set_pool_kernels(0)
+    assert L.lib.nwc_kernel_status(1) == 0
