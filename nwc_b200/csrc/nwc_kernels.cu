@@ -597,11 +597,14 @@ __device__ __forceinline__ void emit_flat(const SegmentArgs &a, const FlatPlan &
     a.y[row] = bf16_round(v);
 }
 
-/* Arrival counters of the row groups that a run boundary cuts (fix-up plans): one per CTA of the grid, indexed by the
-   first CTA that holds a part of the group; zero between kernels (the last arriver clears its counter).  One set per
-   device, so launches that use fix-up plans must be in stream order on their device. */
-constexpr uint32_t kFixCounters = 1024;
-static __device__ unsigned int g_fix_arrivals[kFixCounters];
+/* Equal runs per CTA cut row groups.  Entry i: the 16 row sums (fp32 bits) of the part of its FIRST row group that CTA i
+   holds when that group began in an earlier CTA's run; kCutEmpty (a NaN pattern no sum is allowed to keep) = nothing
+   there.  Written by CTA i, read and emptied by the CTA where the group begins; empty between kernels.  One set per
+   device, so launches that use such plans must be in stream order on their device. */
+constexpr uint32_t kFixCounters = 1024;                          /* most CTAs of such a launch */
+constexpr uint32_t kCutEmpty = 0xFFFFFFFFu;
+constexpr unsigned long long kCutWaitNs = 2000000000ull;         /* longest wait for another CTA's part */
+static __device__ unsigned int g_cut_part[kFixCounters][16];
 
 /* The 16 finished rows of row group `grp`, one per lane of a half-warp (`sub` = lane & 15 = row inside the group, `mask`
    = the 16 lanes, all of which make this call): scale, bias and bf16 rounding as the reference's finalize step, then
@@ -874,6 +877,32 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
             const bool inside = g0 >= c0 && g0 + slots <= c1;
             const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16u);
             if (plan.direct ? (cluster_ctas == 1u || inside) : (plan.fix && inside)) emit_group(a, grp, row, v, half_mask);
+            else if (plan.fix) {
+                /* Equal runs: a row group cut by run boundaries.  A CTA whose run holds a later part of it leaves that part
+                   in its own entry of g_cut_part; the CTA where the group begins adds the later parts in CTA order (so the
+                   sum does not depend on timing), writes the rows and empties the entries again.  One trip through L2 after
+                   the last CTA's loop, no counter. */
+                if (g0 < c0) {
+                    uint32_t w = __float_as_uint(v);
+                    if (w == kCutEmpty) w = 0x7FC00000u;             /* (another NaN) */
+                    *reinterpret_cast<volatile unsigned int *>(&g_cut_part[blockIdx.x][row]) = w;
+                } else {
+                    const uint32_t holders = plan.owner(g0 + slots - 1u) - blockIdx.x;
+                    const unsigned long long t0 = global_timer_ns();
+                    bool ok = true;
+                    for (uint32_t h = 1; h <= holders && ok; h++) {
+                        volatile unsigned int *theirs = &g_cut_part[blockIdx.x + h][row];
+                        uint32_t w = *theirs;
+                        while (w == kCutEmpty) {
+                            if (global_timer_ns() - t0 > kCutWaitNs) { ok = false; break; }
+                            w = *theirs;
+                        }
+                        if (ok) { v += __uint_as_float(w); *theirs = kCutEmpty; }
+                    }
+                    if (!ok) { atomicExch(&g_kernel_status, kStatusWaitTimeout); v = __uint_as_float(0x7FC00000u); }
+                    emit_group(a, grp, row, v, half_mask);
+                }
+            }
             else if (cluster_ctas == 1u) emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner(g0), v);      /* one fp32 partial per CTA */
             else {
                 const uint32_t which = g0 < c0 ? 0u : 1u;            /* the group began before this CTA's run: its first group */
@@ -898,32 +927,6 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
             }
         }
         cluster.sync();                                             /* nobody leaves while its shared memory may still be read */
-    }
-    /* Fix-up plans: the row groups cut by this CTA's run boundaries (its first and its last one, at most) now hold this
-       CTA's partial.  One lane per group counts the arrival; the CTA that arrives last adds the partials in CTA order
-       (so the sum does not depend on timing), writes the rows and clears the counter. */
-    if (plan.fix) {
-        __syncthreads();                                            /* this CTA's partials are written */
-        if (warp == 0u && cn != 0u) {
-            const uint32_t half = lane >> 4, sub = lane & 15u, half_mask = 0xFFFFu << (16u * half);
-            const uint32_t first_group = plan.group_of(c0), last_group = plan.group_of(c1 - 1u);
-            const uint32_t grp = half ? last_group : first_group;
-            const uint32_t g0 = grp * slots;
-            const bool cut = !(g0 >= c0 && g0 + slots <= c1);
-            if (cut && !(half && last_group == first_group)) {
-                const uint32_t first_owner = plan.owner(g0), holders = plan.owner(g0 + slots - 1u) - first_owner + 1u;
-                uint32_t last = 0u;
-                if (sub == 0u) { __threadfence(); last = atomicAdd(&g_fix_arrivals[first_owner], 1u) == holders - 1u ? 1u : 0u; }
-                last = __shfl_sync(half_mask, last, 16u * half);
-                if (last) {
-                    __threadfence();
-                    float v = 0.f;
-                    for (uint32_t p = 0; p < holders; p++) v += __ldcg(a.y32 + (uint64_t)(grp * 16u + sub) * plan.parts + p);
-                    emit_group(a, grp, sub, v, half_mask);
-                    if (sub == 0u) g_fix_arrivals[first_owner] = 0u;
-                }
-            }
-        }
     }
     /* Tensor-parallel output: the CTA that finishes last publishes this rank's partial.  Every CTA orders its peer stores
        before its arrival with a system-scope fence; the last one raises this rank's flag in every buffer. */
@@ -954,7 +957,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
    The result must not depend on which warp took which stage: every stage leaves its own partial sums (16 rows, fp32) in
    shared memory, and the warp that completes a row group's last stage adds the group's stage partials in stage order.
    Runs are equal per CTA (they may cut row groups).  A CTA works front to back, so the part of a row group that began in
-   an earlier CTA's run is complete EARLY in this CTA's run: it is published then (g_pool_partial, one entry per CTA), and
+   an earlier CTA's run is complete EARLY in this CTA's run: it is published then (g_cut_part, one entry per CTA), and
    the CTA where the group began adds the later CTAs' parts, in CTA order, when its own part is complete at the end of its
    run: no counter, no second launch, and normally no wait. */
 struct PoolShape {
@@ -963,10 +966,7 @@ struct PoolShape {
     uint32_t group_shift;       /* log2 G                                                                          */
     FastDiv by_stages;
 };
-constexpr uint32_t kPoolEmpty = 0xFFFFFFFFu;                     /* g_pool_partial word that holds no value (a NaN pattern no sum is allowed to keep) */
-static __device__ unsigned int g_pool_partial[kFixCounters][16];  /* the part of its first row group that CTA i left for the CTA where the group began */
 constexpr uint32_t kPoolCtrlBytes = 256u;                        /* next stage | 15 spare words | 16 arrival counts | 16 generations | 16 floats for the prologue */
-constexpr unsigned long long kPoolWaitNs = 2000000000ull;        /* longest wait for another CTA's part */
 
 static inline uint32_t pool_units(int elem) { return elem == kFp8 ? kRingSlots / 2u : kRingSlots; }
 static inline PoolShape make_pool_shape(const Geometry &g, int elem) {
@@ -1163,8 +1163,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const Seg
         if (!begins_here) {                                      /* the group began in an earlier CTA's run: leave this part for that CTA */
             if (lane < 16u) {
                 uint32_t w = __float_as_uint(v);
-                if (w == kPoolEmpty) w = 0x7FC00000u;            /* (another NaN) */
-                *reinterpret_cast<volatile unsigned int *>(&g_pool_partial[blockIdx.x][row]) = w;
+                if (w == kCutEmpty) w = 0x7FC00000u;            /* (another NaN) */
+                *reinterpret_cast<volatile unsigned int *>(&g_cut_part[blockIdx.x][row]) = w;
             }
             return;
         }
@@ -1174,13 +1174,13 @@ __global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const Seg
         if (lane < 16u) {
             const unsigned long long t0 = global_timer_ns();
             for (uint32_t h = 1; h <= holders && ok; h++) {
-                volatile unsigned int *src_word = &g_pool_partial[blockIdx.x + h][row];
+                volatile unsigned int *src_word = &g_cut_part[blockIdx.x + h][row];
                 uint32_t w = *src_word;
-                while (w == kPoolEmpty) {
-                    if (global_timer_ns() - t0 > kPoolWaitNs) { ok = false; break; }
+                while (w == kCutEmpty) {
+                    if (global_timer_ns() - t0 > kCutWaitNs) { ok = false; break; }
                     w = *src_word;
                 }
-                if (ok) { v += __uint_as_float(w); *src_word = kPoolEmpty; }
+                if (ok) { v += __uint_as_float(w); *src_word = kCutEmpty; }
             }
         }
         if (!__all_sync(0xffffffffu, ok)) { atomicExch(&g_kernel_status, kStatusWaitTimeout); v = __uint_as_float(0x7FC00000u); }
@@ -1265,13 +1265,12 @@ static ClusterRoom cluster_room(int sms);
    groups per cluster of 2, 4 or 8 CTAs that split them (one launch each, bf16 y written by the kernel; the larger the
    cluster the finer the split but the fewer SMs), or equal runs of slots per CTA with per-CTA partials and the finalize
    launch.  Cost = slots the busiest CTA streams, plus what the extra synchronisation or launch is worth in slots. */
-/* With allow_fix the equal runs need no second launch: cut row groups are completed inside the kernel (FlatPlan::fix), which
-   costs a CTA barrier, an atomic with its fences and a few dependent loads at the kernel's end: measured about 2.5 us,
-   the time a CTA streams kFixSlots slots.
+/* With allow_fix the equal runs need no second launch: the parts of a cut row group meet in the CTA where the group
+   begins (FlatPlan::fix, g_cut_part), which costs one trip through L2 after the last CTA's loop: about 1 us, the time a
+   CTA streams kFixSlots slots.
    Cost of a candidate = what its busiest CTA streams, except that CTAs which finish early leave their share of the HBM
-   bandwidth to the others, so only half of the imbalance counts (measured: 10240 x 8192 runs 5 % faster on whole row
-   groups, 4 or 5 per CTA, than on equal runs with the fix-up), plus what the extra synchronisation or launch is worth. */
-constexpr uint64_t kFixSlots = 160;
+   bandwidth to the others, so only half of the imbalance counts, plus what the extra synchronisation or launch is worth. */
+constexpr uint64_t kFixSlots = 96;
 static bool g_disable_ring = false, g_disable_fixup = false;     /* A/B switches of the tests (set_ring_kernels, set_fixup_plans) */
 static void make_cta_plan_layout2(const Geometry &g0, int elem, int sms, FlatPlan &p, uint32_t &cluster, bool allow_fix = false) {
     Geometry g = g0;
@@ -2144,7 +2143,7 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(pool_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     {                                                             /* no CTA has left a part of a row group for another one yet */
         void *parts = nullptr;
-        if (cudaGetSymbolAddress(&parts, g_pool_partial) == cudaSuccess) cudaMemset(parts, 0xFF, sizeof(g_pool_partial)); else cudaGetLastError();
+        if (cudaGetSymbolAddress(&parts, g_cut_part) == cudaSuccess) cudaMemset(parts, 0xFF, sizeof(g_cut_part)); else cudaGetLastError();
     }
     cudaFuncSetAttribute(prefix_ring_kernel_layout1<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
     cudaFuncSetAttribute(prefix_ring_kernel_layout1<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
