@@ -181,7 +181,7 @@ int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, c
    side != NULL  (layout 0, matrices that take the single-launch small-matrix kernel) the table nwc_build_side_table made
                  for this matrix: four warps then decode each block in parallel, one row pair each.
 
-   Calls on one device must be in stream order (the kernels share per-device arrival counters). */
+   Calls on one device must be in stream order (the kernels share a per-device exchange area for row groups cut by CTA boundaries). */
 typedef struct {
     void *const *buffers;
     int rank, world;

@@ -27,7 +27,7 @@ struct SegmentArgs {
     int x_bf16;                 /* token path of layout 0: x is bf16[K16] instead of fp32[K16]                */
     uint32_t splits_forced;     /* the caller's own splits request (0 = none): forced splits take the plain kernels */
     uint32_t fixup;             /* 1: equal runs per CTA are allowed, row groups cut by a run boundary are completed inside
-                                   the kernel by the CTA that arrives last (per-device arrival counters: calls that set
+                                   the kernel by the CTA where the group begins (per-device exchange area: calls that set
                                    this must be in stream order on their device)                                    */
     PeerOutput push;            /* world > 0: y goes to every rank's exchange buffer instead of a.y                   */
 };

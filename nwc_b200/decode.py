@@ -236,12 +236,18 @@ class DecodeEngine:
     @classmethod
     def from_pretrained(cls, path, max_len=1024, device="cuda", tp_group=None, **kw):
         """Decode engine on an NWC checkpoint directory (see DecoderWeights.from_checkpoint); with a process group the
-        matrices are cut into this rank's tensor-parallel shards while loading."""
+        matrices are cut into this rank's tensor-parallel shards while loading, or - a directory of per-rank shards
+        written by `python -m nwc_b200.shard` - read as they are."""
         rank, world = 0, 1
         if tp_group is not None:
             import torch.distributed as dist
             rank, world = dist.get_rank(tp_group), dist.get_world_size(tp_group)
-        return cls(DecoderWeights.from_checkpoint(path, device, rank, world), max_len=max_len, device=device, tp_group=tp_group, **kw)
+        from . import shard as S
+        if S.is_sharded(path):                                       # per-rank folders written by `python -m nwc_b200.shard`: nothing to re-pack
+            weights = S.load_shard(S.rank_dir(path, rank, world), device)
+        else:
+            weights = DecoderWeights.from_checkpoint(path, device, rank, world)
+        return cls(weights, max_len=max_len, device=device, tp_group=tp_group, **kw)
 
     # ---- one token, eager: every call below is one or two kernels of this library on the current stream ----
     def _linear(self, w: NWCWeight, x, y, mode=0, h_in=None, delta=None, h_out=None, norm_w=None, gate_up=None, tp_in=-1, tp_out=-1, then=None):

@@ -178,3 +178,37 @@ def test_command_line_self_check_and_export(tmp_path, capsys):
     assert export.main([d, e]) == 0
     exported = load_file(os.path.join(e, "model.safetensors"))
     assert all(torch.equal(exported[k], v) for k, v in state.items() if k != "lm_head.weight")
+
+
+@pytest.mark.parametrize("layout,tied", [(2, False), (0, True)])
+def test_shard_files_hold_what_the_loader_repacks(tmp_path, layout, tied):
+    """`python -m nwc_b200.shard`: every per-rank folder must hold, tensor for tensor, what DecoderWeights.from_checkpoint
+    re-packs for that rank at load time (matrices and norm vectors), the engine must accept the directory, and a
+    directory written for two ranks must refuse a group of another size.  A one-rank "shard" directory decodes the
+    tokens of the checkpoint it was cut from."""
+    from nwc_b200 import convert, fuse, save_pretrained, shard as S
+    from nwc_b200.decode import DecodeEngine, DecoderWeights
+    hf_cfg, model = qwen3_model(hidden=1024, inter=2048, tied=tied)
+    fuse(model, layout=layout, verbose=False); convert(model, verbose=False, layout=layout)
+    d, out2, out1 = str(tmp_path / "ckpt"), str(tmp_path / "tp2"), str(tmp_path / "tp1")
+    save_pretrained(model, d, base_model="test"); del model
+    assert S.main([d, out2, "--world", "2"]) == 0 and S.is_sharded(out2) and not S.is_sharded(d)
+    for rank in (0, 1):
+        want = DecoderWeights.from_checkpoint(d, tp_rank=rank, tp_world=2)
+        got = S.load_shard(S.rank_dir(out2, rank, 2))
+        assert (got.tp_rank, got.tp_world, got.cfg, got.full_cfg) == (rank, 2, want.cfg, want.full_cfg)
+        assert (got.lm_head is got.embed) == (want.lm_head is want.embed)
+        for a, b in zip(got.matrices(), want.matrices()):
+            assert (a.out_features, a.in_features, a.layout, a.elem) == (b.out_features, b.in_features, b.layout, b.elem)
+            assert torch.equal(a.dequant(), b.dequant())
+            for name, t in b.tensors().items():
+                if name != "data": assert torch.equal(a.tensors()[name][:t.numel()].cpu(), t.cpu()), name     # (gap bytes of data are not defined)
+        for la, lb in zip(got.layers, want.layers):
+            for k in S.VECTOR_KINDS: assert torch.equal(la[k], lb[k])
+        assert torch.equal(got.final_norm, want.final_norm)
+    with pytest.raises(ValueError): S.rank_dir(out2, 0, 4)
+    S.shard_checkpoint(d, out1, 1, log=lambda *_: None)
+    prompt = list(range(5, 17))
+    ref = DecodeEngine.from_pretrained(d, max_len=64); ref.prefill(prompt); want = ref.generate(24).tolist()
+    eng = DecodeEngine.from_pretrained(out1, max_len=64); eng.prefill(prompt)
+    assert eng.generate(24).tolist() == want
