@@ -347,10 +347,10 @@ def op_only(a, cfg):
         M, K, T = (int(v) for v in (arg or "6144x2560x512").lower().split("x"))
         w = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
         x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
-        dense_us = timed(lambda: torch.nn.functional.linear(x, w.dequant()), graph=False)
+        dense_us = timed(lambda: torch.nn.functional.linear(x, w.dequant()), reps=4)
         out.update({"shape": [M, K, T], "dequant_plus_dense_matmul_us": dense_us, "dense_TFLOPs": 2 * M * K * T / dense_us / 1e6})
         if w.linear_prefill(x) is not None:
-            us = timed(lambda: w.linear_prefill(x), graph=False)
+            us = timed(lambda: w.linear_prefill(x), reps=4)
             out.update({"us": us, "TFLOPs": 2 * M * K * T / us / 1e6, "kernel": "prefill_kernel_layout2"})
     elif what == "native_fp8":      # the uncompressed fp8 weight-only matvec (bandwidth baseline of the fp8 configuration)
         from nwc_b200.weight import quantize_fp8

@@ -20,9 +20,9 @@
 
 namespace nwc {
 
-constexpr uint32_t kPfThreads = 512, kPfRows = 128, kPfK = 64, kPfMaxTokens = 256;
+constexpr uint32_t kPfDecodeThreads = 512, kPfThreads = kPfDecodeThreads + 32u /* + the warp that issues the MMAs */, kPfRows = 128, kPfK = 64, kPfMaxTokens = 256, kPfStages = 4, kPfAhead = 3, kPfAheadX = 2;
 constexpr uint32_t kPfABytes = kPfRows * 128u, kPfBBytes = kPfMaxTokens * 128u;
-constexpr uint32_t kPfSmem = 1024u /* alignment slack */ + 2u * kPfABytes + 2u * kPfBBytes + 64u;
+constexpr uint32_t kPfSmem = 1024u /* alignment slack */ + kPfStages * (kPfABytes + kPfBBytes) + 64u;
 
 /* shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart */
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -46,10 +46,17 @@ struct PrefillArgs {
     uint32_t T, ldx, ldy;
 };
 
+/* 16 bytes global -> shared without passing through registers; bytes beyond src_bytes are written as zeros */
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const PrefillArgs p) {
     extern __shared__ uint8_t pf_smem_raw[];
     const uint32_t base = (smem_addr(pf_smem_raw) + 1023u) & ~1023u;            /* swizzled tiles want 1024-byte alignment */
-    const uint32_t a_buf = base, b_buf = base + 2u * kPfABytes, bars = b_buf + 2u * kPfBBytes, tmem_slot = bars + 16u;
+    const uint32_t a_buf = base, b_buf = base + kPfStages * kPfABytes, bars = b_buf + kPfStages * kPfBBytes, tmem_slot = bars + kPfStages * 8u;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, r = lane >> 2, q = lane & 3u;
     const SegmentArgs &a = p.w;
     const Geometry g(a.M, a.K, 2);
@@ -57,72 +64,109 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
     const uint32_t nt = min(kPfMaxTokens, p.T - t0), N = (nt + 15u) & ~15u;         /* MMA N: multiple of 16 */
     uint32_t ncols = 32; while (ncols < N) ncols <<= 1;                              /* tensor-memory columns: power of two >= 32 */
     if (warp == 0) {
-        if (lane == 0) { mbar_init(bars, 1u); mbar_init(bars + 8u, 1u); mbar_init_fence(); }
+        if (lane == 0) { for (uint32_t s = 0; s < kPfStages; s++) mbar_init(bars + s * 8u, 1u); mbar_init_fence(); }
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(ncols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    const uint8_t *raw_plane = a.low + g.nibble_plane_bytes();
+    const uint32_t chunks = (a.K + kPfK - 1u) / kPfK, idesc = instr_desc_bf16(kPfRows, N);
+    const uint32_t rg = (m0 >> 4) + (warp >> 1);                                    /* this warp's row group */
+    /* The pipeline.  Chunk k (64 columns of K) lives in stage k % kPfStages.  Its X tile is copied asynchronously (16 bytes
+       per copy, straight to the swizzled position) and its compressed W slot is loaded into registers kPfAhead chunks
+       before it is needed (X two chunks); in iteration k the warps decode W(k) into the stage's A tile while the tensor
+       core still works on chunks k - 2 and k - 1, then one thread issues the MMAs of chunk k, then everybody waits for the
+       MMAs of chunk k - 2 (bounded) and refills that chunk's stage with the copies of chunk k + 2. */
+    auto load_w = [&](uint32_t k, uint2 &nib, uint4 &raw) {
+        const uint32_t slot = 2u * k + (warp & 1u);
+        nib = make_uint2(0u, 0u); raw = make_uint4(0u, 0u, 0u, 0u);
+        if (k < chunks && rg < g.groups && slot < g.slots) {
+            const uint64_t cell = ((uint64_t)rg * g.slots + slot) * kLanes + lane;
+            nib = ldg_stream64(a.low + cell * 8u);
+            raw = ldg_stream128(raw_plane + cell * 16u);
+        }
+    };
+    /* X tile: N rows of 128 bytes, zero beyond T and beyond K.  Decode thread i copies the 16-byte column i & 7 of rows
+       (i >> 3) + 64 j: the same column and, 64 rows = 8 swizzle groups further on, the same offset + 8192 j in the tile. */
+    const uint32_t xt = tid >> 3, xc = tid & 7u, x_smem = sw128(xt, xc);
+    const uint16_t *x_src = p.X + (uint64_t)(t0 + xt) * p.ldx + xc * 8u;
+    const uint64_t x_rows64 = 64ull * p.ldx;
+    auto load_x = [&](uint32_t k) {
+        if (k < chunks) {
+            const uint32_t bbase = b_buf + (k % kPfStages) * kPfBBytes + x_smem, col = k * kPfK + xc * 8u;
+            const uint32_t bytes = col < a.K ? min(16u, (a.K - col) * 2u) : 0u;
+#pragma unroll
+            for (uint32_t j = 0; j < kPfMaxTokens / 64u; j++) {
+                const uint32_t row = xt + 64u * j;
+                if (row < N) cp_async16(bbase + j * 8192u, row < nt ? x_src + j * x_rows64 + k * kPfK : p.X, row < nt ? bytes : 0u);
+            }
+        }
+        cp_async_commit();                                                           /* one group per chunk, empty or not */
+    };
+    /* exception count of this lane and data offset of the block (512 columns = 8 chunks) that holds chunk k; the next block's
+       are loaded while this one is in use and its entries are pulled towards L1 */
+    uint32_t cnt = 0, ebase = 0, cnt_next = 0, ebase_next = 0, before = 0, total = 0;
+    auto load_block = [&](uint32_t cb, uint32_t &c, uint32_t &b) {
+        c = 0u; b = 0u;
+        if (rg < g.groups && cb < g.CB) { const uint32_t blk = rg * g.CB + cb; c = __ldg(a.hdr + (uint64_t)blk * kLanes + lane); b = __ldg(a.bases + blk); }
+    };
+    uint2 n0, n1, n2; uint4 r0, r1, r2;
+    static_assert(kPfAhead == 3u, "three register sets travel ahead of the decode");
+    const bool decoder = warp < kPfDecodeThreads / 32u;                              /* the last warp only issues MMAs */
+    if (decoder) {
+        load_w(0u, n0, r0); load_w(1u, n1, r1); load_w(2u, n2, r2);
+        load_block(0u, cnt_next, ebase_next);
+        for (uint32_t k = 0; k < kPfAheadX; k++) load_x(k);
+    }
+    const uint64_t adesc0 = smem_desc_sw128(a_buf), bdesc0 = smem_desc_sw128(b_buf);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = lds32(tmem_slot);
     FixedTables tab; tab.load(a.lut);
-    const uint8_t *raw_plane = a.low + g.nibble_plane_bytes();
-    const uint32_t chunks = (a.K + kPfK - 1u) / kPfK, idesc = instr_desc_bf16(kPfRows, N);
-    const uint32_t rg = (m0 >> 4) + (warp >> 1);                                    /* this warp's row group */
     bool alive = true;
-    uint32_t uses[2] = {0u, 0u};
-    for (uint32_t k = 0; k < chunks; k++) {
-        const uint32_t s = k & 1u, abase = a_buf + s * kPfABytes, bbase = b_buf + s * kPfBBytes;
-        bool freed = true;
-        if (uses[s]) freed = mbar_wait(bars + s * 8u, (uses[s] - 1u) & 1u);          /* the MMAs that read this buffer are done */
-        if (!__syncthreads_and(freed)) { alive = false; break; }                     /* one decision for the whole CTA */
-        /* ---- W chunk: one super-chunk slot (16 rows x 32 columns) per warp ---- */
+    /* one chunk; (wn, wr) = the register set that holds its compressed slot and is reloaded with chunk k + kPfAhead (the
+       loop below rotates three sets by name: a register that still waits for its load must not be moved) */
+    auto step = [&](const uint32_t k, uint2 &wn, uint4 &wr) -> bool {
+        const uint32_t s = k % kPfStages, abase = a_buf + s * kPfABytes, bbase = b_buf + s * kPfBBytes;
+        if (decoder) {
+        if ((k & 7u) == 0u) {                                                        /* a new block of W begins */
+            cnt = cnt_next; ebase = ebase_next;
+            before = warp_exclusive_sum(cnt, lane, total);
+            load_block((k >> 3) + 1u, cnt_next, ebase_next);
+            if (cnt) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.data + ebase + (uint64_t)before * 3u));
+        }
+        /* ---- W chunk: one super-chunk slot (16 rows x 32 columns) per warp, from the registers loaded three chunks ago ---- */
         {
             const uint32_t slot = 2u * k + (warp & 1u), mm = (warp >> 1) * 16u + r, c = (warp & 1u) * 4u + q;
-            uint32_t f[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-            if (rg < g.groups && slot < g.slots) {
-                const uint64_t cell = ((uint64_t)rg * g.slots + slot) * kLanes + lane;
-                const uint2 nib = ldg_stream64(a.low + cell * 8u);
-                const uint4 raw = ldg_stream128(raw_plane + cell * 16u);
-                fixed_half<kBf16, 0>(tab, nib.x, raw.x, raw.y, 0u, 0u, 0u, f[0], f[1], f[2], f[3]);
-                fixed_half<kBf16, 2>(tab, nib.y, raw.z, raw.w, 0u, 0u, 0u, f[4], f[5], f[6], f[7]);
-            }
+            uint32_t f[8];
+            fixed_half<kBf16, 0>(tab, wn.x, wr.x, wr.y, 0u, 0u, 0u, f[0], f[1], f[2], f[3]);
+            fixed_half<kBf16, 2>(tab, wn.y, wr.z, wr.w, 0u, 0u, 0u, f[4], f[5], f[6], f[7]);
+            if (!(rg < g.groups && slot < g.slots)) { for (uint32_t e = 0; e < 8u; e++) f[e] = 0u; }
             /* f[0], f[2]: row r, columns 8q + 0..3;  f[1], f[3]: row r + 8;  f[4..7]: the same for columns 8q + 4..7 */
             sts64(abase + sw128(mm, c), f[0], f[2]);          sts64(abase + sw128(mm, c) + 8u, f[4], f[6]);
             sts64(abase + sw128(mm + 8u, c), f[1], f[3]);     sts64(abase + sw128(mm + 8u, c) + 8u, f[5], f[7]);
-            if (rg < g.groups && slot < g.slots) {            /* exceptions of this slot overwrite their +-0 placeholders */
-                const uint32_t b = rg * g.CB + (slot >> 4);
-                uint32_t total;
-                const uint32_t count = __ldg(a.hdr + (uint64_t)b * kLanes + lane), before = warp_exclusive_sum(count, lane, total);
-                if (total) {
-                    const uint8_t *ep = a.data + __ldg(a.bases + b) + (uint64_t)before * 3u;
-                    for (uint32_t e = 0; e < count; e++, ep += 3) {
-                        const uint32_t i = ep[0], j = i & 15u;
-                        if ((i >> 4) != (slot & 15u)) continue;
-                        const uint32_t col = (warp & 1u) * 32u + frag_col(lane, j), row = (warp >> 1) * 16u + frag_row(lane, j);
-                        sts16(abase + sw128(row, col >> 3) + (col & 7u) * 2u, (uint16_t)(ep[1] | (ep[2] << 8)));
-                    }
+            if (total && rg < g.groups && slot < g.slots) {   /* exceptions of this slot overwrite their +-0 placeholders */
+                __syncwarp();                                  /* (another lane's store above may cover the same 8 bytes) */
+                const uint8_t *ep = a.data + ebase + (uint64_t)before * 3u;
+                for (uint32_t e = 0; e < cnt; e++, ep += 3) {
+                    const uint32_t i = ep[0], j = i & 15u;
+                    if ((i >> 4) != (slot & 15u)) continue;
+                    const uint32_t col = (warp & 1u) * 32u + frag_col(lane, j), row = (warp >> 1) * 16u + frag_row(lane, j);
+                    sts16(abase + sw128(row, col >> 3) + (col & 7u) * 2u, (uint16_t)(ep[1] | (ep[2] << 8)));
                 }
             }
         }
-        /* ---- X chunk: N rows of 128 bytes, zero beyond T and beyond K ---- */
-        for (uint32_t i = tid; i < N * 8u; i += kPfThreads) {
-            const uint32_t t = i >> 3, c = i & 7u, col = k * kPfK + c * 8u;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (t < nt && col < a.K) {
-                const uint16_t *src = p.X + (uint64_t)(t0 + t) * p.ldx + col;
-                if (col + 8u <= a.K) v = __ldg(reinterpret_cast<const uint4 *>(src));
-                else { uint16_t tmp[8] = {0, 0, 0, 0, 0, 0, 0, 0}; for (uint32_t e = 0; col + e < a.K; e++) tmp[e] = src[e]; v = *reinterpret_cast<uint4 *>(tmp); }
-            }
-            sts128(bbase + sw128(t, c), v);
+        load_w(k + kPfAhead, wn, wr);
+        cp_async_wait<(int)kPfAheadX - 1>();                                          /* this thread's copies of the X tile of chunk k have landed */
+        async_proxy_fence();                                                         /* generic-proxy writes (stores above, copies) -> visible to the tensor core */
         }
-        async_proxy_fence();                                                       /* generic-proxy stores -> visible to the tensor core */
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
+        if (!__syncthreads_and(alive)) { alive = false; return false; }              /* one decision for the whole CTA */
+        if (!decoder) {                                                              /* the MMAs of chunk k go out while the other warps decode chunk k + 1 */
+          if (lane == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t adesc = smem_desc_sw128(abase), bdesc = smem_desc_sw128(bbase);
+            const uint64_t adesc = adesc0 + ((s * kPfABytes) >> 4), bdesc = bdesc0 + ((s * kPfBBytes) >> 4);
 #pragma unroll
             for (uint32_t kk = 0; kk < kPfK / 16u; kk++) {                          /* 16 bf16 = 32 bytes further along K: +2 in the descriptor's address field */
                 const uint32_t accumulate = (k | kk) ? 1u : 0u;
@@ -130,17 +174,31 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
                              ::"r"(tmem), "l"(adesc + 2u * kk), "l"(bdesc + 2u * kk), "r"(idesc), "r"(accumulate) : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bars + s * 8u) : "memory");
+          }
+          __syncwarp();
+          return true;
         }
-        uses[s]++;
+        /* The stage that chunk k + kPfAheadX will use held chunk k - 2: free once those MMAs are done.  Waiting for chunk
+           k - 2, not k - 1, keeps two chunks' MMAs in flight behind the decode (the wait costs the MMA's latency). */
+        static_assert(kPfAheadX + 2u == kPfStages, "the refilled stage is the one of chunk k - 2");
+        if (k >= 2u) alive = mbar_wait(bars + ((k - 2u) % kPfStages) * 8u, ((k - 2u) / kPfStages) & 1u);
+        if (alive) load_x(k + kPfAheadX); else cp_async_commit();
+        return true;
+    };
+    for (uint32_t k = 0; k < chunks; k += 3u) {
+        if (!step(k, n0, r0)) break;
+        if (k + 1u < chunks && !step(k + 1u, n1, r1)) break;
+        if (k + 2u < chunks && !step(k + 2u, n2, r2)) break;
     }
-    /* ---- epilogue: wait for the last MMAs of both buffers, read the accumulator, scale, bias, round, store ---- */
+    cp_async_wait<0>();
+    /* ---- epilogue: wait for the last MMAs, read the accumulator, scale, bias, round, store ---- */
     {
         bool done = alive;
-        for (uint32_t s = 0; s < 2u && done; s++) if (uses[s]) done = mbar_wait(bars + s * 8u, (uses[s] - 1u) & 1u);
+        if (done && chunks) done = mbar_wait(bars + ((chunks - 1u) % kPfStages) * 8u, ((chunks - 1u) / kPfStages) & 1u);
         alive = __syncthreads_and(done);
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (alive) {
+    if (alive && decoder) {
         const uint32_t quarter = warp & 3u, row = m0 + quarter * 32u + lane;       /* a warp reads the 32 tensor-memory lanes of its quarter */
         const float sc = (a.scale && row < a.M) ? __ldg(a.scale + row) : 1.f, bi = (a.bias && row < a.M) ? bf16_to_float(__ldg(a.bias + row)) : 0.f;
         for (uint32_t c0 = (warp >> 2) * 16u; c0 < N; c0 += 64u) {                 /* the four warps of a quarter take every fourth 16-column group */
