@@ -311,6 +311,13 @@ def op_only(a, cfg):
             if err: raise RuntimeError(f"nwc_gather error {err}")
         us = timed(lookup, reps=4)
         out.update({"rows": n, "us": us, "kernel": "gather_kernel", "output_GBs": n * w.K16 * 2 / us / 1e3, "table_bits_per_weight": 8 * w.bytes / w.n})
+        if a.layout == 0:           # the same lookup with the side table: every row's walk starts at its row pair
+            w.build_side_table()
+            def lookup_side():
+                err = L.lib.nwc_gather_side(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), L.ptr(ids), n, L.ptr(out_rows), w.n, w.block,
+                                            w.in_features, w.code, L.ptr(w.side))
+                if err: raise RuntimeError(f"nwc_gather_side error {err}")
+            out["us_with_side_table"] = timed(lookup_side, reps=4)
     elif what == "attention":       # one token of grouped-query attention over POS cached positions
         pos = int(arg or 256)
         c = cfg

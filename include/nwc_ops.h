@@ -210,6 +210,12 @@ int nwc_linear_fused_opt(void *stream, const uint8_t *data, const uint32_t *base
    parallel instead of one warp walking each 128-symbol stream from its first bit.  Returns 0, -1 for a bad shape or a
    layout other than 0, or a CUDA error. */
 uint64_t nwc_side_table_bytes(uint64_t M, uint32_t K);
+/* nwc_gather for a layout-0 matrix with its side table: the walk of a lane's stream starts at the row pair that holds
+   the requested row (at most one row is decoded and dropped instead of up to seven).  side == NULL is nwc_gather;
+   a side table with another layout returns -1.  Bit-identical output. */
+int nwc_gather_side(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                    const uint8_t *low, const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block,
+                    uint32_t K, int elem, const uint16_t *side);
 int nwc_build_side_table(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, uint16_t *side,
                          uint64_t n, uint32_t block, uint32_t K, int elem);
 

@@ -53,6 +53,7 @@ _SIGNATURES = {
     "nwc_matvec": (I, [P, P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_dequant": (I, [P, P, P, P, P, P, P, U64, U32, U32, I]),
     "nwc_gather": (I, [P, P, P, P, P, P, P, U32, P, U64, U32, U32, I]),
+    "nwc_gather_side": (I, [P, P, P, P, P, P, P, U32, P, U64, U32, U32, I, P]),
     "nwc_ref_fp8": (I, [P, P, P, P, P, U64, U32]),
     "nwc_setup": (I, []),
     "nwc_kernel_status": (I, [I]),

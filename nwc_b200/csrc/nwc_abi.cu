@@ -220,14 +220,26 @@ NWC_EXPORT int nwc_dequant(void *stream, const uint8_t *data, const uint32_t *ba
     return run_segments(1, stream, data, bases, hdr, lut, low, nullptr, nullptr, out, nullptr, nullptr, nullptr, n, block, K, elem, 0);
 }
 
-NWC_EXPORT int nwc_gather(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
-                          const uint8_t *low, const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem) {
+static int gather_rows(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut, const uint8_t *low,
+                       const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem, const uint16_t *side) {
     if (!shape_ok(n, block, K) || layout_of(elem) > 2 || type_of(elem) > 1) return -1;
+    if (side && layout_of(elem) != 0) return -1;
     if (n_ids == 0) return 0;
     if (!aligned16(data) || !aligned16(low) || !aligned16(lut) || !aligned16(out)) return -1;
     if (!device_sms()) return (int)cudaErrorNoDevice;
     SegmentArgs a{data, bases, hdr, lut, low, nullptr, nullptr, out, nullptr, nullptr, nullptr, (uint32_t)(n / K), K, 1, 0, 0};
-    return (int)launch_gather(elem, (cudaStream_t)stream, a, ids, n_ids);
+    return (int)launch_gather(elem, (cudaStream_t)stream, a, ids, n_ids, side);
+}
+
+NWC_EXPORT int nwc_gather(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                          const uint8_t *low, const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem) {
+    return gather_rows(stream, data, bases, hdr, lut, low, ids, n_ids, out, n, block, K, elem, nullptr);
+}
+
+NWC_EXPORT int nwc_gather_side(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
+                               const uint8_t *low, const int64_t *ids, uint32_t n_ids, uint16_t *out, uint64_t n, uint32_t block, uint32_t K, int elem,
+                               const uint16_t *side) {
+    return gather_rows(stream, data, bases, hdr, lut, low, ids, n_ids, out, n, block, K, elem, side);
 }
 
 NWC_EXPORT int nwc_ref_fp8(void *stream, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint64_t M, uint32_t K) {

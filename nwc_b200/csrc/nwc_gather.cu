@@ -21,15 +21,20 @@ namespace nwc {
 
 constexpr uint32_t kGatherThreads = 128;
 
+/* side (may be null): per block and lane the bit positions at which rows 2, 4 and 6 begin in the lane's stream
+   (launch_side_table); with it the walk starts at the row pair that holds the row instead of at the block's first row. */
 template <int ELEM>
 __device__ __forceinline__ void gather_block0(const SegmentArgs &a, const Geometry &g, uint32_t row, uint32_t cb, uint32_t lane,
-                                              uint32_t table, const uint8_t *sym, uint16_t *dst) {
+                                              uint32_t table, const uint8_t *sym, uint16_t *dst, const uint16_t *side) {
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
-    const uint32_t rb = row >> 3, skip = row & 7u, b = rb * g.CB + cb, col0 = cb * kBlockCols + lane * 16u;
+    const uint32_t rb = row >> 3, b = rb * g.CB + cb, col0 = cb * kBlockCols + lane * 16u;
+    uint32_t skip = row & 7u, start_bit = 0u;
+    if (side != nullptr && skip >= 2u) { start_bit = __ldg(side + ((uint64_t)b * 3u + ((skip >> 1) - 1u)) * kLanes + lane); skip &= 1u; }
     const bool col_ok = col0 < g.K16;
     uint32_t total;
     const uint32_t words = __ldg(a.hdr + (uint64_t)b * kLanes + lane), before = warp_exclusive_sum(words, lane, total);
-    BitWindow<MR> W; W.open(reinterpret_cast<const uint32_t *>(a.data + __ldg(a.bases + b)) + before);
+    BitWindow<MR> W; W.open(reinterpret_cast<const uint32_t *>(a.data + __ldg(a.bases + b)) + before + (start_bit >> 5));
+    if (start_bit & 31u) W.consume(start_bit & 31u);
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (col_ok) raw = ELEM == kFp8 ? expand_nibbles(ldg_stream64(a.low + (uint64_t)row * (g.K16 >> 1) + (col0 >> 1)))
                                    : ldg_stream128(a.low + (uint64_t)row * g.K16 + col0);
@@ -116,7 +121,7 @@ __device__ __forceinline__ void gather_block2(const SegmentArgs &a, const Geomet
 }
 
 template <int LAYOUT, int ELEM>
-__global__ void __launch_bounds__(kGatherThreads) gather_kernel(const SegmentArgs a, const int64_t *__restrict__ ids, uint32_t n_ids) {
+__global__ void __launch_bounds__(kGatherThreads) gather_kernel(const SegmentArgs a, const int64_t *__restrict__ ids, uint32_t n_ids, const uint16_t *__restrict__ side) {
     __shared__ __align__(16) uint32_t smem[LAYOUT == 2 ? 4 : kTableWords + 4];
     uint32_t table = 0; const uint8_t *sym = nullptr;
     if constexpr (LAYOUT != 2) {
@@ -132,19 +137,19 @@ __global__ void __launch_bounds__(kGatherThreads) gather_kernel(const SegmentArg
     const int64_t id = ids[which];
     if (id < 0 || id >= (int64_t)a.M) return;                    /* ids outside the matrix leave their output row untouched */
     uint16_t *dst = a.out + (uint64_t)which * g.K16;
-    if (LAYOUT == 0) gather_block0<ELEM>(a, g, (uint32_t)id, cb, lane, table, sym, dst);
+    if (LAYOUT == 0) gather_block0<ELEM>(a, g, (uint32_t)id, cb, lane, table, sym, dst, side);
     else if (LAYOUT == 1) gather_block1<ELEM>(a, g, (uint32_t)id, cb, lane, table, sym, dst);
     else { FixedTables t; t.load(a.lut); gather_block2<ELEM>(a, g, t, (uint32_t)id, cb, lane, dst); }
 }
 
-cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids) {
+cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids, const uint16_t *side) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(a.M, a.K, layout);
     const uint64_t warps = (uint64_t)n_ids * g.CB;
     const unsigned grid = (unsigned)((warps * 32u + kGatherThreads - 1) / kGatherThreads);
-    if (layout == 0) { if (elem == kFp8) gather_kernel<0, kFp8><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids); else gather_kernel<0, kBf16><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids); }
-    else if (layout == 1) { if (elem == kFp8) gather_kernel<1, kFp8><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids); else gather_kernel<1, kBf16><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids); }
-    else { if (elem == kFp8) gather_kernel<2, kFp8><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids); else gather_kernel<2, kBf16><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids); }
+    if (layout == 0) { if (elem == kFp8) gather_kernel<0, kFp8><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids, side); else gather_kernel<0, kBf16><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids, side); }
+    else if (layout == 1) { if (elem == kFp8) gather_kernel<1, kFp8><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids, side); else gather_kernel<1, kBf16><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids, side); }
+    else { if (elem == kFp8) gather_kernel<2, kFp8><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids, side); else gather_kernel<2, kBf16><<<grid, kGatherThreads, 0, st>>>(a, ids, n_ids, side); }
     return cudaGetLastError();
 }
 

@@ -22,6 +22,7 @@
  * kern_f32_to_bf16_bias 553-565.
  */
 #include <cstdlib>
+#include <mutex>
 #include <cooperative_groups.h>
 #include "nwc_decode.cuh"
 #include "nwc_async.cuh"
@@ -2105,6 +2106,8 @@ static void opt_in_smem() {
 static ClusterRoom cluster_room(int sms) {
     static ClusterRoom cache[64];
     static bool known[64];
+    static std::mutex guard;                                     /* launches may come from several host threads */
+    std::lock_guard<std::mutex> hold(guard);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;

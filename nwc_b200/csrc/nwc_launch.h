@@ -83,7 +83,8 @@ int read_model_status(bool clear);           /* 0, or 3 when the sharded argmax 
 unsigned long long peer_timeout_ns();        /* longest wait for other ranks inside a kernel (nwc_comm_set_timeout_ms) */
 void configure_model_kernels();              /* per-device opt-ins of the decode-step kernels */
 int read_comm_status(bool clear);            /* 0, or 3 when a rank gave up waiting for its peers */
-cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids);
+/* side: layout 0 only, the matrix's side table (launch_side_table) or null */
+cudaError_t launch_gather(int code, cudaStream_t st, const SegmentArgs &a, const int64_t *ids, uint32_t n_ids, const uint16_t *side = nullptr);
 cudaError_t launch_native_fp8(int sms, cudaStream_t st, const uint8_t *w, const float *scale, const float *x, uint16_t *y, uint32_t M, uint32_t K);
 
 }  // namespace nwc

@@ -81,6 +81,8 @@ class NWCEmbedding(nn.Module):
         self.padding_idx = padding_idx if emb is None else emb.padding_idx
 
     def forward(self, ids):
+        # many ids at once (a prompt) from a layout-0 table: the side table lets every row's walk start at its row pair
+        if self.w.layout == 0 and self.w.side is None and ids.numel() >= 64: self.w.build_side_table()
         rows = self.w.gather(ids)
         if self.w.scale is None: return rows
         row_scale = self.w.scale[ids.to(self.w.scale.device)]     # fp8 table: codes come back unscaled

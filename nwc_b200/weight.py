@@ -216,7 +216,7 @@ class NWCWeight:
         """Rows ids -> bf16[..., in] (embedding lookup straight from the compressed matrix)."""
         flat = ids.reshape(-1).to(device=self.data.device, dtype=torch.int64).contiguous()
         out = torch.empty(flat.numel(), self.K16, dtype=torch.bfloat16, device=self.data.device)
-        err = L.lib.nwc_gather(L.stream(), *self._operands(), L.ptr(flat), flat.numel(), L.ptr(out), *self._shape_args())
+        err = L.lib.nwc_gather_side(L.stream(), *self._operands(), L.ptr(flat), flat.numel(), L.ptr(out), *self._shape_args(), L.ptr(self.side))
         if err: raise RuntimeError(f"nwc_gather error {err}")
         if self.K16 != self.in_features: out = out[:, : self.in_features].contiguous()
         return out.view(*ids.shape, self.in_features)

@@ -244,3 +244,27 @@ def test_pool_kernel_repeats_bit_for_bit_and_agrees_with_the_ring_kernel(M, K, e
     finally:
         L.lib.nwc_set_pool_kernels(0)
     assert L.lib.nwc_kernel_status(1) == 0
+
+
+@pytest.mark.parametrize("M,K,elem", [(100, 1000, 0), (64, 2048, 0), (100, 1000, 1), (4096, 1024, 0), (13, 40, 0)])
+def test_gather_with_side_table_is_bit_identical(M, K, elem):
+    """Layout 0: with the side table the walk of a lane's stream starts at the row pair that holds the requested row; the
+    rows must come back bit for bit as without it (every row of the matrix, so every position inside a block), and both
+    equal the oracle's dequantised rows."""
+    from gpu_helpers import bits, make_case, to_weight
+    from nwc_b200 import _lib as L
+    p, _, _ = make_case(M, K, elem, 0, seed=M + K, escapes=True)
+    nw = to_weight(p)
+    ids = torch.randperm(M, generator=torch.Generator().manual_seed(3)).cuda()
+    plain = nw.gather(ids)
+    assert nw.side is None
+    nw.build_side_table()
+    with_side = nw.gather(ids)
+    assert torch.equal(plain, with_side)
+    want = O.gather(p, ids.cpu().numpy())[:, :K]
+    assert np.array_equal(bits(with_side)[:, :K], want)
+    out = torch.empty(M, plain.shape[1], dtype=torch.bfloat16, device="cuda")
+    other = to_weight(make_case(64, 1024, 0, 2, seed=1, escapes=False)[0])
+    err = L.lib.nwc_gather_side(L.stream(), L.ptr(other.data), L.ptr(other.bases), L.ptr(other.hdr), L.ptr(other.lut), L.ptr(other.low), L.ptr(ids), 1, L.ptr(out),
+                                other.n, other.block, 1024, other.code, L.ptr(nw.side))
+    assert err == -1                                                  # a side table goes with layout 0 only
