@@ -169,13 +169,15 @@ int nwc_linear_fused(void *stream, const uint8_t *data, const uint32_t *bases, c
    Tensor-parallel group of one node ("push" protocol; `buffers` as for nwc_allreduce_add_rmsnorm: a host array of `world`
    exchange buffers, this rank's own at [rank]; buffers == NULL: no group):
      out_slot >= 0  (row-parallel matrices: o, down) y is not written; the kernel stores its bf16 result into push slot
-                    out_slot (0 or 1, used in turn) of EVERY rank's buffer with plain stores over NVLink, and its last CTA
-                    raises this rank's flag in every buffer after a system-scope fence.  M <= H, no bias / scale.
-     in_slot >= 0   (the matrix after a row-parallel one; mode must be 1, delta NULL, K == H) the prologue waits -
-                    bounded by nwc_comm_set_timeout_ms - until every rank's flag for that slot has arrived in this rank's
-                    buffer, adds the `world` partials in rank order in fp32 (every rank gets the same bits), and continues
-                    as mode 1 with that sum as delta.  After a timeout nwc_kernel_status() reports 3 and y is NaN.
-   So the sum over the ranks costs no kernel of its own and one NVLink trip.  Only matrices that run on the layout-2 bf16
+                    out_slot (0 or 1, used in turn) of EVERY rank's buffer over NVLink as 8-byte words {two rows, number of
+                    this push}: a word is valid once it carries the number the reader expects, so there is no flag and
+                    no fence.  M == H, no bias / scale.
+     in_slot >= 0   (the matrix after a row-parallel one; mode must be 1, delta NULL, K == H) the prologue reads the
+                    `world` partials of that slot in its own buffer - polling, bounded by nwc_comm_set_timeout_ms, any word
+                    that does not carry the expected push number yet - adds them in rank order in fp32 (every rank gets
+                    the same bits), and continues as mode 1 with that sum as delta.  After a timeout nwc_kernel_status()
+                    reports 3 and y is NaN.
+   So the sum over the ranks costs no kernel of its own and one NVLink store latency.  Only matrices that run on the layout-2 bf16
    ring kernel are covered (-2 otherwise: use nwc_allreduce_add_rmsnorm).  All ranks must make the same sequence of calls.
 
    side != NULL  (layout 0, matrices that take the single-launch small-matrix kernel) the table nwc_build_side_table made

@@ -128,7 +128,7 @@ static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases
         if (tp->world < 1 || tp->world > (int)kCommMaxRanks || tp->rank < 0 || tp->rank >= tp->world || !tp->H || (tp->H & 7u)) return -1;
         for (int r = 0; r < tp->world; r++) if (!tp->buffers[r]) return -1;
         if (peer_in && (mode != kInputNorm || K != tp->H || tp->in_slot > 1 || delta)) return -1;
-        if (peer_out && (M > tp->H || tp->out_slot > 1 || bias || scale)) return -1;
+        if (peer_out && (M != tp->H || tp->out_slot > 1 || bias || scale)) return -1;     /* the consumer polls every word of the H-vector */
         if (peer_in) in_mode = kInputPeerNorm;
         /* both directions are part of the layout-2 ring kernel only */
         if (!token_path_fuses_input(elem, M, K, in_mode)) return -2;

@@ -307,28 +307,26 @@ __device__ __forceinline__ uint4 ld_volatile128(const void *p) {                
     return v;
 }
 
-/* kInputPeerNorm: wait until every rank of the group has pushed its partial of `in.slot` into this rank's exchange
-   buffer.  The flag this rank expects is its own push count for the slot (all ranks make the same sequence of calls; the
-   own push finished before this kernel passed its dependency wait).  The wait is bounded by the global timer; when it
-   runs out the status word is set to 3 and false is returned to every thread.  Ends with a CTA barrier. */
-__device__ __forceinline__ bool wait_for_pushes(const FusedInput &in) {
-    const CommControl *ctl = reinterpret_cast<const CommControl *>(in.comm);
-    bool ok = true;
-    if (threadIdx.x < in.world) {
-        const uint32_t epoch = *reinterpret_cast<const volatile uint32_t *>(&ctl->push_epoch[in.slot]);
-        const volatile uint32_t *flag = &ctl->push_flag[in.slot][threadIdx.x];
-        if ((int32_t)(*flag - epoch) < 0) {
-            const unsigned long long t0 = global_timer_ns();
-            while ((int32_t)(*flag - epoch) < 0) {
-                if (global_timer_ns() - t0 > in.timeout_ns) { ok = false; break; }
-                __nanosleep(20);
-            }
-        }
-        __threadfence_system();                                  /* the partials are read after the flags */
+/* kInputPeerNorm: the call number that the words of push slot `in.slot` must carry = this rank's own push count for
+   the slot (all ranks make the same sequence of calls; the own push finished before this kernel passed its dependency
+   wait). */
+__device__ __forceinline__ uint32_t expected_push(const FusedInput &in) {
+    return *reinterpret_cast<const volatile uint32_t *>(&reinterpret_cast<const CommControl *>(in.comm)->push_epoch[in.slot]);
+}
+/* Eight rows of rank r's partial = four 8-byte words {two rows, call number} = two 16-byte loads, repeated until all four
+   words carry the expected call number (they normally do at the first look).  Bounded by the global timer: ok = false
+   when it runs out. */
+__device__ __forceinline__ uint4 pushed_chunk(const uint8_t *words, uint32_t epoch, unsigned long long timeout_ns, bool &ok) {
+    uint4 a = ld_volatile128(words), b = ld_volatile128(words + 16);
+    auto fresh = [&]() { return (int32_t)(a.y - epoch) >= 0 && (int32_t)(a.w - epoch) >= 0 && (int32_t)(b.y - epoch) >= 0 && (int32_t)(b.w - epoch) >= 0; };
+    if (!fresh()) {
+        const unsigned long long t0 = global_timer_ns();
+        do {
+            if (global_timer_ns() - t0 > timeout_ns) { ok = false; break; }
+            a = ld_volatile128(words); b = ld_volatile128(words + 16);
+        } while (!fresh());
     }
-    ok = __syncthreads_and(ok) != 0;
-    if (!ok && threadIdx.x == 0) atomicExch(&g_kernel_status, kStatusPeerTimeout);
-    return ok;
+    return make_uint4(a.x, a.z, b.x, b.z);
 }
 
 /* two fp32 values -> bf16x2 (first value in the low half), round to nearest even in hardware */
@@ -361,14 +359,14 @@ __device__ __forceinline__ void stage_norm_weight(const FusedInput &in, uint32_t
 
 /* eight values of h_in + delta (delta = a local vector, or the sum of the ranks' pushed partials in rank order), rounded to
    bf16 as the residual stream is: four bf16x2 words; *ss gets the sum of their squares in element order */
-__device__ __forceinline__ void residual_chunk(const FusedInput &in, bool peer, uint32_t K, uint32_t c, uint32_t (&out)[4], float &ss) {
+__device__ __forceinline__ void residual_chunk(const FusedInput &in, bool peer, uint32_t epoch, uint32_t K, uint32_t c, uint32_t (&out)[4], float &ss, bool &ok) {
     const uint4 h = *(reinterpret_cast<const uint4 *>(in.h_in) + c);
     const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
     if (peer) {                                                  /* all loads in flight before the first add */
         uint4 part[kCommMaxRanks];
 #pragma unroll
         for (uint32_t r = 0; r < kCommMaxRanks; r++)
-            part[r] = r < in.world ? ld_volatile128(in.comm + comm_push_offset(K, in.slot, r) + (uint64_t)c * 16u) : make_uint4(0u, 0u, 0u, 0u);
+            part[r] = r < in.world ? pushed_chunk(in.comm + comm_push_offset(K, in.slot, r) + (uint64_t)c * 32u, epoch, in.timeout_ns, ok) : make_uint4(0u, 0u, 0u, 0u);
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (uint32_t r = 0; r < kCommMaxRanks; r++) {
@@ -417,11 +415,8 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
     const bool vec = (K & 7u) == 0u;
     if (norm_like(in.mode)) {
         const bool peer = in.mode == kInputPeerNorm;             /* (the entry point admits this mode only with K % 8 == 0) */
-        if (peer && !wait_for_pushes(in)) {                      /* a rank is missing: poison x so that nothing downstream looks valid */
-            for (uint32_t c = tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u));
-            __syncthreads();
-            return;
-        }
+        const uint32_t epoch = peer ? expected_push(in) : 0u;
+        bool ok = true;
         const bool write_h = blockIdx.x == 0 && in.h_out != nullptr;
         float ss = 0.f;
         uint32_t held[kNormRegChunks][4];                        /* register path: the thread's chunks of h_out */
@@ -430,14 +425,14 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
             for (uint32_t i = 0; i < kNormRegChunks; i++) {
                 const uint32_t c = tid + i * THREADS;
                 if (c < live) {
-                    residual_chunk(in, peer, K, c, held[i], ss);
+                    residual_chunk(in, peer, epoch, K, c, held[i], ss, ok);
                     if (write_h) *(reinterpret_cast<uint4 *>(in.h_out) + c) = make_uint4(held[i][0], held[i][1], held[i][2], held[i][3]);
                 }
             }
         } else if (vec) {
             for (uint32_t c = tid; c < live; c += THREADS) {
                 uint32_t o[4];
-                residual_chunk(in, peer, K, c, o, ss);
+                residual_chunk(in, peer, epoch, K, c, o, ss, ok);
                 if (write_h) *(reinterpret_cast<uint4 *>(in.h_out) + c) = make_uint4(o[0], o[1], o[2], o[3]);
                 sts128(xs_addr + c * 16u, make_uint4(o[0], o[1], o[2], o[3]));
             }
@@ -453,7 +448,12 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) scal[warp] = ss;
-        __syncthreads();
+        if (!__syncthreads_and(ok)) {                            /* a rank is missing: poison x so that nothing downstream looks valid */
+            if (tid == 0) atomicExch(&g_kernel_status, kStatusPeerTimeout);
+            for (uint32_t c = tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u));
+            __syncthreads();
+            return;
+        }
         float tot = 0.f;
         for (uint32_t i = 0; i < THREADS / 32u; i++) tot += scal[i];
         const float inv = rsqrtf(tot / (float)K + in.eps);
@@ -611,7 +611,7 @@ static __device__ unsigned int g_cut_part[kFixCounters][16];
    = the 16 lanes, all of which make this call): scale, bias and bf16 rounding as the reference's finalize step, then
    either the local y or, for a row-parallel matrix of a tensor-parallel group, the push slot of EVERY rank's exchange
    buffer (plain 4-byte stores over NVLink, two rows each; the flag that publishes them is raised at the kernel's end). */
-__device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, uint32_t sub, float v, uint32_t mask) {
+__device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, uint32_t sub, float v, uint32_t mask, uint32_t push_call) {
     const uint32_t row = grp * 16u + sub;
     const bool live = row < a.M;
     if (live && a.scale) v *= __ldg(a.scale + row);
@@ -620,10 +620,10 @@ __device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, u
     if (a.push.world == 0u) { if (live) a.y[row] = (uint16_t)h; return; }
     const uint32_t pair = h | (__shfl_down_sync(mask, h, 1) << 16);
     if ((sub & 1u) == 0u && live) {
-        const uint64_t off = comm_push_offset(a.push.H, a.push.slot, a.push.rank) + (uint64_t)row * 2u;
+        const uint64_t off = comm_push_offset(a.push.H, a.push.slot, a.push.rank) + (uint64_t)(row >> 1) * 8u;
 #pragma unroll
         for (uint32_t p = 0; p < kCommMaxRanks; p++)
-            if (p < a.push.world) *reinterpret_cast<volatile uint32_t *>(a.push.buf[p] + off) = pair;
+            if (p < a.push.world) asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.push.buf[p] + off), "r"(pair), "r"(push_call) : "memory");
     }
 }
 
@@ -763,6 +763,9 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
     if (threadIdx.x < kRingEntries) share_group[threadIdx.x] = kNoGroup;
     if (threadIdx.x < 2u) cta_group[threadIdx.x] = kNoGroup;
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    /* tensor-parallel output: the call number that this launch's words carry = this rank's pushes to the slot so far + 1
+       (read by every CTA before any CTA can finish; the last CTA to finish counts the push) */
+    const uint32_t push_call = a.push.world ? *reinterpret_cast<const volatile uint32_t *>(&reinterpret_cast<const CommControl *>(a.push.buf[a.push.rank])->push_epoch[a.push.slot]) + 1u : 0u;
     promote(); load_ahead(next_block + 1u);                      /* the first block's entries travel while x is built */
     build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
     const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * (ELEM == kFp8 ? 4u : 16u), xq = xs + (lane & 3u) * 16u;
@@ -778,7 +781,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
             if (plan.direct || plan.fix) {                       /* final: row i of the group to lane i < 16, from the quad leader that holds it */
                 const uint32_t src = (lane & 7u) << 2;
                 const float vlo = __shfl_sync(0xffffffffu, lo, src), vhi = __shfl_sync(0xffffffffu, hi, src);
-                if (lane < 16u) emit_group(a, rb, lane, (lane & 8u) ? vhi : vlo, 0x0000FFFFu);
+                if (lane < 16u) emit_group(a, rb, lane, (lane & 8u) ? vhi : vlo, 0x0000FFFFu, push_call);
             } else if ((lane & 3u) == 0u) {
                 const uint32_t part = cluster_id - plan.owner(rb * slots);
                 emit_flat(a, plan, rb * 16u + r, part, lo); emit_flat(a, plan, rb * 16u + r + 8u, part, hi);
@@ -877,7 +880,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
             const uint32_t g0 = grp * slots;
             const bool inside = g0 >= c0 && g0 + slots <= c1;
             const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16u);
-            if (plan.direct ? (cluster_ctas == 1u || inside) : (plan.fix && inside)) emit_group(a, grp, row, v, half_mask);
+            if (plan.direct ? (cluster_ctas == 1u || inside) : (plan.fix && inside)) emit_group(a, grp, row, v, half_mask, push_call);
             else if (plan.fix) {
                 /* Equal runs: a row group cut by run boundaries.  A CTA whose run holds a later part of it leaves that part
                    in its own entry of g_cut_part; the CTA where the group begins adds the later parts in CTA order (so the
@@ -901,7 +904,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
                         if (ok) { v += __uint_as_float(w); *theirs = kCutEmpty; }
                     }
                     if (!ok) { atomicExch(&g_kernel_status, kStatusWaitTimeout); v = __uint_as_float(0x7FC00000u); }
-                    emit_group(a, grp, row, v, half_mask);
+                    emit_group(a, grp, row, v, half_mask, push_call);
                 }
             }
             else if (cluster_ctas == 1u) emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner(g0), v);      /* one fp32 partial per CTA */
@@ -924,27 +927,19 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
                     if (theirs == grp) v += cluster.map_shared_rank(cta_value, r)[row];
                     else if (theirs != kNoGroup) break;          /* (no entry: an empty run, or one that starts on a group boundary) */
                 }
-                emit_group(a, grp, row, v, 0xFFFFu << (threadIdx.x & 16u));
+                emit_group(a, grp, row, v, 0xFFFFu << (threadIdx.x & 16u), push_call);
             }
         }
         cluster.sync();                                             /* nobody leaves while its shared memory may still be read */
     }
-    /* Tensor-parallel output: the CTA that finishes last publishes this rank's partial.  Every CTA orders its peer stores
-       before its arrival with a system-scope fence; the last one raises this rank's flag in every buffer. */
-    if (a.push.world) {
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
-            __threadfence_system();
-            if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
-                own->push_done = 0u;
-                volatile uint32_t *count = &own->push_epoch[a.push.slot];
-                const uint32_t epoch = *count + 1u;
-                *count = epoch;
-                __threadfence_system();
-                for (uint32_t p = 0; p < a.push.world; p++)
-                    *reinterpret_cast<volatile uint32_t *>(&reinterpret_cast<CommControl *>(a.push.buf[p])->push_flag[a.push.slot][a.push.rank]) = epoch;
-            }
+    /* Tensor-parallel output: the words this launch stored carry their own call number, nothing has to be published; the
+       CTA that finishes last counts the push (every CTA read the count before any CTA could get here). */
+    if (a.push.world && threadIdx.x == 0) {
+        CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
+        if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
+            own->push_done = 0u;
+            volatile uint32_t *count = &own->push_epoch[a.push.slot];
+            *count = *count + 1u;
         }
     }
 }
@@ -1076,6 +1071,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const Seg
     stage_norm_weight<kRingThreads>(in, a.K, reinterpret_cast<uint16_t *>(ring_smem + x_bytes), norm_regs);
     if (threadIdx.x < 48u) ctrl[threadIdx.x] = threadIdx.x == 0u ? 2u * (kRingThreads / 32u) : 0u;      /* (visible after build_activation's barrier) */
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t push_call = a.push.world ? *reinterpret_cast<const volatile uint32_t *>(&reinterpret_cast<const CommControl *>(a.push.buf[a.push.rank])->push_epoch[a.push.slot]) + 1u : 0u;
     promote(EC0, EB0, EP0); promote(EC1, EB1, EP1);
     build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
     const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * (ELEM == kFp8 ? 4u : 16u), xq = xs + (lane & 3u) * 16u;
@@ -1160,7 +1156,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const Seg
         if (lane == 0) { arrived[gslot] = 0u; __threadfence_block(); generation[gslot] = turn + 1u; }
         const uint32_t grp = grp0 + s.gi, g_first = grp * slots;
         const bool begins_here = g_first >= c0, ends_here = g_first + slots <= c1;
-        if (begins_here && ends_here) { if (lane < 16u) emit_group(a, grp, row, v, 0x0000FFFFu); return; }
+        if (begins_here && ends_here) { if (lane < 16u) emit_group(a, grp, row, v, 0x0000FFFFu, push_call); return; }
         if (!begins_here) {                                      /* the group began in an earlier CTA's run: leave this part for that CTA */
             if (lane < 16u) {
                 uint32_t w = __float_as_uint(v);
@@ -1185,7 +1181,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const Seg
             }
         }
         if (!__all_sync(0xffffffffu, ok)) { atomicExch(&g_kernel_status, kStatusWaitTimeout); v = __uint_as_float(0x7FC00000u); }
-        if (lane < 16u) emit_group(a, grp, row, v, 0x0000FFFFu);
+        if (lane < 16u) emit_group(a, grp, row, v, 0x0000FFFFu, push_call);
     };
 #pragma unroll 1
     while ((T0 != kNone || T1 != kNone) && !failed) {
@@ -1197,21 +1193,14 @@ __global__ void __launch_bounds__(kRingThreads, 1) pool_kernel_layout2(const Seg
         for (uint32_t b = 0; b < kRingStages; b++) for (uint32_t i = 0; i < 64u && !mbar_poll(bars + b * 8u, parity); i++) {}
     }
     if (lane == 0 && !hinted) prefetch_next_fill(nx, warp);
-    /* Tensor-parallel output: the CTA that finishes last publishes this rank's partial (as in the kernel above). */
-    if (a.push.world) {
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
-            __threadfence_system();
-            if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
-                own->push_done = 0u;
-                volatile uint32_t *count = &own->push_epoch[a.push.slot];
-                const uint32_t epoch = *count + 1u;
-                *count = epoch;
-                __threadfence_system();
-                for (uint32_t p = 0; p < a.push.world; p++)
-                    *reinterpret_cast<volatile uint32_t *>(&reinterpret_cast<CommControl *>(a.push.buf[p])->push_flag[a.push.slot][a.push.rank]) = epoch;
-            }
+    /* Tensor-parallel output: the words this launch stored carry their own call number, nothing has to be published; the
+       CTA that finishes last counts the push (every CTA read the count before any CTA could get here). */
+    if (a.push.world && threadIdx.x == 0) {
+        CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
+        if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
+            own->push_done = 0u;
+            volatile uint32_t *count = &own->push_epoch[a.push.slot];
+            *count = *count + 1u;
         }
     }
 }
