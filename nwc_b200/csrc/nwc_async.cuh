@@ -42,6 +42,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return ok;
 }
 
+/* One thread's wait (the other lanes of its warp are elsewhere): true when the phase completed, false after kWaitPolls
+   polls (status word set). */
+__device__ __forceinline__ bool mbar_wait_one(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitPolls; i++) if (mbar_poll(bar, parity)) return true;
+    atomicExch(&g_kernel_status, kStatusWaitTimeout);
+    return false;
+}
+
 __device__ __forceinline__ uint2 lds64(uint32_t addr) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr)); return v; }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)); return v; }
 
