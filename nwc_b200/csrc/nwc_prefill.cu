@@ -24,7 +24,7 @@
 
 namespace nwc {
 
-constexpr uint32_t kPfDecodeThreads = 512, kPfThreads = kPfDecodeThreads + 64u /* + the warp that copies X and the warp that issues the MMAs */, kPfRows = 128, kPfK = 64, kPfMaxTokens = 256, kPfStages = 4, kPfAhead = 3;
+constexpr uint32_t kPfDecodeThreads = 512, kPfThreads = kPfDecodeThreads + 64u /* + the warp that copies X and the warp that issues the MMAs */, kPfRows = 128, kPfK = 64, kPfMaxTokens = 256, kPfStages = 4, kPfAhead = 3, kPfFar = 12;
 constexpr uint32_t kPfABytes = kPfRows * 128u, kPfBBytes = kPfMaxTokens * 128u;
 constexpr uint32_t kPfSmem = 1024u /* alignment slack */ + kPfStages * (kPfABytes + kPfBBytes) + 3u * kPfStages * 8u + 32u;
 
@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
         /* ---- decoders ---- */
         const uint32_t rg = (m0 >> 4) + (warp >> 1);                                /* this warp's row group */
         const bool rows_live = rg < g.groups;
+        /* the slot of chunk k into registers; the slot of chunk k + kPfFar is asked into L2 at the same time, so that the
+           register loads (three chunks ahead of their use) find their lines there instead of in HBM */
         auto load_w = [&](uint32_t k, uint2 &nib, uint4 &raw) {
             const uint32_t slot = 2u * k + (warp & 1u);
             nib = make_uint2(0u, 0u); raw = make_uint4(0u, 0u, 0u, 0u);
@@ -104,20 +106,35 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
                 const uint64_t cell = ((uint64_t)rg * g.slots + slot) * kLanes + lane;
                 nib = ldg_stream64(a.low + cell * 8u);
                 raw = ldg_stream128(raw_plane + cell * 16u);
+                if (slot + 2u * kPfFar < g.slots) {
+                    const uint64_t far = cell + (uint64_t)2u * kPfFar * kLanes;
+                    if ((lane & 15u) == 0u) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.low + far * 8u));          /* 128 bytes per 16 lanes */
+                    if ((lane & 7u) == 0u) asm volatile("prefetch.global.L2 [%0];" ::"l"(raw_plane + far * 16u));       /* 128 bytes per 8 lanes  */
+                }
             }
         };
         /* exception count of this lane and data offset of the block (512 columns = 8 chunks) that holds chunk k; the next
            block's are loaded while this one is in use and its entries are pulled towards L1 */
-        uint32_t cnt = 0, ebase = 0, cnt_next = 0, ebase_next = 0, before = 0, total = 0;
+        uint32_t cnt = 0, ebase = 0, cnt_next = 0, ebase_next = 0, before = 0, total = 0, before_next = 0, total_next = 0;
+        uint32_t e0 = 0, e1 = 0, e0_next = 0, e1_next = 0;       /* this lane's first two exception entries of the block: index | value << 8 */
         auto load_block = [&](uint32_t cb, uint32_t &c, uint32_t &b) {
             c = 0u; b = 0u;
             if (rows_live && cb < g.CB) { const uint32_t blk = rg * g.CB + cb; c = __ldg(a.hdr + (uint64_t)blk * kLanes + lane); b = __ldg(a.bases + blk); }
+        };
+        /* where the lane's entries of the next block start, and its first two entries, into registers (the rest, rare, is
+           read when needed) */
+        auto load_entries = [&]() {
+            before_next = warp_exclusive_sum(cnt_next, lane, total_next);
+            const uint8_t *ep = a.data + ebase_next + (uint64_t)before_next * 3u;
+            e0_next = cnt_next >= 1u ? (uint32_t)ep[0] | ((uint32_t)ep[1] << 8) | ((uint32_t)ep[2] << 16) : 0u;
+            e1_next = cnt_next >= 2u ? (uint32_t)ep[3] | ((uint32_t)ep[4] << 8) | ((uint32_t)ep[5] << 16) : 0u;
         };
         FixedTables tab; tab.load(a.lut);
         uint2 n0, n1, n2; uint4 r0, r1, r2;
         static_assert(kPfAhead == 3u, "three register sets travel ahead of the decode");
         load_w(0u, n0, r0); load_w(1u, n1, r1); load_w(2u, n2, r2);
         load_block(0u, cnt_next, ebase_next);
+        load_entries();
         const uint32_t mm = (warp >> 1) * 16u + r, cc = (warp & 1u) * 4u + q;
         const uint32_t off_lo = sw128(mm, cc), off_hi = sw128(mm + 8u, cc);       /* where this lane's two rows of the slot go */
         /* one chunk; (wn, wr) = the register set that holds its compressed slot and is reloaded with chunk k + kPfAhead
@@ -125,11 +142,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
         auto step = [&](const uint32_t k, uint2 &wn, uint4 &wr) -> bool {
             const uint32_t s = k % kPfStages, abase = a_buf + s * kPfABytes;
             if ((k & 7u) == 0u) {                                                    /* a new block of W begins */
-                cnt = cnt_next; ebase = ebase_next;
-                before = warp_exclusive_sum(cnt, lane, total);
+                cnt = cnt_next; ebase = ebase_next; before = before_next; total = total_next; e0 = e0_next; e1 = e1_next;
                 load_block((k >> 3) + 1u, cnt_next, ebase_next);
-                if (cnt) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.data + ebase + (uint64_t)before * 3u));
-            }
+            } else if ((k & 7u) == 4u) load_entries();                               /* (the next block's counts have arrived by now) */
             const uint32_t slot = 2u * k + (warp & 1u);
             const bool live = rows_live && slot < g.slots;
             uint32_t f[8];
@@ -143,12 +158,17 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
             sts64(abase + off_lo, f[0], f[2]);      sts64(abase + off_lo + 8u, f[4], f[6]);
             sts64(abase + off_hi, f[1], f[3]);      sts64(abase + off_hi + 8u, f[5], f[7]);
             if (total && live) {                                  /* exceptions of this slot overwrite their +-0 placeholders */
-                const uint8_t *ep = a.data + ebase + (uint64_t)before * 3u;
-                for (uint32_t e = 0; e < cnt; e++, ep += 3) {
-                    const uint32_t i = ep[0], j = i & 15u;
-                    if ((i >> 4) != (slot & 15u)) continue;
+                auto patch = [&](uint32_t entry) {
+                    const uint32_t i = entry & 0xFFu, j = i & 15u;
+                    if ((i >> 4) != (slot & 15u)) return;
                     const uint32_t col = (warp & 1u) * 32u + frag_col(lane, j), row = (warp >> 1) * 16u + frag_row(lane, j);
-                    sts16(abase + sw128(row, col >> 3) + (col & 7u) * 2u, (uint16_t)(ep[1] | (ep[2] << 8)));
+                    sts16(abase + sw128(row, col >> 3) + (col & 7u) * 2u, (uint16_t)(entry >> 8));
+                };
+                if (cnt >= 1u) patch(e0);
+                if (cnt >= 2u) patch(e1);
+                if (cnt > 2u) {
+                    const uint8_t *ep = a.data + ebase + (uint64_t)before * 3u + 6u;
+                    for (uint32_t e = 2; e < cnt; e++, ep += 3) patch((uint32_t)ep[0] | ((uint32_t)ep[1] << 8) | ((uint32_t)ep[2] << 16));
                 }
             }
             async_proxy_fence();                                                     /* generic-proxy stores -> visible to the tensor core */
