@@ -230,6 +230,9 @@ void nwc_comm_set_timeout_ms(uint32_t ms);
    tensor-memory GEMM; no decompressed copy is written.  The reference dequantises into a temporary and calls a dense
    matmul instead (nwc/nwc_torch.py:320-323).  Returns 0, -1 bad arguments, -2 when the element type / layout is not
    covered by this path yet (layout 2 bf16 is), or a CUDA error. */
+/* tests: 1 or 2 = every nwc_linear_prefill CTA multiplies its rows with that many halves of 256 tokens; 0 (default) = the
+   launcher chooses (two halves when that saves whole waves of CTAs). */
+void nwc_set_prefill_halves(int halves);
 int nwc_linear_prefill(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,
                        const uint8_t *low, const uint16_t *X, uint32_t T, uint32_t ldx, const uint16_t *bias,
                        const float *scale, uint16_t *Y, uint32_t ldy, uint64_t n, uint32_t block, uint32_t K, int elem);

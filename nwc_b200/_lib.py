@@ -58,6 +58,7 @@ _SIGNATURES = {
     "nwc_setup": (I, []),
     "nwc_kernel_status": (I, [I]),
     "nwc_set_ring_kernels": (None, [I]),
+    "nwc_set_prefill_halves": (None, [I]),
     "nwc_set_fixup_plans": (None, [I]),
     "nwc_set_pool_kernels": (None, [I]),
     "nwc_comm_bytes": (U64, [U32]),

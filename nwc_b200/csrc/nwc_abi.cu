@@ -272,6 +272,7 @@ NWC_EXPORT int nwc_linear_prefill(void *stream, const uint8_t *data, const uint3
     return (int)launch_prefill_layout2((cudaStream_t)stream, a, X, Y, T, ldx, ldy);
 }
 
+NWC_EXPORT void nwc_set_prefill_halves(int halves) { set_prefill_halves(halves); }
 NWC_EXPORT void nwc_set_ring_kernels(int on) { set_ring_kernels(on != 0); }
 NWC_EXPORT void nwc_set_fixup_plans(int on) { set_fixup_plans(on != 0); }
 NWC_EXPORT void nwc_set_pool_kernels(int on) { set_pool_kernels(on != 0); }

@@ -76,6 +76,7 @@ void configure_segment_kernels();
 int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_fix = false);
 
 cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy);
+void set_prefill_halves(int halves);         /* tests: 1 or 2 token halves of 256 per CTA of the prefill GEMM, 0 = chosen per launch */
 int read_prefill_status(bool clear);
 void configure_prefill_kernels();
 void prepare_static_scratch();               /* nwc_linear_bf16_static: look up the built-in scratch area of the current device */

@@ -24,9 +24,12 @@
 
 namespace nwc {
 
-constexpr uint32_t kPfDecodeThreads = 512, kPfThreads = kPfDecodeThreads + 64u /* + the warp that copies X and the warp that issues the MMAs */, kPfRows = 128, kPfK = 64, kPfMaxTokens = 256, kPfStages = 4, kPfAhead = 3, kPfFar = 12;
-constexpr uint32_t kPfABytes = kPfRows * 128u, kPfBBytes = kPfMaxTokens * 128u;
-constexpr uint32_t kPfSmem = 1024u /* alignment slack */ + kPfStages * (kPfABytes + kPfBBytes) + 3u * kPfStages * 8u + 32u;
+constexpr uint32_t kPfDecodeThreads = 512, kPfThreads = kPfDecodeThreads + 64u /* + the warp that copies X and the warp that issues the MMAs */, kPfRows = 128, kPfK = 64, kPfHalfTokens = 256 /* most tokens of one MMA */, kPfAhead = 3, kPfFar = 12;
+constexpr uint32_t kPfABytes = kPfRows * 128u, kPfHalfBytes = kPfHalfTokens * 128u;
+/* A CTA multiplies its 128 rows with one or two halves of 256 tokens (HALVES): two halves reuse every decoded W tile for
+   twice the tokens and fill all 512 columns of tensor memory, but their B tiles leave room for two operand stages only. */
+__host__ __device__ constexpr uint32_t pf_stages(uint32_t halves) { return halves == 1u ? 4u : 2u; }
+__host__ __device__ constexpr uint32_t pf_smem(uint32_t halves) { return 1024u /* alignment slack */ + pf_stages(halves) * (kPfABytes + halves * kPfHalfBytes) + 3u * pf_stages(halves) * 8u + 32u; }
 
 /* shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart */
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -65,7 +68,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarri
    the chunk and commits them to the stage's `freed` barrier, which the decoders and the copier wait for before they
    overwrite the stage four chunks later.  No CTA barrier inside the loop: the three roles run up to kPfStages chunks
    apart.  Every wait is bounded; a role that gives up records the status word and stops, the others then run out too. */
+template <uint32_t HALVES>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const PrefillArgs p, const __grid_constant__ CUtensorMap xmap) {
+    constexpr uint32_t kPfStages = pf_stages(HALVES), kPfMaxTokens = HALVES * kPfHalfTokens, kPfBBytes = HALVES * kPfHalfBytes;
     extern __shared__ uint8_t pf_smem_raw[];
     const uint32_t base = (smem_addr(pf_smem_raw) + 1023u) & ~1023u;            /* swizzled tiles want 1024-byte alignment */
     const uint32_t a_buf = base, b_buf = base + kPfStages * kPfABytes, bars = b_buf + kPfStages * kPfBBytes;
@@ -87,7 +92,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     const uint8_t *raw_plane = a.low + g.nibble_plane_bytes();
-    const uint32_t chunks = (a.K + kPfK - 1u) / kPfK, idesc = instr_desc_bf16(kPfRows, N);
+    const uint32_t chunks = (a.K + kPfK - 1u) / kPfK;
+    const uint32_t n_lo = min(N, kPfHalfTokens), n_hi = N - n_lo;                   /* tokens of the first and the second MMA of a step */
+    const uint32_t idesc = instr_desc_bf16(kPfRows, n_lo), idesc_hi = instr_desc_bf16(kPfRows, n_hi ? n_hi : 16u);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -188,7 +195,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
                 const uint32_t s = k % kPfStages;
                 if (k >= kPfStages && !mbar_wait_one(freed + s * 8u, ((k / kPfStages) - 1u) & 1u)) { alive = false; break; }
                 mbar_expect(landed + s * 8u, kPfBBytes);
-                tma_load_x(b_buf + s * kPfBBytes, &xmap, k * kPfK, t0, landed + s * 8u);
+#pragma unroll
+                for (uint32_t h = 0; h < HALVES; h++)                               /* (a box wholly beyond T arrives as zeros) */
+                    tma_load_x(b_buf + s * kPfBBytes + h * kPfHalfBytes, &xmap, k * kPfK, t0 + h * kPfHalfTokens, landed + s * 8u);
             }
         }
         alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
@@ -206,6 +215,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel_layout2(const Pr
                     const uint32_t accumulate = (k | kk) ? 1u : 0u;
                     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                                  ::"r"(tmem), "l"(adesc + 2u * kk), "l"(bdesc + 2u * kk), "r"(idesc), "r"(accumulate) : "memory");
+                    if (HALVES > 1u && n_hi)                                        /* the same W tile against the second half of the tokens */
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                                     ::"r"(tmem + kPfHalfTokens), "l"(adesc + 2u * kk), "l"(bdesc + (kPfHalfBytes >> 4) + 2u * kk), "r"(idesc_hi), "r"(accumulate) : "memory");
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(freed + s * 8u) : "memory");
             }
@@ -255,6 +267,9 @@ static EncodeTiledFn encode_tiled() {
     return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
+static uint32_t g_prefill_halves = 0;                            /* 0 = choose per launch; 1 or 2 = the tests' choice */
+void set_prefill_halves(int halves) { g_prefill_halves = halves == 1 || halves == 2 ? (uint32_t)halves : 0u; }
+
 cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const uint16_t *X, uint16_t *Y, uint32_t T, uint32_t ldx, uint32_t ldy) {
     PrefillArgs p{w, X, Y, T, ldx, ldy};
     /* X as a 2-D tensor (K innermost, T rows of ldx elements), boxes of 64 columns x 256 tokens, 128-byte swizzle, zeros
@@ -263,16 +278,29 @@ cudaError_t launch_prefill_layout2(cudaStream_t st, const SegmentArgs &w, const 
     if (!encode) return cudaErrorNotSupported;
     alignas(64) CUtensorMap xmap;
     const cuuint64_t dims[2] = {w.K, T}, strides[1] = {(cuuint64_t)ldx * 2u};
-    const cuuint32_t box[2] = {kPfK, kPfMaxTokens}, elem_strides[2] = {1u, 1u};
+    const cuuint32_t box[2] = {kPfK, kPfHalfTokens}, elem_strides[2] = {1u, 1u};
     if (encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2u, const_cast<uint16_t *>(X), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    const dim3 grid((w.M + kPfRows - 1u) / kPfRows, (T + kPfMaxTokens - 1u) / kPfMaxTokens);
-    prefill_kernel_layout2<<<grid, kPfThreads, kPfSmem, st>>>(p, xmap);
+    /* Two halves per CTA halve the decode work per token but also the number of CTAs, and a two-halves CTA takes about
+       1.15 x as long (measured: 6144 x 2560 x 512 runs 44 us on 96 one-half CTAs, 50 us on 48 two-halves CTAs; 19456 x 2560
+       x 512 runs 106 us on 304 and 92 us on 152): take them when they save whole waves of CTAs. */
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return cudaErrorNoDevice;
+    const uint32_t row_tiles = (w.M + kPfRows - 1u) / kPfRows;
+    const uint64_t ctas1 = (uint64_t)row_tiles * ((T + kPfHalfTokens - 1u) / kPfHalfTokens), ctas2 = (uint64_t)row_tiles * ((T + 2u * kPfHalfTokens - 1u) / (2u * kPfHalfTokens));
+    const uint64_t waves1 = (ctas1 + (uint64_t)sms - 1u) / (uint64_t)sms, waves2 = (ctas2 + (uint64_t)sms - 1u) / (uint64_t)sms;
+    const uint32_t halves = g_prefill_halves ? g_prefill_halves : (T > kPfHalfTokens && waves2 * 115u < waves1 * 100u ? 2u : 1u), tokens = halves * kPfHalfTokens;
+    const dim3 grid(row_tiles, (T + tokens - 1u) / tokens);
+    if (halves == 2u) prefill_kernel_layout2<2u><<<grid, kPfThreads, pf_smem(2u), st>>>(p, xmap);
+    else prefill_kernel_layout2<1u><<<grid, kPfThreads, pf_smem(1u), st>>>(p, xmap);
     return cudaGetLastError();
 }
 
 /* shared-memory opt-in of the prefill kernel on the current device (attributes of a function are per device) */
-void configure_prefill_kernels() { cudaFuncSetAttribute(prefill_kernel_layout2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem); }
+void configure_prefill_kernels() {
+    cudaFuncSetAttribute(prefill_kernel_layout2<1u>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_smem(1u));
+    cudaFuncSetAttribute(prefill_kernel_layout2<2u>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_smem(2u));
+}
 
 int read_prefill_status(bool clear) {
     int v = 0;

@@ -8,10 +8,22 @@ import oracle as O
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("M,K,T", [(128, 64, 16), (128, 512, 32), (300, 1000, 33), (1024, 1024, 256), (130, 1536, 300), (2048, 2560, 512), (16, 40, 1)])
-def test_prefill_matches_dequant_matmul(M, K, T):
+@pytest.mark.parametrize("M,K,T", [(128, 64, 16), (128, 512, 32), (300, 1000, 33), (1024, 1024, 256), (130, 1536, 300), (2048, 2560, 512), (16, 40, 1), (256, 1024, 1100), (384, 200, 257)])
+@pytest.mark.parametrize("halves", [1, 2])
+def test_prefill_matches_dequant_matmul(M, K, T, halves):
+    """halves: a CTA multiplies its 128 rows with one or two halves of 256 tokens (the launcher's own choice depends on how
+    many CTAs the shape gives; both kernels must agree with the reference product on every shape)."""
     from gpu_helpers import make_case, to_weight, bf16_tensor
     from nwc_b200 import _lib as L
+    L.lib.nwc_set_prefill_halves(halves)
+    try:
+        _prefill_case(M, K, T, L)
+    finally:
+        L.lib.nwc_set_prefill_halves(0)
+
+
+def _prefill_case(M, K, T, L):
+    from gpu_helpers import make_case, to_weight, bf16_tensor
     values, _ = O.synth_weights(M, K, M + K + T)
     values = values.copy(); values.reshape(-1)[:: max(1, M * K // 50)] = 0x4F00       # 2^31: a rare exponent -> exception entries
     p = O.encode(values, O.code_of(0, 2))
