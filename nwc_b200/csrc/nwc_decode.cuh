@@ -169,16 +169,19 @@ __device__ __forceinline__ void fixed_group(const FixedTables &t, uint32_t nibbl
     out23 = prmt(lowbytes, high, 0x7362u);
 }
 
-/* fp8 layout 2: bits [12g, 12g+12) of the 96-bit little-endian integer (w2:w1:w0): four 3-bit fields */
+/* fp8 layout 2: bits [12g, 12g+12) of the 96-bit little-endian integer (w2:w1:w0): four 3-bit fields (in the low 12 bits
+   of the result) */
 template <int G>
 __device__ __forceinline__ uint32_t field12(uint32_t w0, uint32_t w1, uint32_t w2) {
     constexpr int bit = 12 * G, word = bit >> 5, sh = bit & 31;
     const uint32_t a = word == 0 ? w0 : (word == 1 ? w1 : w2), b = word == 0 ? w1 : (word == 1 ? w2 : 0u);
-    return __funnelshift_r(a, b, sh) & 0xFFFu;
+    return __funnelshift_r(a, b, sh);                            /* bits 12.. are not the field's: spread_fields masks */
 }
-/* four 3-bit fields -> four bytes (field << 4) */
+/* four 3-bit fields (low 12 bits of f, anything above is ignored) -> four bytes (field << 4) */
 __device__ __forceinline__ uint32_t spread_fields(uint32_t f) {
-    return ((f & 7u) << 4) | ((f & 0x38u) << 9) | ((f & 0x1C0u) << 14) | ((f & 0xE00u) << 19);
+    /* two doubling steps (fields 2, 3 to the upper half, then fields 1 and 3 to their bytes): 7 instructions instead of 11 */
+    const uint32_t t = (f & 0x03Fu) | ((f & 0xFC0u) << 10);
+    return ((t & 0x00070007u) | ((t & 0x00380038u) << 5)) << 4;
 }
 
 /* Half a super-chunk of layout 2 (eight weights of one lane, one mma's A fragment).  `word` holds the eight
