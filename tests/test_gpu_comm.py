@@ -106,35 +106,39 @@ def _io(L, table, rank, world, in_slot, out_slot, H):
     return io, ctypes.byref(io)
 
 
-@pytest.mark.parametrize("H,Kshard", [(1024, 512), (2048, 1536), (8192, 1024)])
-def test_push_protocol_two_local_ranks(H, Kshard):
-    """o-projection shards of two ranks push into both buffers; the consumer (a column-parallel matrix with the fused
-    peer prologue) must see h + (partial0 + partial1) and the RMSNorm of it, for both ranks alike, twice in a row."""
+@pytest.mark.parametrize("H,Kshard,world", [(1024, 512, 2), (2048, 1536, 2), (8192, 1024, 2), (1024, 512, 4), (8192, 1024, 4), (8192, 1024, 8), (2048, 512, 8)])
+def test_push_protocol_local_ranks(H, Kshard, world):
+    """o-projection shards of `world` ranks (all on this GPU, one exchange buffer each) push into every buffer; the consumer
+    (a column-parallel matrix with the fused peer prologue) must see h + (the partials added in rank order) and the RMSNorm
+    of it, for every rank alike, twice in a row.  From four ranks on the consumer's CTAs share the sum (each adds up a
+    slice, all wait for all slices): h_out must still be bit-identical."""
     from nwc_b200 import NWCWeight, _lib as L
     from nwc_b200.decode import synthetic_matrix
     g = torch.Generator().manual_seed(H + Kshard)
-    o_shards = [NWCWeight(synthetic_matrix(H, Kshard, 10 + r), layout=2) for r in range(2)]       # row-parallel: [H, K / 2] each
+    o_shards = [NWCWeight(synthetic_matrix(H, Kshard, 10 + r), layout=2) for r in range(world)]   # row-parallel: [H, K / world] each
     consumer = NWCWeight(synthetic_matrix(768, H, 20), layout=2)                                  # the matrix after the sum
-    xs = [torch.randn(Kshard, generator=g).to(torch.bfloat16).cuda() for _ in range(2)]
+    xs = [torch.randn(Kshard, generator=g).to(torch.bfloat16).cuda() for _ in range(world)]
     h = torch.randn(H, generator=g).to(torch.bfloat16).cuda()
     norm_w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
-    a, b = _buffers(L, H, 2)
-    table = (ctypes.c_void_p * 2)(a, b)
+    bufs = _buffers(L, H, world)
+    table = (ctypes.c_void_p * world)(*bufs)
     try:
         for round_no in range(2):
             slot = round_no & 1
             parts = []
-            for r in range(2):                                            # both pushers first
-                keep, io = _io(L, table, r, 2, -1, slot, H)
+            for r in range(world):                                        # all pushers first
+                keep, io = _io(L, table, r, world, -1, slot, H)
                 assert _tp_linear(L, o_shards[r], 0, io, x=xs[r]) == 0
                 parts.append(o_shards[r].linear_bf16(xs[r], None))           # the same product through the plain entry point
-            total = (parts[0].float() + parts[1].float()).to(torch.bfloat16)
+            total = parts[0].float()
+            for part in parts[1:]: total = total + part.float()           # fp32, in rank order
+            total = total.to(torch.bfloat16)
             want_h = (h.float() + total.float()).to(torch.bfloat16)
             want_x = torch.zeros(H, dtype=torch.bfloat16, device="cuda")
             assert L.lib.nwc_add_rmsnorm(L.stream(), L.ptr(h), L.ptr(total), L.ptr(torch.zeros_like(h)), L.ptr(norm_w), 1e-6, H, L.ptr(want_x), None) == 0
             want_y = consumer.linear_bf16(want_x, None)
-            for r in range(2):                                            # then both consumers: every flag is already there
-                keep, io = _io(L, table, r, 2, slot, -1, H)
+            for r in range(world):                                        # then the consumers: every word is already there
+                keep, io = _io(L, table, r, world, slot, -1, H)
                 h_out, y = torch.zeros_like(h), torch.zeros(768, dtype=torch.bfloat16, device="cuda")
                 assert _tp_linear(L, consumer, 1, io, h_in=h, h_out=h_out, norm_w=norm_w, y=y) == 0
                 torch.cuda.synchronize()
@@ -142,11 +146,12 @@ def test_push_protocol_two_local_ranks(H, Kshard):
                 assert (y.float() - want_y.float()).abs().max().item() <= 2.0 ** -6 * want_y.float().abs().max().item() + 1e-6
             assert L.lib.nwc_kernel_status(1) == 0
     finally:
-        L.lib.nwc_comm_free(ctypes.c_void_p(a)); L.lib.nwc_comm_free(ctypes.c_void_p(b))
+        for buf in bufs: L.lib.nwc_comm_free(ctypes.c_void_p(buf))
 
 
-def test_push_consumer_gives_up_when_a_rank_never_pushes():
-    """Rank 1 never pushes: rank 0's consumer waits the (shortened) limit, reports status 3 and poisons its output with
+@pytest.mark.parametrize("world", [2, 4])
+def test_push_consumer_gives_up_when_a_rank_never_pushes(world):
+    """The last rank never pushes: rank 0's consumer waits the (shortened) limit, reports status 3 and poisons its output with
     NaN instead of publishing a sum that misses a partial; the context stays usable."""
     from nwc_b200 import NWCWeight, _lib as L
     from nwc_b200.decode import synthetic_matrix
@@ -155,13 +160,14 @@ def test_push_consumer_gives_up_when_a_rank_never_pushes():
     consumer = NWCWeight(synthetic_matrix(256, H, 2), layout=2)
     x = torch.ones(512, dtype=torch.bfloat16, device="cuda")
     h = torch.ones(H, dtype=torch.bfloat16, device="cuda")
-    a, b = _buffers(L, H, 2)
-    table = (ctypes.c_void_p * 2)(a, b)
+    bufs = _buffers(L, H, world)
+    table = (ctypes.c_void_p * world)(*bufs)
     L.lib.nwc_comm_set_timeout_ms(40)
     try:
-        keep, io = _io(L, table, 0, 2, -1, 0, H)
-        assert _tp_linear(L, o0, 0, io, x=x) == 0
-        keep2, io2 = _io(L, table, 0, 2, 0, -1, H)
+        for r in range(world - 1):                                        # everybody but the last rank pushes
+            keep, io = _io(L, table, r, world, -1, 0, H)
+            assert _tp_linear(L, o0, 0, io, x=x) == 0
+        keep2, io2 = _io(L, table, 0, world, 0, -1, H)
         h_out, y = torch.zeros_like(h), torch.zeros(256, dtype=torch.bfloat16, device="cuda")
         assert _tp_linear(L, consumer, 1, io2, h_in=h, h_out=h_out, norm_w=h, y=y) == 0
         torch.cuda.synchronize()
@@ -170,7 +176,7 @@ def test_push_consumer_gives_up_when_a_rank_never_pushes():
         assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
     finally:
         L.lib.nwc_comm_set_timeout_ms(2000)
-        L.lib.nwc_comm_free(ctypes.c_void_p(a)); L.lib.nwc_comm_free(ctypes.c_void_p(b))
+        for buf in bufs: L.lib.nwc_comm_free(ctypes.c_void_p(buf))
 
 
 def test_sharded_argmax_exchanges_one_word_per_rank():
