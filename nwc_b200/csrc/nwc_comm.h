@@ -22,8 +22,6 @@
 namespace nwc {
 
 constexpr uint32_t kCommMaxRanks = 8;
-constexpr uint32_t kCommMaxCtas = 256;                          /* most CTAs of a consumer that shares the sum over the ranks */
-constexpr uint32_t kCommSharedSumRanks = 4;                     /* from this many ranks on the consumer's CTAs share the sum   */
 constexpr int kStatusPeerTimeout = 3;
 
 struct CommControl {
@@ -38,13 +36,8 @@ struct CommControl {
     uint32_t reserved[2][kCommMaxRanks];        /* [192]                                                                */
     unsigned long long argmax_key[kCommMaxRanks]; /* [256] per source rank: epoch << 48 | value key << 32 | ~index      */
     uint32_t pad3[48];
-    /* the consumer's CTAs share the sum over the ranks (groups of four ranks and more): CTA i adds up its slice of the
-       vector, leaves the slice's sum of squares and then the push number here; every CTA waits for all of them */
-    uint32_t cta_ready[2][kCommMaxCtas];        /* [512]  per slot and CTA: the push number whose slice that CTA has added up */
-    float cta_squares[2][kCommMaxCtas];         /* [2560] the slice's sum of squares                                          */
 };
-static_assert(sizeof(CommControl) == 512 + 16 * kCommMaxCtas, "exchange buffer header");
-static_assert(sizeof(CommControl) % 256 == 0, "slots stay 256-byte aligned");
+static_assert(sizeof(CommControl) == 512, "exchange buffer header");
 
 constexpr uint32_t kCommHeader = sizeof(CommControl);
 #if defined(__CUDACC__)

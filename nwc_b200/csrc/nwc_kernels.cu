@@ -417,80 +417,6 @@ __device__ __forceinline__ void build_activation(const FusedInput &in, const voi
         const bool peer = in.mode == kInputPeerNorm;             /* (the entry point admits this mode only with K % 8 == 0) */
         const uint32_t epoch = peer ? expected_push(in) : 0u;
         bool ok = true;
-        if (peer && vec && in.world >= kCommSharedSumRanks && in.h_out != nullptr && gridDim.x <= kCommMaxCtas && gridDim.x > 1u) {
-            /* Many ranks: if every CTA added up the whole vector itself, all of them would read the same world x 4 K
-               bytes out of L2 at the same time (measured: 0.9 us per rank and exchange).  Instead CTA i adds up slice i of
-               the vector - every word is read once - writes it to h_out and leaves the slice's sum of squares and then
-               the push number in this rank's exchange buffer; all CTAs wait (bounded) for all slices and read the summed
-               vector, 2 K bytes, back from h_out. */
-            CommControl *ctl = const_cast<CommControl *>(reinterpret_cast<const CommControl *>(in.comm));
-            const uint32_t lo = (uint32_t)(((uint64_t)live * blockIdx.x) / gridDim.x), hi = (uint32_t)(((uint64_t)live * (blockIdx.x + 1u)) / gridDim.x);
-            float ss = 0.f;
-            for (uint32_t c = lo + tid; c < hi; c += THREADS) {
-                uint32_t o[4];
-                residual_chunk(in, true, epoch, K, c, o, ss, ok);
-                *(reinterpret_cast<uint4 *>(in.h_out) + c) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-            __threadfence();                                      /* this thread's part of the slice before the CTA's announcement */
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) scal[warp] = ss;
-            ok = __syncthreads_and(ok) != 0;
-            if (tid == 0) {
-                float mine = 0.f;
-                for (uint32_t i = 0; i < THREADS / 32u; i++) mine += scal[i];
-                *reinterpret_cast<volatile float *>(&ctl->cta_squares[in.slot][blockIdx.x]) = mine;
-                __threadfence();
-                if (ok) *reinterpret_cast<volatile uint32_t *>(&ctl->cta_ready[in.slot][blockIdx.x]) = epoch;      /* (a CTA that gave up announces nothing: the others run out too) */
-            }
-            if (ok) {
-                const unsigned long long t0 = global_timer_ns();
-                for (uint32_t i = tid; i < gridDim.x && ok; i += THREADS) {
-                    const volatile uint32_t *ready = &ctl->cta_ready[in.slot][i];
-                    while ((int32_t)(*ready - epoch) < 0) {
-                        if (global_timer_ns() - t0 > in.timeout_ns) { ok = false; break; }
-                        __nanosleep(20);
-                    }
-                }
-                __threadfence();                                  /* the slices are read after their announcements */
-            }
-            __syncthreads();                                      /* scal is read above and written below */
-            float part = 0.f;                                     /* sum of squares: the CTAs' sums in CTA order (warp w takes a run of CTAs, then the warps in order) */
-            {
-                const uint32_t per = (gridDim.x + THREADS / 32u - 1u) / (THREADS / 32u), first = warp * per;
-                if (lane == 0) {
-                    for (uint32_t i = first; i < min(first + per, gridDim.x); i++) part += *reinterpret_cast<const volatile float *>(&ctl->cta_squares[in.slot][i]);
-                    scal[warp] = part;
-                }
-            }
-            if (!__syncthreads_and(ok)) {
-                if (tid == 0) atomicExch(&g_kernel_status, kStatusPeerTimeout);
-                for (uint32_t c = tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u));
-                __syncthreads();
-                return;
-            }
-            float tot = 0.f;
-            for (uint32_t i = 0; i < THREADS / 32u; i++) tot += scal[i];
-            const float inv = rsqrtf(tot / (float)K + in.eps);
-            auto summed = [&](uint32_t c, uint4 weight) {          /* chunk c of the summed vector (written by another CTA: never from L1), normalised */
-                const uint4 hv = ld_volatile128(reinterpret_cast<const uint4 *>(in.h_out) + c);
-                const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
-                return normalised_chunk(hw, weight, inv);
-            };
-            if (nr.in_regs) {
-#pragma unroll
-                for (uint32_t i = 0; i < kNormRegChunks; i++) {
-                    const uint32_t c = tid + i * THREADS;
-                    if (c < live) sts128(xs_addr + c * 16u, summed(c, nr.w[i]));
-                }
-                for (uint32_t c = live + tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0u, 0u, 0u, 0u));
-            } else {
-                for (uint32_t c = tid; c < chunks; c += THREADS)
-                    sts128(xs_addr + c * 16u, c < live ? summed(c, lds128(nw_addr + c * 16u)) : make_uint4(0u, 0u, 0u, 0u));
-            }
-            __syncthreads();
-            return;
-        }
         const bool write_h = blockIdx.x == 0 && in.h_out != nullptr;
         float ss = 0.f;
         uint32_t held[kNormRegChunks][4];                        /* register path: the thread's chunks of h_out */

@@ -110,8 +110,7 @@ def _io(L, table, rank, world, in_slot, out_slot, H):
 def test_push_protocol_local_ranks(H, Kshard, world):
     """o-projection shards of `world` ranks (all on this GPU, one exchange buffer each) push into every buffer; the consumer
     (a column-parallel matrix with the fused peer prologue) must see h + (the partials added in rank order) and the RMSNorm
-    of it, for every rank alike, twice in a row.  From four ranks on the consumer's CTAs share the sum (each adds up a
-    slice, all wait for all slices): h_out must still be bit-identical."""
+    of it, for every rank alike, twice in a row."""
     from nwc_b200 import NWCWeight, _lib as L
     from nwc_b200.decode import synthetic_matrix
     g = torch.Generator().manual_seed(H + Kshard)
