@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--prompt", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="", help="time one token matvec alone: lm_head | qkv | o | gate_up | down | MxK (small case for ncu)")
-    ap.add_argument("--op", default="", help="time one of the other kernels alone (small cases for ncu): gather:N | attention:POS | encode:MxK | prefill:MxKxT | native_fp8:MxK")
+    ap.add_argument("--op", default="", help="time one of the other kernels alone (small cases for ncu): gather:N | attention:POS | encode:MxK | prefill:MxKxT | native_fp8:MxK | exchange:WORLD")
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
@@ -373,6 +373,43 @@ def op_only(a, cfg):
         us = timed(call, reps=n8)
         out.update({"shape": [M, K], "us": us, "kernel": "native_fp8_kernel", "roofline": {"bound": "hbm", "achieved": (M * K + 4 * M) / us / 1e3, "peak": peak, "peak_kind": kind, "unit": "GB/s",
                                                                                                "frac": (M * K + 4 * M) / us / 1e3 / peak}})
+    elif what == "exchange":        # tensor-parallel consumer on ONE GPU: WORLD local exchange buffers stand in for the ranks' buffers
+        import ctypes
+        world = int(arg or 8)
+        H, rows = cfg.hidden, 2 * cfg.intermediate // world
+        bufs = []
+        for _ in range(world):
+            p = ctypes.c_void_p()
+            if L.lib.nwc_comm_alloc(ctypes.byref(p), H): raise RuntimeError("nwc_comm_alloc failed")
+            bufs.append(p.value)
+        table = (ctypes.c_void_p * world)(*bufs)
+        o_shard = NWCWeight(synthetic_matrix(H, cfg.n_q * cfg.head_dim // world, 1), layout=2)                 # row-parallel producer: [H, K / world]
+        copies = max(2, min(8, -(-(400 << 20) // (rows * H * 3 // 2))))
+        gate_up = [NWCWeight(synthetic_matrix(rows, H, 10 + i), layout=2) for i in range(copies)]              # the consumer's shard, rotating copies
+        bf = lambda n, v=0.0: torch.full((n,), v, dtype=torch.bfloat16, device="cuda")
+        attn, h, h2, nw, y, delta = bf(o_shard.in_features, 0.1), bf(H, 1.0), bf(H), bf(H, 1.0), bf(rows), bf(H, 0.01)
+        xtmp = bf(H + 32)
+        L.lib.nwc_set_dependent_launch(1)
+        def fused(w, mode, opt, **kw):
+            g_ = lambda k: L.ptr(kw.get(k))
+            err = L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, g_("x"), g_("h_in"), g_("delta"), g_("h_out"),
+                                             g_("norm_w"), cfg.eps, None, L.ptr(xtmp), None, None, L.ptr(w.scratch), g_("y"), w.n, w.block, w.in_features, w.code, opt)
+            if err: raise RuntimeError(f"nwc_linear_fused_opt error {err}")
+        for r in range(world):          # every "rank" pushes its partial of slot 0 into every buffer, once: the words stay valid for all timed calls
+            fused(o_shard, 0, ctypes.byref(L.FusedOptions(ctypes.cast(table, ctypes.c_void_p), r, world, -1, 0, H, None)), x=attn)
+        torch.cuda.synchronize()
+        peer_opt = L.FusedOptions(ctypes.cast(table, ctypes.c_void_p), 0, world, 0, -1, H, None)
+        it = [0]
+        def consumer(peer):
+            w = gate_up[it[0] % copies]; it[0] += 1
+            if peer: fused(w, 1, ctypes.byref(peer_opt), h_in=h, h_out=h2, norm_w=nw, y=y)
+            else: fused(w, 1, None, h_in=h, delta=delta, h_out=h2, norm_w=nw, y=y)
+        local_us = timed(lambda: consumer(False), reps=2 * copies)
+        peer_us = timed(lambda: consumer(True), reps=2 * copies)
+        if L.lib.nwc_kernel_status(1): raise RuntimeError("a bounded wait inside a kernel gave up")
+        out.update({"world": world, "consumer": [rows, H], "kernel": "ring_kernel_layout2 (RMSNorm prologue over the ranks' pushed partials)", "us_local_delta": local_us,
+                    "us_peer_partials": peer_us, "us_sum_over_ranks": peer_us - local_us, "partial_bytes_read_per_cta": world * H * 4})
+        for b in bufs: L.lib.nwc_comm_free(ctypes.c_void_p(b))
     else:
         raise SystemExit(f"unknown --op {a.op}")
     if L.lib.nwc_kernel_status(1): raise RuntimeError("a bounded wait inside a kernel gave up")
