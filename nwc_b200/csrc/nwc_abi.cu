@@ -139,7 +139,7 @@ static int linear_fused(void *stream, const uint8_t *data, const uint32_t *bases
     }
     FusedInput in{in_mode, h_in, delta, h_out, norm_w, eps, gate_up, nullptr, 0u, 0u, g_peer_timeout_ns};
     if (peer_in) { in.comm = static_cast<const uint8_t *>(tp->buffers[tp->rank]); in.world = (uint32_t)tp->world; in.slot = (uint32_t)tp->in_slot; }
-    if (!peer_in && !peer_out && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) {
+    if (!peer_in && !peer_out && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u && (side || small_layout0_preferred(M, K, sms, mode))) {
         SegmentArgs a{data, bases, hdr, lut, low, x, scratch, nullptr, bias, scale, y, M, K, 0, 1, 0};
         return (int)launch_small_layout0(elem, sms, (cudaStream_t)stream, a, in, side);
     }
@@ -200,7 +200,7 @@ NWC_EXPORT int nwc_linear_launches(uint64_t n, uint32_t K, int elem, int fused_m
     if (!sms) return -1;
     const uint32_t M = (uint32_t)(n / K);
     const Geometry g(M, K, layout_of(elem));
-    if (fused_mode >= 0 && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u) return 1;
+    if (fused_mode >= 0 && layout_of(elem) == 0 && g.nb <= 2u * (uint32_t)sms * 32u && g.K16 <= 40960u && small_layout0_preferred(M, K, sms, fused_mode)) return 1;
     const bool ring = fused_mode >= 0 && token_path_fuses_input(elem, M, K, fused_mode);
     return count_token_launches(elem, sms, M, K, ring) + (fused_mode > 0 && !ring ? 1 : 0);
 }

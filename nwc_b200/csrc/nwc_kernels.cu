@@ -1989,6 +1989,21 @@ int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_f
     return choose_splits(g, kModeLinear, code, sms) > 1 ? 2 : 1;
 }
 
+/* Layout 0, a matrix of at most two blocks per resident warp: the single-launch small-matrix kernel, or the prologue
+   kernel + the large-matrix ring kernel + finalize?  Both are bound by the serial walk of a block (about 5.5 us on B200).
+   The small kernel gives a row group to a team of up to 8 warps and runs its row groups in rounds of 2 CTAs per SM, so a
+   matrix of many column blocks (2560 x 9728: 19 blocks per group, 320 groups) walks 3 blocks per warp in each of 2 rounds
+   (35 us measured) where the ring kernel's 32 warps per SM walk 2 (22 us + the prologue launch); matrices of few column
+   blocks are faster on the small kernel (4096 x 1024: 8 against 16 us).  Measured fixed costs: 4 us and 14 us. */
+bool small_layout0_preferred(uint32_t M, uint32_t K, int sms, int input_mode) {
+    const Geometry g(M, K, 0);
+    const uint32_t wg = small_group_warps(g.CB), per_pass = kSmallWarps / wg, passes = (g.groups + per_pass - 1u) / per_pass;
+    const uint32_t rounds = (passes + 2u * (uint32_t)sms - 1u) / (2u * (uint32_t)sms), walks = (g.CB + wg - 1u) / wg;
+    const uint32_t small_cost = 55u * walks * rounds + 40u;                                               /* tenths of a microsecond */
+    const uint32_t ring_cost = 55u * ((g.nb + 32u * (uint32_t)sms - 1u) / (32u * (uint32_t)sms)) + 140u + (input_mode != kInputPlain ? 35u : 0u);
+    return g_disable_ring || small_cost <= ring_cost;
+}
+
 /* the token path of this matrix builds its activation vector itself (nwc_linear_fused needs no prologue launch) */
 bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode) {
     const Geometry g(M, K, layout_of(code));

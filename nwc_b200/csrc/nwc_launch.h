@@ -72,6 +72,7 @@ int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gav
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input = nullptr, const NextMatrix *next = nullptr);
 void set_next_fill_stages(uint32_t stages);   /* tests and tuning: ring stages per warp fetched ahead for the next launch (0 = off) */
 bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode);
+bool small_layout0_preferred(uint32_t M, uint32_t K, int sms, int input_mode);   /* layout 0: single-launch small-matrix kernel rather than prologue + ring kernel + finalize */
 void configure_segment_kernels();
 int count_token_launches(int code, int sms, uint32_t M, uint32_t K, bool allow_fix = false);
 

@@ -11,6 +11,9 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("M,K,layout,elem", [(4096, 1024, 0, 0), (1024, 2048, 0, 0), (1024, 3072, 0, 0), (6144, 1024, 0, 0), (100, 1000, 0, 0), (13, 40, 0, 0),
                                              (1024, 5120, 0, 0), (256, 1024, 0, 1), (512, 1024, 2, 0), (512, 1024, 1, 0),
+                                             # layout 0 with many column blocks and more row groups than one round of the small kernel holds:
+                                             # the entry point takes prologue + ring kernel + finalize instead
+                                             (2560, 9728, 0, 0),
                                              (6144, 2560, 2, 0), (2560, 9728, 2, 0), (100, 1000, 2, 0), (13, 40, 2, 0), (48, 1004, 2, 0),
                                              # layout 2 shapes whose row groups do not divide over the SMs: equal runs per CTA, cut row groups completed
                                              # inside the kernel by the last CTA to arrive (no finalize launch)
