@@ -212,3 +212,29 @@ def test_shard_files_hold_what_the_loader_repacks(tmp_path, layout, tied):
     ref = DecodeEngine.from_pretrained(d, max_len=64); ref.prefill(prompt); want = ref.generate(24).tolist()
     eng = DecodeEngine.from_pretrained(out1, max_len=64); eng.prefill(prompt)
     assert eng.generate(24).tolist() == want
+
+
+@pytest.mark.parametrize("stored", [0, 1])
+def test_checkpoint_in_another_layout_served_as_layout_2(tmp_path, stored):
+    """relayout=2: a checkpoint written in layout 0 or 1 is re-encoded into layout 2 while loading - every matrix must
+    decode to exactly the weights it was stored with, report layout 2, and the engine must produce the tokens of an engine
+    built in layout 2 from the bf16 matrices (the same kernels on the same weights)."""
+    from nwc_b200 import convert, fuse, save_pretrained
+    from nwc_b200.decode import DecodeEngine, DecoderConfig, DecoderWeights
+    hf_cfg, model = qwen3_model(tied=False)
+    sd = {k: v.clone() for k, v in model.state_dict().items()}
+    fuse(model, layout=stored, verbose=False); convert(model, verbose=False, layout=stored)
+    d = str(tmp_path / "ckpt"); save_pretrained(model, d, base_model="test"); del model
+    as_stored = DecoderWeights.from_checkpoint(d)
+    relaid = DecoderWeights.from_checkpoint(d, relayout=2)
+    for a, b in zip(as_stored.matrices(), relaid.matrices()):
+        assert a.layout == stored and b.layout == 2
+        assert torch.equal(a.dequant(), b.dequant())
+    cfg = DecoderConfig("t", 2, 256, 1024, 4, 2, 64, 2048, False, True, rope_theta=1e6, eps=1e-6)
+    source, vector = engine_sources(sd)
+    ref = DecodeEngine(DecoderWeights(cfg, source, vector, layout=2), max_len=96)
+    eng = DecodeEngine.from_pretrained(d, max_len=96, relayout=2)
+    prompt = list(range(3, 15))
+    ref.prefill(prompt); want = ref.generate(48).tolist()
+    eng.prefill(prompt)
+    assert eng.generate(48).tolist() == want
