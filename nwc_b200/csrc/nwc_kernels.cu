@@ -1460,7 +1460,7 @@ __device__ __forceinline__ float prefix_block_layout0(WIN &W, const SegmentArgs 
    low bytes one slot ahead from the plane, the sums stay in the mma accumulators d (rows r and r + 8 of lane group r). */
 template <class WIN, int ELEM>
 __device__ __forceinline__ void prefix_block_layout1(WIN &W, const SegmentArgs &a, const Geometry &g, uint32_t rb, uint32_t cb, uint32_t lane,
-                                                     uint32_t table, uint32_t sym, uint32_t four, float (&d)[4]) {
+                                                     uint32_t table, uint32_t sym, uint32_t four, float (&d)[4], uint32_t xs = 0u) {
     constexpr uint32_t RB = ELEM == kFp8 ? 8u : 16u;             /* raw bytes per lane and super-chunk */
     const uint32_t q = lane & 3u, nsc = g.supers_in(cb);
     const uint8_t *rp = a.low + ((uint64_t)(rb * g.slots + cb * 16u) * kLanes + lane) * RB;
@@ -1470,7 +1470,9 @@ __device__ __forceinline__ void prefix_block_layout1(WIN &W, const SegmentArgs &
         const uint4 cw = ahead;
         rp += kLanes * RB;                                       /* one slot ahead, unguarded: the plane carries 512 B of slack */
         ahead = ELEM == kFp8 ? expand_nibbles(ldg_stream64(rp)) : ldg_stream128(rp);
-        XFrag8<false> xf; xf.load(a.x, cb * kBlockCols + sc * 32u + 8u * q);
+        XFrag8<false> xf;
+        if (xs) xf.load_shared(xs + (cb * kBlockCols + sc * 32u + 8u * q) * 2u);           /* x staged by the CTA */
+        else xf.load(a.x, cb * kBlockCols + sc * 32u + 8u * q);
         const uint32_t c[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -1482,13 +1484,27 @@ __device__ __forceinline__ void prefix_block_layout1(WIN &W, const SegmentArgs &
     __syncwarp();                                                /* all lanes are done with the stage that held this block */
 }
 
+/* in.mode != kInputPlain (bf16 x only): the CTA builds the activation vector itself in shared memory behind the rings
+   (RMSNorm of the residual stream or SwiGLU of a gate/up vector, as in the layout-2 kernel), so nwc_linear_fused needs no
+   prologue launch; the launcher takes this form only when the vector and the norm weights' registers suffice. */
 template <int LAYOUT, int ELEM, bool XF32, uint32_t THREADS, uint32_t STAGE>
-__device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const FlatPlan &plan, const uint32_t four) {
+__device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const FlatPlan &plan, const uint32_t four, const FusedInput &in) {
     constexpr uint32_t kWarpBytes = 2u * STAGE + 256u + 16u;
     constexpr uint32_t MR = ELEM == kFp8 ? kMaxRankFp8 : kMaxRankBf16;
     extern __shared__ __align__(128) uint8_t ring_smem[];
     uint32_t *tables = reinterpret_cast<uint32_t *>(ring_smem);
     stage_tables(tables, a.lut, threadIdx.x, THREADS);
+    uint32_t xs_addr = 0u;
+    if (!XF32 && in.mode != kInputPlain) {                       /* (uniform over the grid; before any warp leaves: it ends with a CTA barrier) */
+        const Geometry gx(a.M, a.K, LAYOUT);
+        uint8_t *behind = ring_smem + 16416u + (THREADS / 32u) * kWarpBytes;
+        float *scal = reinterpret_cast<float *>(behind);
+        uint16_t *xs = reinterpret_cast<uint16_t *>(behind + 128u);
+        NormWeights norm_regs;
+        stage_norm_weight<THREADS>(in, a.K, xs, norm_regs);     /* (the weights fit the registers: the launcher checked) */
+        build_activation<THREADS>(in, a.x, a.K, (gx.K16 + 31u) & ~31u, xs, xs, scal, norm_regs);      /* zero up to the end of the last 32-column slot (layout 1 reads whole slots) */
+        xs_addr = smem_addr(xs);
+    }
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t table = smem_addr(tables), sym = table + 4u * kTableWords;
     uint8_t *mine = ring_smem + 16416u + warp * kWarpBytes;
@@ -1536,13 +1552,13 @@ __device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const Fla
             }
             phase_bits ^= 1u << buf;
             SmemWindow<MR> W; W.open(stages + buf * STAGE + (base - start) + 4u * before);
-            if (LAYOUT == 0) row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
-            else prefix_block_layout1<SmemWindow<MR>, ELEM>(W, a, g, rb, cb, lane, table, sym, four, d);
+            if (LAYOUT == 0) row_sum += prefix_block_layout0<SmemWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
+            else prefix_block_layout1<SmemWindow<MR>, ELEM>(W, a, g, rb, cb, lane, table, sym, four, d, xs_addr);
         } else {
             GlobalWindow<MR> W; W.sym_ptr = reinterpret_cast<const uint8_t *>(tables + kTableWords);
             W.open(reinterpret_cast<const uint32_t *>(a.data + base) + before);
-            if (LAYOUT == 0) row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash);
-            else prefix_block_layout1<GlobalWindow<MR>, ELEM>(W, a, g, rb, cb, lane, table, sym, four, d);
+            if (LAYOUT == 0) row_sum += prefix_block_layout0<GlobalWindow<MR>, ELEM, XF32>(W, a, g, rb, cb, lane, table, sym, four, stash, xs_addr);
+            else prefix_block_layout1<GlobalWindow<MR>, ELEM>(W, a, g, rb, cb, lane, table, sym, four, d, xs_addr);
         }
         if (b + 2u < b1) issue(b + 2u, words_after);              /* the stage just decoded is free again (all lanes passed the block's last __syncwarp) */
         words = words_next; words_next = words_after;
@@ -1557,15 +1573,27 @@ __device__ __forceinline__ void prefix_ring_body(const SegmentArgs &a, const Fla
 }
 
 template <int ELEM, bool XF32>
-__global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(const SegmentArgs a, const FlatPlan plan, const uint32_t four) {
-    prefix_ring_body<0, ELEM, XF32, kPrefixThreads, kPrefixStageBytes>(a, plan, four);
+__global__ void __launch_bounds__(kPrefixThreads, 1) prefix_ring_kernel_layout0(const SegmentArgs a, const FlatPlan plan, const uint32_t four, const FusedInput in) {
+    prefix_ring_body<0, ELEM, XF32, kPrefixThreads, kPrefixStageBytes>(a, plan, four, in);
 }
 /* layout 1: a block is 16 x 512 (twice the stream), so half as many warps with stages twice as large; x is bf16 */
 constexpr uint32_t kPrefix1Threads = 512, kPrefix1StageBytes = 4608;
 constexpr uint32_t kPrefix1SmemBytes = 16416u + (kPrefix1Threads / 32u) * (2u * kPrefix1StageBytes + 256u + 16u);
+/* shared memory behind the rings when the kernel builds x itself: 128 bytes of reduction scratch + the vector */
+static inline size_t prefix_fused_bytes(const Geometry &g) { return 128u + (size_t)((g.K16 + 31u) & ~31u) * 2u; }
+/* the layout 0 / 1 ring kernel can build x for this matrix: the vector fits behind the rings and the RMSNorm weights fit the
+   registers of the threads that normalise them (or K is not a multiple of 8: the scalar path reads them from memory) */
+static inline bool prefix_ring_fuses(int code, const Geometry &g, int input_mode) {
+    const int layout = layout_of(code);
+    if (layout > 1 || input_mode == kInputPlain || input_mode == kInputPeerNorm) return false;
+    const uint32_t threads = layout == 0 ? kPrefixThreads : kPrefix1Threads;
+    const size_t rings = layout == 0 ? kPrefixSmemBytes : kPrefix1SmemBytes;
+    if (rings + prefix_fused_bytes(g) > kRingMaxSmem) return false;
+    return (g.K & 7u) != 0u || (g.K >> 3) <= kNormRegChunks * threads;
+}
 template <int ELEM>
-__global__ void __launch_bounds__(kPrefix1Threads, 1) prefix_ring_kernel_layout1(const SegmentArgs a, const FlatPlan plan, const uint32_t four) {
-    prefix_ring_body<1, ELEM, false, kPrefix1Threads, kPrefix1StageBytes>(a, plan, four);
+__global__ void __launch_bounds__(kPrefix1Threads, 1) prefix_ring_kernel_layout1(const SegmentArgs a, const FlatPlan plan, const uint32_t four, const FusedInput in) {
+    prefix_ring_body<1, ELEM, false, kPrefix1Threads, kPrefix1StageBytes>(a, plan, four, in);
 }
 
 /* ---- layout 0, small matrices of the decode step: one launch, activation prologue fused ------------------------------ */
@@ -2007,7 +2035,8 @@ bool small_layout0_preferred(uint32_t M, uint32_t K, int sms, int input_mode) {
 /* the token path of this matrix builds its activation vector itself (nwc_linear_fused needs no prologue launch) */
 bool token_path_fuses_input(int code, uint32_t M, uint32_t K, int input_mode) {
     const Geometry g(M, K, layout_of(code));
-    return !g_disable_ring && ring_covers(code, g, input_mode);
+    if (g_disable_ring) return false;
+    return layout_of(code) == 2 ? ring_covers(code, g, input_mode) : prefix_ring_fuses(code, g, input_mode);
 }
 
 static uint32_t g_next_fill_stages = kRingStages;
@@ -2045,11 +2074,15 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     const size_t smem = layout == 2 ? 0 : kTableSmemBytes + (size_t)warps_per_cta * 64u * sizeof(float);
     cudaError_t err;
     FlatPlan plan;
+    FusedInput fin{kInputPlain, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr, nullptr, 0u, 0u, 0ull};
+    if (input && a.x_bf16 && prefix_ring_fuses(code, g, input->mode)) fin = *input;       /* the layout 0 / 1 ring kernels build x themselves */
+    const size_t fused_bytes = fin.mode != kInputPlain ? prefix_fused_bytes(g) : 0u;
     if (layout == 0 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
         make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefixThreads / 32u), plan);
         const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
-        if (elem == kFp8) { if (a.x_bf16) prefix_ring_kernel_layout0<kFp8, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kFp8, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
-        else { if (a.x_bf16) prefix_ring_kernel_layout0<kBf16, false><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); else prefix_ring_kernel_layout0<kBf16, true><<<rgrid, kPrefixThreads, kPrefixSmemBytes, st>>>(a, plan, 4u); }
+        const size_t rsmem = kPrefixSmemBytes + fused_bytes;
+        if (elem == kFp8) { if (a.x_bf16) prefix_ring_kernel_layout0<kFp8, false><<<rgrid, kPrefixThreads, rsmem, st>>>(a, plan, 4u, fin); else prefix_ring_kernel_layout0<kFp8, true><<<rgrid, kPrefixThreads, rsmem, st>>>(a, plan, 4u, fin); }
+        else { if (a.x_bf16) prefix_ring_kernel_layout0<kBf16, false><<<rgrid, kPrefixThreads, rsmem, st>>>(a, plan, 4u, fin); else prefix_ring_kernel_layout0<kBf16, true><<<rgrid, kPrefixThreads, rsmem, st>>>(a, plan, 4u, fin); }
         err = cudaGetLastError();
         if (err == cudaSuccess && !plan.direct) {
             finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
@@ -2060,8 +2093,8 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
     if (layout == 1 && mode == kModeLinear && !g_disable_ring && a.splits_forced == 0) {
         make_flat_plan(g, g.CB, (uint64_t)sms * (kPrefix1Threads / 32u), plan);
         const int rgrid = (int)(plan.warps < (uint32_t)sms ? plan.warps : (uint32_t)sms);
-        if (elem == kFp8) prefix_ring_kernel_layout1<kFp8><<<rgrid, kPrefix1Threads, kPrefix1SmemBytes, st>>>(a, plan, 4u);
-        else prefix_ring_kernel_layout1<kBf16><<<rgrid, kPrefix1Threads, kPrefix1SmemBytes, st>>>(a, plan, 4u);
+        if (elem == kFp8) prefix_ring_kernel_layout1<kFp8><<<rgrid, kPrefix1Threads, kPrefix1SmemBytes + fused_bytes, st>>>(a, plan, 4u, fin);
+        else prefix_ring_kernel_layout1<kBf16><<<rgrid, kPrefix1Threads, kPrefix1SmemBytes + fused_bytes, st>>>(a, plan, 4u, fin);
         err = cudaGetLastError();
         if (err == cudaSuccess && !plan.direct) {
             finalize_flat_kernel<<<(a.M + 255u) / 256u, 256, 0, st>>>(a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
@@ -2152,12 +2185,12 @@ void configure_segment_kernels() {
         void *parts = nullptr;
         if (cudaGetSymbolAddress(&parts, g_cut_part) == cudaSuccess) cudaMemset(parts, 0xFF, sizeof(g_cut_part)); else cudaGetLastError();
     }
-    cudaFuncSetAttribute(prefix_ring_kernel_layout1<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
-    cudaFuncSetAttribute(prefix_ring_kernel_layout1<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefix1SmemBytes);
-    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
-    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
-    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
-    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmemBytes);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout1<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);      /* rings (+ the activation vector) */
+    cudaFuncSetAttribute(prefix_ring_kernel_layout1<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(prefix_ring_kernel_layout0<kFp8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     opt_in_smem<0, kBf16>(); opt_in_smem<0, kFp8>(); opt_in_smem<1, kBf16>(); opt_in_smem<1, kFp8>();
 }
 
