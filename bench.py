@@ -52,6 +52,7 @@ def parse():
     ap.add_argument("--vs-ref", action="store_true", help="--kernel: also time the reference's own kernel (oracle/_ref/nwc_ops.so) on the same matrices")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replicas", "tp"], help="N > 1: tensor parallel (auto, tp) or independent replicas")
     ap.add_argument("--tp-reduce", default="push", choices=["push", "pull", "nccl"], help="how the partial outputs of o and down are summed over the ranks")
+    ap.add_argument("--peer-sharing", type=int, default=0, help="tensor parallel: from this many ranks on, clusters of CTAs share the sum of the pushed partials (0 = every CTA adds up all of them; A/B)")
     ap.add_argument("--pool", type=int, default=0, help="1: layout-2 matvecs on the kernel whose warps draw stages from a per-CTA pool instead of one fixed run per warp (A/B)")
     ap.add_argument("--prefetch-next", type=int, default=1, help="0: matvecs do not ask L2 for the next matrix's first bytes at their end (A/B)")
     ap.add_argument("--side-tables", type=int, default=0, help="1: layout 0 decoder-layer matrices on four warps per block along a side table instead of one (A/B)")
@@ -195,6 +196,7 @@ def kernel_only(a, cfg):
     torch.cuda.set_device(0)
     L.lib.nwc_set_fixup_plans(int(a.fixup))
     L.lib.nwc_set_pool_kernels(int(a.pool))
+    L.lib.nwc_set_peer_sharing(int(a.peer_sharing))
     L.lib.nwc_set_dependent_launch(int(a.dependent_launch))
     first = NWCWeight(synthetic_matrix(M, K, 1), layout=a.layout, elem=a.elem)
     copies = max(1, min(64, -(-(320 << 20) // first.bytes)))          # rotate over > 320 MB so that no launch finds its matrix in L2
@@ -390,6 +392,7 @@ def op_only(a, cfg):
         attn, h, h2, nw, y, delta = bf(o_shard.in_features, 0.1), bf(H, 1.0), bf(H), bf(H, 1.0), bf(rows), bf(H, 0.01)
         xtmp = bf(H + 32)
         L.lib.nwc_set_dependent_launch(1)
+        L.lib.nwc_set_peer_sharing(int(a.peer_sharing))
         def fused(w, mode, opt, **kw):
             g_ = lambda k: L.ptr(kw.get(k))
             err = L.lib.nwc_linear_fused_opt(L.stream(), L.ptr(w.data), L.ptr(w.bases), L.ptr(w.hdr), L.ptr(w.lut), L.ptr(w.low), mode, g_("x"), g_("h_in"), g_("delta"), g_("h_out"),
@@ -408,7 +411,8 @@ def op_only(a, cfg):
         peer_us = timed(lambda: consumer(True), reps=2 * copies)
         if L.lib.nwc_kernel_status(1): raise RuntimeError("a bounded wait inside a kernel gave up")
         out.update({"world": world, "consumer": [rows, H], "kernel": "ring_kernel_layout2 (RMSNorm prologue over the ranks' pushed partials)", "us_local_delta": local_us,
-                    "us_peer_partials": peer_us, "us_sum_over_ranks": peer_us - local_us, "partial_bytes_read_per_cta": world * H * 4})
+                    "us_peer_partials": peer_us, "us_sum_over_ranks": peer_us - local_us, "partial_bytes_read_per_cta": world * H * 4,
+                    "peer_sharing_from_ranks": int(a.peer_sharing)})
         for b in bufs: L.lib.nwc_comm_free(ctypes.c_void_p(b))
     else:
         raise SystemExit(f"unknown --op {a.op}")
@@ -483,6 +487,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
     tp = is_tp(a, world)
     L.lib.nwc_set_pool_kernels(int(a.pool))
+    L.lib.nwc_set_peer_sharing(int(a.peer_sharing))
     if tp and a.tp_reduce == "nccl": a.dependent_launch = 0         # NCCL kernels sit in the chain: keep plain stream order around them
     max_len = a.prompt + 2 * (a.warmup + a.steps) + 16
     if tp:      # one model sharded over all ranks: same seed everywhere, every rank keeps its shard and decodes the same sequence

@@ -119,6 +119,14 @@ void nwc_set_fixup_plans(int on);
    tests); on = 0 (default) goes back. */
 void nwc_set_pool_kernels(int on);
 
+/* Tensor-parallel token matvecs whose input is the sum of the ranks' pushed partials (nwc_linear_fused_opt, tp_in): from
+   min_world ranks on (0 = never, the default) the layout-2 kernel is launched as clusters of 2 or 4 CTAs that each add up
+   a share of the partials and exchange the sums through distributed shared memory, instead of every CTA adding up all of
+   them.  Same residual stream; the RMSNorm's sum of squares is added in another order.  Off by default: the sum itself
+   gets cheaper (8.4 -> 4.4 us at 8 ranks) but a cluster launch gives up more than that at the kernel boundary before it
+   (measured: 155 against 169 tokens/s on 8 GPUs); kept for A/B tests. */
+void nwc_set_peer_sharing(int min_world);
+
 /* nwc_linear_bf16 with a bf16 activation vector for every layout (layout 0: bf16[K16]; layouts 1, 2: bf16[K rounded up
    to 32]): the decode loop keeps activations in bf16, which spares layout 0 the fp32 copy and the second mma pass. */
 int nwc_linear_x16(void *stream, const uint8_t *data, const uint32_t *bases, const uint8_t *hdr, const uint32_t *lut,

@@ -61,6 +61,7 @@ _SIGNATURES = {
     "nwc_set_prefill_halves": (None, [I]),
     "nwc_set_fixup_plans": (None, [I]),
     "nwc_set_pool_kernels": (None, [I]),
+    "nwc_set_peer_sharing": (None, [I]),
     "nwc_comm_bytes": (U64, [U32]),
     "nwc_comm_alloc": (I, [P, U32]),
     "nwc_comm_free": (I, [P]),

@@ -276,3 +276,4 @@ NWC_EXPORT void nwc_set_prefill_halves(int halves) { set_prefill_halves(halves);
 NWC_EXPORT void nwc_set_ring_kernels(int on) { set_ring_kernels(on != 0); }
 NWC_EXPORT void nwc_set_fixup_plans(int on) { set_fixup_plans(on != 0); }
 NWC_EXPORT void nwc_set_pool_kernels(int on) { set_pool_kernels(on != 0); }
+NWC_EXPORT void nwc_set_peer_sharing(int min_world) { set_peer_sharing(min_world); }

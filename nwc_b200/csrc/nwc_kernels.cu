@@ -406,6 +406,97 @@ __device__ __forceinline__ uint4 normalised_chunk(const uint32_t (&h)[4], uint4 
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+/* distributed shared memory of a thread-block cluster */
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cluster_sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void cluster_sts64(uint32_t addr, float a, float b) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+/* kInputPeerNorm when the launch runs clusters of `ctas` CTAs (FusedInput::share).  Every CTA of a launch needs the whole
+   vector h = h_in + the ranks' partials, and with one CTA per SM every SM would pull world x 4 K bytes out of L2 for it:
+   at 8 ranks that is 38 MB per launch from the same few lines, 7 to 8 us.  Here CTA `rank` of a cluster adds up chunks
+   [rank, rank + 1) * live / ctas only and stores the sums, and its warps' sums of squares, into the shared memory of
+   every CTA of the cluster; after one cluster barrier each CTA normalises its own copy.  The caller has made every
+   thread arrive at the cluster barrier once (at the kernel's top): the wait for that arrival, after the loads, is what
+   guarantees that the other CTAs run before their shared memory is written.  cl: ctas * THREADS / 32 pairs of floats
+   {sum of squares, 1 = all of the warp's words arrived}.  Needs the RMSNorm weight in registers (nr.in_regs) and
+   live % ctas == 0.  The sum of squares is added in another order than build_activation adds it (lane-strided, then a
+   butterfly), the same one in every CTA of every rank.  Ends with __syncthreads(). */
+template <uint32_t THREADS>
+__device__ __forceinline__ void build_activation_shared(const FusedInput &in, uint32_t K, uint32_t cols, uint16_t *xs, float *cl, const NormWeights &nr,
+                                                        uint32_t ctas, uint32_t rank, bool first_cluster) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t xs_addr = smem_addr(xs), cl_addr = smem_addr(cl), chunks = cols >> 3, live = K >> 3, per = live / ctas;
+    const uint32_t epoch = expected_push(in);
+    const bool write_h = first_cluster && in.h_out != nullptr;
+    bool ok = true;
+    float ss = 0.f;
+    uint32_t held[kNormRegChunks][4];
+#pragma unroll
+    for (uint32_t i = 0; i < kNormRegChunks; i++) {
+        const uint32_t j = tid + i * THREADS;
+        if (j < per) {
+            const uint32_t c = rank * per + j;
+            residual_chunk(in, true, epoch, K, c, held[i], ss, ok);
+            if (write_h) *(reinterpret_cast<uint4 *>(in.h_out) + c) = make_uint4(held[i][0], held[i][1], held[i][2], held[i][3]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const bool warp_ok = __all_sync(0xffffffffu, ok);
+    cluster_wait();                                              /* every CTA of the cluster has started */
+#pragma unroll
+    for (uint32_t i = 0; i < kNormRegChunks; i++) {
+        const uint32_t j = tid + i * THREADS;
+        if (j < per) {
+            const uint32_t at = xs_addr + (rank * per + j) * 16u;
+            const uint4 v = make_uint4(held[i][0], held[i][1], held[i][2], held[i][3]);
+            for (uint32_t r = 0; r < ctas; r++) cluster_sts128(cluster_addr(at, r), v);
+        }
+    }
+    if (lane == 0)
+        for (uint32_t r = 0; r < ctas; r++) cluster_sts64(cluster_addr(cl_addr + (rank * (THREADS / 32u) + warp) * 8u, r), ss, warp_ok ? 1.f : 0.f);
+    __syncwarp();
+    cluster_arrive();
+    cluster_wait();
+    float tot = 0.f;
+    bool good = true;
+    for (uint32_t e = lane; e < ctas * (THREADS / 32u); e += 32u) {
+        const float2 v = *reinterpret_cast<const float2 *>(cl + 2u * e);
+        tot += v.x;
+        good = good && v.y != 0.f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    if (!__all_sync(0xffffffffu, good)) {                        /* a rank is missing (every CTA of the cluster sees it): poison x */
+        if (tid == 0) atomicExch(&g_kernel_status, kStatusPeerTimeout);
+        for (uint32_t c = tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u));
+        __syncthreads();
+        return;
+    }
+    const float inv = rsqrtf(tot / (float)K + in.eps);
+#pragma unroll
+    for (uint32_t i = 0; i < kNormRegChunks; i++) {
+        const uint32_t c = tid + i * THREADS;
+        if (c < live) {
+            const uint4 v = lds128(xs_addr + c * 16u);
+            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+            sts128(xs_addr + c * 16u, normalised_chunk(vw, nr.w[i], inv));
+        }
+    }
+    for (uint32_t c = live + tid; c < chunks; c += THREADS) sts128(xs_addr + c * 16u, make_uint4(0u, 0u, 0u, 0u));
+    __syncthreads();
+}
+
 /* after the dependency wait; ends with __syncthreads().  scal: THREADS / 32 floats of shared memory. */
 template <uint32_t THREADS>
 __device__ __forceinline__ void build_activation(const FusedInput &in, const void *x, uint32_t K, uint32_t cols, uint16_t *xs, uint16_t *nw, float *scal,
@@ -690,7 +781,9 @@ constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 
 /* ELEM = fp8: the raw plane holds 3-bit fields, 96 bits per lane and PAIR of slots (384 B per pair), so the unit of all
    counting below is a pair of slots; the launcher takes this kernel only when every row group has an even number of slots. */
-template <int ELEM>
+/* SHARE: the instance that is launched when FusedInput::share is set (a kernel of its own so that the cluster's code
+   costs the other launches nothing). */
+template <int ELEM, bool SHARE>
 __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in, const NextFill nx) {
     constexpr uint32_t U = ELEM == kFp8 ? 2u : 1u;               /* slots per unit                                  */
     constexpr uint32_t kUnits = kRingSlots / U;                  /* units per stage                                 */
@@ -714,7 +807,11 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
        split the cluster's run evenly, then the warps split the CTA's run. */
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t cluster_ctas = cluster.num_blocks(), cta_rank = cluster.block_rank(), cluster_id = blockIdx.x / cluster_ctas;
+    /* (a cluster that exists only to share the pushed partials, FusedInput::share bit 1, is invisible to the plan) */
+    const uint32_t real_ctas = cluster.num_blocks(), real_rank = cluster.block_rank();
+    const bool share_only = SHARE && (in.share & 2u) != 0u;
+    const uint32_t cluster_ctas = share_only ? 1u : real_ctas, cta_rank = share_only ? 0u : real_rank, cluster_id = blockIdx.x / cluster_ctas;
+    if (SHARE) cluster_arrive();                                 /* "this CTA runs": waited for before the first store into its shared memory */
     const uint32_t k0 = plan.start(cluster_id), k1 = plan.start(cluster_id + 1u), cluster_shift = (uint32_t)__ffs((int)cluster_ctas) - 1u;   /* clusters of 1, 2, 4 or 8 */
     const uint32_t c0 = k0 + (((k1 - k0) * cta_rank) >> cluster_shift), c1 = k0 + (((k1 - k0) * (cta_rank + 1u)) >> cluster_shift);
     const uint32_t cn = c1 - c0, w0 = cn * warp / (kRingThreads / 32u), w1 = cn * (warp + 1u) / (kRingThreads / 32u);
@@ -767,7 +864,11 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
        (read by every CTA before any CTA can finish; the last CTA to finish counts the push) */
     const uint32_t push_call = a.push.world ? *reinterpret_cast<const volatile uint32_t *>(&reinterpret_cast<const CommControl *>(a.push.buf[a.push.rank])->push_epoch[a.push.slot]) + 1u : 0u;
     promote(); load_ahead(next_block + 1u);                      /* the first block's entries travel while x is built */
-    build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
+    if (SHARE)                                                   /* (the RMSNorm weight is in registers: its place in shared memory holds the cluster's scalars) */
+        build_activation_shared<kRingThreads>(in, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<float *>(ring_smem + x_bytes), norm_regs,
+                                              real_ctas, real_rank, blockIdx.x < real_ctas);
+    else
+        build_activation<kRingThreads>(in, a.x, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<uint16_t *>(ring_smem + x_bytes), scal, norm_regs);
     const uint32_t lane8 = lane * 8u, lane16 = kRingSlots * 256u + lane * (ELEM == kFp8 ? 4u : 16u), xq = xs + (lane & 3u) * 16u;
     uint32_t seg_first = s, entry = 2u * warp;                   /* first slot of the current segment; where a shared one goes */
     float d[4] = {0.f, 0.f, 0.f, 0.f}, ex_lo = 0.f, ex_hi = 0.f;
@@ -1309,6 +1410,39 @@ static void choose_ring_plan(int code, const Geometry &g, int input_mode, int sm
     }
     make_cta_plan_layout2(g, elem, ring_ctas(g, input_mode, sms), plan, cluster, allow_fix);
     pool = pool && plan.direct && cluster == 1u;
+}
+
+/* kInputPeerNorm: from this many ranks on, the ring kernel's launch is made of clusters that share the sum of the pushed
+   partials (build_activation_shared); 0 = never, the default.  Measured on B200 with 8192 values per partial and the same
+   kernel before and after: every CTA adding up all of them costs 2.3 / 4.4 / 8.4 us at 2 / 4 / 8 ranks, the clusters
+   2.2 / 3.0 / 4.4 us.  In the decode loop of the Llama-3-70B shapes on 2 / 4 / 8 GPUs the clusters nevertheless lose:
+   79.4 / 119.1 / 155.2 against 87.0 / 131.0 / 168.8 tokens/s, 3 to 7 us per cluster launch, with clusters of 2 as with
+   clusters of 4 - a cluster launch that follows a kernel of single CTAs does not start on the SMs that kernel frees one by
+   one, so the overlap that the dependent launch buys (about 4.5 us per boundary) is lost. */
+static int g_share_min_world = 0;
+void set_peer_sharing(int min_world) { g_share_min_world = min_world; }
+
+/* Decides FusedInput::share for a launch of the layout-2 ring kernel whose plan and cluster size have been chosen: a plan
+   that runs clusters anyway shares inside them; a plan of single CTAs is made again for the CTAs that clusters of 4 (else
+   2) can occupy at once, if those are nearly all of the device and the plan still wants single CTAs. */
+static uint32_t choose_peer_sharing(int code, const Geometry &g, const FusedInput &in, int sms, bool allow_fix, FlatPlan &plan, uint32_t &cluster) {
+    const uint32_t live = g.K >> 3;
+    if (in.mode != kInputPeerNorm || g_share_min_world <= 0 || (int)in.world < g_share_min_world) return 0u;
+    if ((g.K & 7u) != 0u || g.K < 1024u || live > kNormRegChunks * kRingThreads) return 0u;
+    if (cluster > 1u) return live % cluster == 0u ? 1u : 0u;
+    const ClusterRoom room = cluster_room(sms);
+    for (uint32_t lg = 2; lg >= 1u; lg--) {
+        const uint32_t size = 1u << lg, ctas = (uint32_t)room.count[lg] * size;
+        if (live % size != 0u || (uint64_t)ctas * 100u < (uint64_t)sms * 97u || ctas > (uint32_t)sms) continue;
+        FlatPlan p;
+        uint32_t c = 1u;
+        make_cta_plan_layout2(g, type_of(code), (int)ctas, p, c, allow_fix);
+        if (c != 1u || p.warps % size != 0u || p.direct != plan.direct || p.fix != plan.fix) continue;     /* (same number of launches either way) */
+        plan = p;
+        cluster = size;
+        return 3u;
+    }
+    return 0u;
 }
 
 /* ---- layouts 0 and 1, token path: lane streams staged in shared memory by bulk copies -------------------------------- */
@@ -2115,8 +2249,20 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
             return elem == kFp8 ? launch_kernel(pool_kernel_layout2<kFp8>, dim3(plan.warps), dim3(kRingThreads), smem, st, a, plan, in, nx, ps)
                                 : launch_kernel(pool_kernel_layout2<kBf16>, dim3(plan.warps), dim3(kRingThreads), smem, st, a, plan, in, nx, ps);
         }
-        err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
-                           : launch_cluster_kernel(ring_kernel_layout2<kBf16>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+        in.share = choose_peer_sharing(code, g, in, sms, a.fixup != 0u, plan, cluster);
+        if (in.share & 2u) {                                     /* clusters of CTAs that each own a run of the plan */
+            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, true>, cluster, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, true>, cluster, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+            if (err == cudaSuccess && !plan.direct && !plan.fix)
+                err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
+            return err;
+        }
+        if (in.share)                                            /* the plan's own clusters share the partials as well */
+            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, true>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, true>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+        else
+            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, false>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, false>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
         if (err == cudaSuccess && !plan.direct && !plan.fix)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
@@ -2150,7 +2296,7 @@ static ClusterRoom cluster_room(int sms) {
     if (dev < 0 || dev >= 64) dev = 0;
     if (!known[dev]) {
         ClusterRoom r{{sms, 0, 0, 0}};
-        cudaFuncSetAttribute(ring_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+        cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
         for (int lg = 1; lg < 4; lg++) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)sms / (1u << lg) * (1u << lg)); cfg.blockDim = dim3(kRingThreads); cfg.dynamicSmemBytes = kRingMaxSmem;
@@ -2158,7 +2304,7 @@ static ClusterRoom cluster_room(int sms) {
             attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 1u << lg; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr; cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
+            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16, false>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
         }
         cache[dev] = r; known[dev] = true;
     }
@@ -2177,8 +2323,10 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(small_split_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kFp8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(pool_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(pool_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     {                                                             /* no CTA has left a part of a row group for another one yet */

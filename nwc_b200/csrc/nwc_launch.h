@@ -47,6 +47,10 @@ struct FusedInput {
     const uint8_t *comm;
     uint32_t world, slot;
     unsigned long long timeout_ns;   /* longest wait for the peers' flags */
+    /* set by the launcher, kInputPeerNorm on the layout-2 ring kernel: bit 0 = the CTAs of a cluster each add up a share of
+       the pushed partials and hand the sums to one another through distributed shared memory; bit 1 = the cluster exists
+       for that alone (the plan's runs belong to single CTAs) */
+    uint32_t share;
 };
 /* The matrix that the launch following this one on the stream will read (a hint; null low = none).  When both launches
    take the layout-2 ring kernel, this launch asks L2 for the next launch's first bytes while its own tail runs. */
@@ -65,6 +69,7 @@ bool dependent_launch();
 
 uint32_t choose_splits(const Geometry &g, int mode, int code, int sms);
 void set_ring_kernels(bool on);               /* tests: switch the bulk-copy ring kernels off to compare with the plain ones */
+void set_peer_sharing(int min_world);         /* clusters share the sum of the pushed partials from this many ranks on (0 = never) */
 void set_pool_kernels(bool on);               /* tests: layout-2 kernel whose warps draw stages from a per-CTA pool on / off */
 void set_fixup_plans(bool on);                /* tests: equal runs with in-kernel fix-up of cut row groups on / off */
 int read_kernel_status(bool clear);           /* 0, or 2 when a bounded wait gave up; synchronises */

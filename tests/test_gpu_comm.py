@@ -106,16 +106,20 @@ def _io(L, table, rank, world, in_slot, out_slot, H):
     return io, ctypes.byref(io)
 
 
-@pytest.mark.parametrize("H,Kshard,world", [(1024, 512, 2), (2048, 1536, 2), (8192, 1024, 2), (1024, 512, 4), (8192, 1024, 4), (8192, 1024, 8), (2048, 512, 8)])
-def test_push_protocol_local_ranks(H, Kshard, world):
+@pytest.mark.parametrize("sharing", [0, 2])
+@pytest.mark.parametrize("H,Kshard,world,rows", [(1024, 512, 2, 768), (2048, 1536, 2, 768), (8192, 1024, 2, 768), (1024, 512, 4, 768), (8192, 1024, 4, 768),
+                                                 (8192, 1024, 8, 768), (2048, 512, 8, 768), (8192, 512, 8, 7168), (4096, 512, 4, 2576)])
+def test_push_protocol_local_ranks(H, Kshard, world, rows, sharing):
     """o-projection shards of `world` ranks (all on this GPU, one exchange buffer each) push into every buffer; the consumer
     (a column-parallel matrix with the fused peer prologue) must see h + (the partials added in rank order) and the RMSNorm
-    of it, for every rank alike, twice in a row."""
+    of it, for every rank alike, twice in a row - whether every CTA of the consumer adds up all partials (sharing 0) or the
+    CTAs of a cluster share that work (from 2 ranks on)."""
     from nwc_b200 import NWCWeight, _lib as L
     from nwc_b200.decode import synthetic_matrix
     g = torch.Generator().manual_seed(H + Kshard)
     o_shards = [NWCWeight(synthetic_matrix(H, Kshard, 10 + r), layout=2) for r in range(world)]   # row-parallel: [H, K / world] each
-    consumer = NWCWeight(synthetic_matrix(768, H, 20), layout=2)                                  # the matrix after the sum
+    consumer = NWCWeight(synthetic_matrix(rows, H, 20), layout=2)                                 # the matrix after the sum
+    L.lib.nwc_set_peer_sharing(sharing)
     xs = [torch.randn(Kshard, generator=g).to(torch.bfloat16).cuda() for _ in range(world)]
     h = torch.randn(H, generator=g).to(torch.bfloat16).cuda()
     norm_w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
@@ -138,20 +142,22 @@ def test_push_protocol_local_ranks(H, Kshard, world):
             want_y = consumer.linear_bf16(want_x, None)
             for r in range(world):                                        # then the consumers: every word is already there
                 keep, io = _io(L, table, r, world, slot, -1, H)
-                h_out, y = torch.zeros_like(h), torch.zeros(768, dtype=torch.bfloat16, device="cuda")
+                h_out, y = torch.zeros_like(h), torch.zeros(rows, dtype=torch.bfloat16, device="cuda")
                 assert _tp_linear(L, consumer, 1, io, h_in=h, h_out=h_out, norm_w=norm_w, y=y) == 0
                 torch.cuda.synchronize()
                 assert torch.equal(h_out, want_h), (round_no, r)
                 assert (y.float() - want_y.float()).abs().max().item() <= 2.0 ** -6 * want_y.float().abs().max().item() + 1e-6
             assert L.lib.nwc_kernel_status(1) == 0
     finally:
+        L.lib.nwc_set_peer_sharing(0)
         for buf in bufs: L.lib.nwc_comm_free(ctypes.c_void_p(buf))
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_push_consumer_gives_up_when_a_rank_never_pushes(world):
+@pytest.mark.parametrize("world,sharing", [(2, 0), (4, 0), (4, 2)])
+def test_push_consumer_gives_up_when_a_rank_never_pushes(world, sharing):
     """The last rank never pushes: rank 0's consumer waits the (shortened) limit, reports status 3 and poisons its output with
-    NaN instead of publishing a sum that misses a partial; the context stays usable."""
+    NaN instead of publishing a sum that misses a partial; the context stays usable.  (sharing 2: the CTAs of a cluster
+    share the sum, and all of them learn that a word is missing.)"""
     from nwc_b200 import NWCWeight, _lib as L
     from nwc_b200.decode import synthetic_matrix
     H = 1024
@@ -162,6 +168,7 @@ def test_push_consumer_gives_up_when_a_rank_never_pushes(world):
     bufs = _buffers(L, H, world)
     table = (ctypes.c_void_p * world)(*bufs)
     L.lib.nwc_comm_set_timeout_ms(40)
+    L.lib.nwc_set_peer_sharing(sharing)
     try:
         for r in range(world - 1):                                        # everybody but the last rank pushes
             keep, io = _io(L, table, r, world, -1, 0, H)
@@ -174,6 +181,7 @@ def test_push_consumer_gives_up_when_a_rank_never_pushes(world):
         assert torch.isnan(y.float()).all()
         assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
     finally:
+        L.lib.nwc_set_peer_sharing(0)
         L.lib.nwc_comm_set_timeout_ms(2000)
         for buf in bufs: L.lib.nwc_comm_free(ctypes.c_void_p(buf))
 
