@@ -782,9 +782,11 @@ constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 /* ELEM = fp8: the raw plane holds 3-bit fields, 96 bits per lane and PAIR of slots (384 B per pair), so the unit of all
    counting below is a pair of slots; the launcher takes this kernel only when every row group has an even number of slots. */
 /* SHARE: the instance that is launched when FusedInput::share is set (a kernel of its own so that the cluster's code
-   costs the other launches nothing). */
-template <int ELEM, bool SHARE>
-__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in, const NextFill nx) {
+   costs the other launches nothing).  MODE: the launch's FusedInputMode. */
+template <int ELEM, bool SHARE, int MODE>
+__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput input, const NextFill nx) {
+    FusedInput in = input;
+    in.mode = MODE;                                              /* one instance per input mode: the prologues of the other modes cost this one nothing */
     constexpr uint32_t U = ELEM == kFp8 ? 2u : 1u;               /* slots per unit                                  */
     constexpr uint32_t kUnits = kRingSlots / U;                  /* units per stage                                 */
     constexpr uint32_t kNibUnit = 256u * U, kRawUnit = ELEM == kFp8 ? 384u : 512u;      /* bytes of a unit in the two planes */
@@ -2196,6 +2198,18 @@ static NextFill make_next_fill(const NextMatrix *next, int sms) {
     return nx;
 }
 
+template <int ELEM>
+static cudaError_t launch_ring_kernel(uint32_t cluster, uint32_t ctas, size_t smem, cudaStream_t st, const SegmentArgs &a, const FlatPlan &plan, const FusedInput &in, const NextFill &nx) {
+    const dim3 grid(ctas), block(kRingThreads);
+    if (in.share) return launch_cluster_kernel(ring_kernel_layout2<ELEM, true, kInputPeerNorm>, cluster, grid, block, smem, st, a, plan, in, nx);
+    switch (in.mode) {
+        case kInputNorm: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputNorm>, cluster, grid, block, smem, st, a, plan, in, nx);
+        case kInputSwiglu: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputSwiglu>, cluster, grid, block, smem, st, a, plan, in, nx);
+        case kInputPeerNorm: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputPeerNorm>, cluster, grid, block, smem, st, a, plan, in, nx);
+        default: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputPlain>, cluster, grid, block, smem, st, a, plan, in, nx);
+    }
+}
+
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input, const NextMatrix *next) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(a.M, a.K, layout);
@@ -2250,19 +2264,9 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
                                 : launch_kernel(pool_kernel_layout2<kBf16>, dim3(plan.warps), dim3(kRingThreads), smem, st, a, plan, in, nx, ps);
         }
         in.share = choose_peer_sharing(code, g, in, sms, a.fixup != 0u, plan, cluster);
-        if (in.share & 2u) {                                     /* clusters of CTAs that each own a run of the plan */
-            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, true>, cluster, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
-                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, true>, cluster, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
-            if (err == cudaSuccess && !plan.direct && !plan.fix)
-                err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
-            return err;
-        }
-        if (in.share)                                            /* the plan's own clusters share the partials as well */
-            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, true>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
-                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, true>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
-        else
-            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, false>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
-                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, false>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+        /* (sharing alone: the clusters are made of CTAs that each own a run of the plan) */
+        err = elem == kFp8 ? launch_ring_kernel<kFp8>(cluster, (in.share & 2u) ? plan.warps : plan.warps * cluster, ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                           : launch_ring_kernel<kBf16>(cluster, (in.share & 2u) ? plan.warps : plan.warps * cluster, ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
         if (err == cudaSuccess && !plan.direct && !plan.fix)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
@@ -2286,6 +2290,14 @@ static void opt_in_smem() {
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeDequant, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeAtomic, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
+template <int ELEM>
+static void opt_in_ring() {
+    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputNorm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputPeerNorm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, true, kInputPeerNorm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+}
 static ClusterRoom cluster_room(int sms) {
     static ClusterRoom cache[64];
     static bool known[64];
@@ -2296,7 +2308,7 @@ static ClusterRoom cluster_room(int sms) {
     if (dev < 0 || dev >= 64) dev = 0;
     if (!known[dev]) {
         ClusterRoom r{{sms, 0, 0, 0}};
-        cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+        cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false, kInputPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
         for (int lg = 1; lg < 4; lg++) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)sms / (1u << lg) * (1u << lg)); cfg.blockDim = dim3(kRingThreads); cfg.dynamicSmemBytes = kRingMaxSmem;
@@ -2304,7 +2316,7 @@ static ClusterRoom cluster_room(int sms) {
             attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 1u << lg; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr; cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16, false>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
+            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16, false, kInputPlain>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
         }
         cache[dev] = r; known[dev] = true;
     }
@@ -2323,10 +2335,7 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(small_split_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<kFp8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    opt_in_ring<kBf16>(); opt_in_ring<kFp8>();
     cudaFuncSetAttribute(pool_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(pool_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     {                                                             /* no CTA has left a part of a row group for another one yet */
