@@ -702,14 +702,13 @@ static __device__ unsigned int g_cut_part[kFixCounters][16];
    = the 16 lanes, all of which make this call): scale, bias and bf16 rounding as the reference's finalize step, then
    either the local y or, for a row-parallel matrix of a tensor-parallel group, the push slot of EVERY rank's exchange
    buffer (plain 4-byte stores over NVLink, two rows each; the flag that publishes them is raised at the kernel's end). */
-template <bool LOCAL = false>                                    /* LOCAL: the caller knows that the output stays on this GPU */
 __device__ __forceinline__ void emit_group(const SegmentArgs &a, uint32_t grp, uint32_t sub, float v, uint32_t mask, uint32_t push_call) {
     const uint32_t row = grp * 16u + sub;
     const bool live = row < a.M;
     if (live && a.scale) v *= __ldg(a.scale + row);
     if (live && a.bias) v += bf16_to_float(__ldg(a.bias + row));
     const uint32_t h = live ? (uint32_t)bf16_round_nan(v) : 0u;        /* (the reference's rounding for every finite value; NaN stays NaN) */
-    if (LOCAL || a.push.world == 0u) { if (live) a.y[row] = (uint16_t)h; return; }
+    if (a.push.world == 0u) { if (live) a.y[row] = (uint16_t)h; return; }
     const uint32_t pair = h | (__shfl_down_sync(mask, h, 1) << 16);
     if ((sub & 1u) == 0u && live) {
         const uint64_t off = comm_push_offset(a.push.H, a.push.slot, a.push.rank) + (uint64_t)(row >> 1) * 8u;
@@ -783,14 +782,16 @@ constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 /* ELEM = fp8: the raw plane holds 3-bit fields, 96 bits per lane and PAIR of slots (384 B per pair), so the unit of all
    counting below is a pair of slots; the launcher takes this kernel only when every row group has an even number of slots. */
 /* SHARE: the instance that is launched when FusedInput::share is set (a kernel of its own so that the cluster's code
-   costs the other launches nothing).  MODE: the launch's FusedInputMode.  WHOLE: see below. */
-template <int ELEM, bool SHARE, int MODE, bool WHOLE>
-__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput input, const NextFill nx) {
-    FusedInput in = input;
-    in.mode = MODE;                                              /* one instance per input mode: the prologues of the other modes cost this one nothing */
-    /* WHOLE: whole row groups per CTA, no clusters, output on this GPU - the plan's other shapes compiled out */
-    const bool plan_direct = WHOLE || plan.direct != 0u, plan_fix = !WHOLE && plan.fix != 0u;
-    const uint32_t push_world = WHOLE ? 0u : a.push.world;
+   costs the other launches nothing).
+   Everything else - the four input modes, whole and cut row groups, local and pushed output - is deliberately ONE
+   instance per element type.  Instances per input mode, and instances with the cut-group, cluster and push code compiled
+   out for plans of whole row groups, were built and measured on B200 against this one on the same box: each of them is
+   faster when it runs back to back with itself (6144 x 2560: 8.15 against 8.65 us; 57344 x 8192: 112.4 against 115.0 us),
+   but a decode step alternates between them and comes out slower (Qwen3-4B 428 against 439 tokens/s, Llama-3-70B shapes
+   50.4 against 50.8, two GPUs 82 against 87): a launch whose code the previous launch left in the instruction caches
+   starts faster than a shorter kernel that has to be fetched. */
+template <int ELEM, bool SHARE>
+__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layout2(const SegmentArgs a, const FlatPlan plan, const FusedInput in, const NextFill nx) {
     constexpr uint32_t U = ELEM == kFp8 ? 2u : 1u;               /* slots per unit                                  */
     constexpr uint32_t kUnits = kRingSlots / U;                  /* units per stage                                 */
     constexpr uint32_t kNibUnit = 256u * U, kRawUnit = ELEM == kFp8 ? 384u : 512u;      /* bytes of a unit in the two planes */
@@ -814,7 +815,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     /* (a cluster that exists only to share the pushed partials, FusedInput::share bit 1, is invisible to the plan) */
-    const uint32_t real_ctas = WHOLE ? 1u : cluster.num_blocks(), real_rank = WHOLE ? 0u : cluster.block_rank();
+    const uint32_t real_ctas = cluster.num_blocks(), real_rank = cluster.block_rank();
     const bool share_only = SHARE && (in.share & 2u) != 0u;
     const uint32_t cluster_ctas = share_only ? 1u : real_ctas, cta_rank = share_only ? 0u : real_rank, cluster_id = blockIdx.x / cluster_ctas;
     if (SHARE) cluster_arrive();                                 /* "this CTA runs": waited for before the first store into its shared memory */
@@ -868,7 +869,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
     asm volatile("griddepcontrol.wait;" ::: "memory");
     /* tensor-parallel output: the call number that this launch's words carry = this rank's pushes to the slot so far + 1
        (read by every CTA before any CTA can finish; the last CTA to finish counts the push) */
-    const uint32_t push_call = push_world ? *reinterpret_cast<const volatile uint32_t *>(&reinterpret_cast<const CommControl *>(a.push.buf[a.push.rank])->push_epoch[a.push.slot]) + 1u : 0u;
+    const uint32_t push_call = a.push.world ? *reinterpret_cast<const volatile uint32_t *>(&reinterpret_cast<const CommControl *>(a.push.buf[a.push.rank])->push_epoch[a.push.slot]) + 1u : 0u;
     promote(); load_ahead(next_block + 1u);                      /* the first block's entries travel while x is built */
     if (SHARE)                                                   /* (the RMSNorm weight is in registers: its place in shared memory holds the cluster's scalars) */
         build_activation_shared<kRingThreads>(in, a.K, x_bytes >> 1, reinterpret_cast<uint16_t *>(ring_smem), reinterpret_cast<float *>(ring_smem + x_bytes), norm_regs,
@@ -885,10 +886,10 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
         const float lo = d[0] + ex_lo, hi = d[2] + ex_hi;
         const uint32_t r = lane >> 2;
         if (seg_first == 0u && s == slots) {                     /* a whole row group: nobody else adds to it */
-            if (plan_direct || plan_fix) {                       /* final: row i of the group to lane i < 16, from the quad leader that holds it */
+            if (plan.direct || plan.fix) {                       /* final: row i of the group to lane i < 16, from the quad leader that holds it */
                 const uint32_t src = (lane & 7u) << 2;
                 const float vlo = __shfl_sync(0xffffffffu, lo, src), vhi = __shfl_sync(0xffffffffu, hi, src);
-                if (lane < 16u) emit_group<WHOLE>(a, rb, lane, (lane & 8u) ? vhi : vlo, 0x0000FFFFu, push_call);
+                if (lane < 16u) emit_group(a, rb, lane, (lane & 8u) ? vhi : vlo, 0x0000FFFFu, push_call);
             } else if ((lane & 3u) == 0u) {
                 const uint32_t part = cluster_id - plan.owner(rb * slots);
                 emit_flat(a, plan, rb * 16u + r, part, lo); emit_flat(a, plan, rb * 16u + r + 8u, part, hi);
@@ -987,8 +988,8 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
             const uint32_t g0 = grp * slots;
             const bool inside = g0 >= c0 && g0 + slots <= c1;
             const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16u);
-            if (plan_direct ? (cluster_ctas == 1u || inside) : (plan_fix && inside)) emit_group<WHOLE>(a, grp, row, v, half_mask, push_call);
-            else if (plan_fix) {
+            if (plan.direct ? (cluster_ctas == 1u || inside) : (plan.fix && inside)) emit_group(a, grp, row, v, half_mask, push_call);
+            else if (plan.fix) {
                 /* Equal runs: a row group cut by run boundaries.  A CTA whose run holds a later part of it leaves that part
                    in its own entry of g_cut_part; the CTA where the group begins adds the later parts in CTA order (so the
                    sum does not depend on timing), writes the rows and empties the entries again.  One trip through L2 after
@@ -1011,7 +1012,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
                         if (ok) { v += __uint_as_float(w); *theirs = kCutEmpty; }
                     }
                     if (!ok) { atomicExch(&g_kernel_status, kStatusWaitTimeout); v = __uint_as_float(0x7FC00000u); }
-                    emit_group<WHOLE>(a, grp, row, v, half_mask, push_call);
+                    emit_group(a, grp, row, v, half_mask, push_call);
                 }
             }
             else if (cluster_ctas == 1u) emit_flat(a, plan, grp * 16u + row, cluster_id - plan.owner(g0), v);      /* one fp32 partial per CTA */
@@ -1034,14 +1035,14 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) ring_kernel_layo
                     if (theirs == grp) v += cluster.map_shared_rank(cta_value, r)[row];
                     else if (theirs != kNoGroup) break;          /* (no entry: an empty run, or one that starts on a group boundary) */
                 }
-                emit_group<WHOLE>(a, grp, row, v, 0xFFFFu << (threadIdx.x & 16u), push_call);
+                emit_group(a, grp, row, v, 0xFFFFu << (threadIdx.x & 16u), push_call);
             }
         }
         cluster.sync();                                             /* nobody leaves while its shared memory may still be read */
     }
     /* Tensor-parallel output: the words this launch stored carry their own call number, nothing has to be published; the
        CTA that finishes last counts the push (every CTA read the count before any CTA could get here). */
-    if (push_world && threadIdx.x == 0) {
+    if (a.push.world && threadIdx.x == 0) {
         CommControl *own = reinterpret_cast<CommControl *>(a.push.buf[a.push.rank]);
         if (atomicAdd(&own->push_done, 1u) == gridDim.x - 1u) {
             own->push_done = 0u;
@@ -2202,24 +2203,6 @@ static NextFill make_next_fill(const NextMatrix *next, int sms) {
     return nx;
 }
 
-template <int ELEM, bool WHOLE>
-static cudaError_t launch_ring_modes(uint32_t cluster, dim3 grid, size_t smem, cudaStream_t st, const SegmentArgs &a, const FlatPlan &plan, const FusedInput &in, const NextFill &nx) {
-    const dim3 block(kRingThreads);
-    switch (in.mode) {
-        case kInputNorm: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputNorm, WHOLE>, cluster, grid, block, smem, st, a, plan, in, nx);
-        case kInputSwiglu: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputSwiglu, WHOLE>, cluster, grid, block, smem, st, a, plan, in, nx);
-        case kInputPeerNorm: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputPeerNorm, WHOLE>, cluster, grid, block, smem, st, a, plan, in, nx);
-        default: return launch_cluster_kernel(ring_kernel_layout2<ELEM, false, kInputPlain, WHOLE>, cluster, grid, block, smem, st, a, plan, in, nx);
-    }
-}
-template <int ELEM>
-static cudaError_t launch_ring_kernel(uint32_t cluster, uint32_t ctas, size_t smem, cudaStream_t st, const SegmentArgs &a, const FlatPlan &plan, const FusedInput &in, const NextFill &nx) {
-    const dim3 grid(ctas);
-    if (in.share) return launch_cluster_kernel(ring_kernel_layout2<ELEM, true, kInputPeerNorm, false>, cluster, grid, dim3(kRingThreads), smem, st, a, plan, in, nx);
-    if (plan.direct && !plan.fix && cluster == 1u && a.push.world == 0u) return launch_ring_modes<ELEM, true>(cluster, grid, smem, st, a, plan, in, nx);
-    return launch_ring_modes<ELEM, false>(cluster, grid, smem, st, a, plan, in, nx);
-}
-
 cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, SegmentArgs a, const FusedInput *input, const NextMatrix *next) {
     const int layout = layout_of(code), elem = type_of(code);
     const Geometry g(a.M, a.K, layout);
@@ -2274,9 +2257,19 @@ cudaError_t launch_segments(int mode, int code, int sms, cudaStream_t st, Segmen
                                 : launch_kernel(pool_kernel_layout2<kBf16>, dim3(plan.warps), dim3(kRingThreads), smem, st, a, plan, in, nx, ps);
         }
         in.share = choose_peer_sharing(code, g, in, sms, a.fixup != 0u, plan, cluster);
-        /* (sharing alone: the clusters are made of CTAs that each own a run of the plan) */
-        err = elem == kFp8 ? launch_ring_kernel<kFp8>(cluster, (in.share & 2u) ? plan.warps : plan.warps * cluster, ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
-                           : launch_ring_kernel<kBf16>(cluster, (in.share & 2u) ? plan.warps : plan.warps * cluster, ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+        if (in.share & 2u) {                                     /* clusters of CTAs that each own a run of the plan */
+            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, true>, cluster, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, true>, cluster, dim3(plan.warps), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+            if (err == cudaSuccess && !plan.direct && !plan.fix)
+                err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
+            return err;
+        }
+        if (in.share)                                            /* the plan's own clusters share the partials as well */
+            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, true>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, true>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
+        else
+            err = elem == kFp8 ? launch_cluster_kernel(ring_kernel_layout2<kFp8, false>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx)
+                               : launch_cluster_kernel(ring_kernel_layout2<kBf16, false>, cluster, dim3(plan.warps * cluster), dim3(kRingThreads), ring_smem_bytes(g, in.mode), st, a, plan, in, nx);
         if (err == cudaSuccess && !plan.direct && !plan.fix)
             err = launch_kernel(finalize_flat_kernel, dim3((a.M + 255u) / 256u), dim3(256), 0, st, a.y32, a.bias, a.scale, a.y, a.M, g.rows, plan);
         return err;
@@ -2300,18 +2293,6 @@ static void opt_in_smem() {
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeDequant, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     cudaFuncSetAttribute(segment_kernel<LAYOUT, ELEM, kModeAtomic, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
-template <int ELEM, bool WHOLE>
-static void opt_in_ring_modes() {
-    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputPlain, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputNorm, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputSwiglu, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, false, kInputPeerNorm, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-}
-template <int ELEM>
-static void opt_in_ring() {
-    opt_in_ring_modes<ELEM, false>(); opt_in_ring_modes<ELEM, true>();
-    cudaFuncSetAttribute(ring_kernel_layout2<ELEM, true, kInputPeerNorm, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-}
 static ClusterRoom cluster_room(int sms) {
     static ClusterRoom cache[64];
     static bool known[64];
@@ -2322,7 +2303,7 @@ static ClusterRoom cluster_room(int sms) {
     if (dev < 0 || dev >= 64) dev = 0;
     if (!known[dev]) {
         ClusterRoom r{{sms, 0, 0, 0}};
-        cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false, kInputPlain, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+        cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
         for (int lg = 1; lg < 4; lg++) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)sms / (1u << lg) * (1u << lg)); cfg.blockDim = dim3(kRingThreads); cfg.dynamicSmemBytes = kRingMaxSmem;
@@ -2330,7 +2311,7 @@ static ClusterRoom cluster_room(int sms) {
             attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 1u << lg; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr; cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16, false, kInputPlain, false>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
+            if (cudaOccupancyMaxActiveClusters(&n, ring_kernel_layout2<kBf16, false>, &cfg) == cudaSuccess) r.count[lg] = n; else cudaGetLastError();
         }
         cache[dev] = r; known[dev] = true;
     }
@@ -2349,7 +2330,10 @@ void configure_segment_kernels() {
     cudaFuncSetAttribute(small_split_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(small_kernel_layout0<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
-    opt_in_ring<kBf16>(); opt_in_ring<kFp8>();
+    cudaFuncSetAttribute(ring_kernel_layout2<kBf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kFp8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
+    cudaFuncSetAttribute(ring_kernel_layout2<kFp8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(pool_kernel_layout2<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     cudaFuncSetAttribute(pool_kernel_layout2<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingMaxSmem);
     {                                                             /* no CTA has left a part of a row group for another one yet */
