@@ -32,6 +32,16 @@ def test_abi_exports_every_declared_symbol(lib):
     for name in declared: assert hasattr(lib, name), name
 
 
+@pytest.mark.parametrize("H", [8, 1024, 2560, 8192, 16384])
+def test_exchange_buffer_size_follows_the_documented_layout(lib, H):
+    """A tensor-parallel exchange buffer = a 512-byte header, two pull slots of H bf16 values and, for each of two push
+    slots, one partial per possible rank (8) of H / 2 eight-byte words {two bf16 rows, push number}; every slot rounded up
+    to 256 bytes.  Pure host arithmetic: the hosts that allocate the buffer themselves rely on it."""
+    lib.nwc_comm_bytes.restype, lib.nwc_comm_bytes.argtypes = ctypes.c_uint64, [ctypes.c_uint32]
+    up = lambda n: (n + 255) // 256 * 256
+    assert lib.nwc_comm_bytes(H) == 512 + 2 * up(2 * H) + 2 * 8 * up(4 * H)
+
+
 def test_info_and_layout_match_reference_contract(lib):
     lib.nwc_info.restype = ctypes.c_int
     assert [lib.nwc_info(i) for i in range(9)] == [11, 1, 4096, 32, 4096, 1, 1, 1, -1]
